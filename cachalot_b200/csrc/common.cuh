@@ -1,0 +1,96 @@
+// Shared helpers for the sm_100a kernels: error plumbing, cache-hinted loads, small numeric
+// conversions.  Everything here is header-only and internal to the library.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/cachalot_b200.h"
+
+namespace cachalot {
+
+void set_error(const char* fmt, ...);
+
+inline int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  set_error("%s", buf);
+  return code;
+}
+
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(CACHALOT_ECUDA, "%s: %s", what, cudaGetErrorString(e));
+  return CACHALOT_OK;
+}
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// ---- device helpers ---------------------------------------------------------------------
+
+// 128-bit streaming load: weights are read exactly once, so keep them out of L1.
+__device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ld_stream_u2(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_stream_u32(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// 2**(raw-127) for an E8M0 byte, exact: normal floats for raw >= 1, the denormal 2**-127 for raw == 0.
+__device__ __forceinline__ float e8m0_to_f32(uint32_t raw) {
+  return raw ? __uint_as_float(raw << 23) : __uint_as_float(0x00400000u);
+}
+
+// E2M1 code (low 3 bits = magnitude index, bit 3 = sign) -> float.  Magnitudes 0,.5,1,1.5,2,3,4,6;
+// code 8 gives +0.0 like the reference's table.
+__device__ __forceinline__ float e2m1_to_f32(uint32_t code) {
+  // magnitude m: e = m>>1, f = m&1.  e==0: f*0.5 ; else 2**(e-1) * (1 + f/2)
+  uint32_t m = code & 7u;
+  uint32_t e = m >> 1, f = m & 1u;
+  uint32_t bits = e ? (((e + 126u) << 23) | (f << 22)) : (f ? 0x3F000000u : 0u);
+  if ((code & 8u) && m) bits |= 0x80000000u;
+  return __uint_as_float(bits);
+}
+
+// SwiGLU with the reference's clamp: up both sides, gate from above only, when limit > 0.
+__device__ __forceinline__ float swiglu(float g, float u, float limit) {
+  if (limit > 0.f) {
+    u = fminf(fmaxf(u, -limit), limit);
+    g = fminf(g, limit);
+  }
+  return g / (1.0f + expf(-g)) * u;
+}
+
+}  // namespace cachalot

@@ -1,0 +1,367 @@
+// Decode-time routed experts over bank slots: two launches per call for all (token, route slot)
+// rows, as the reference's fused pair does for one token:
+//   gate_up : hidden[r, i] = silu(min(g,L)) * clip(u,+-L) * gate_w[r]      r = token*k + route slot
+//   down    : out[t, n]    = sum_j  W2_{slot(t,j)}[n, :] . hidden[t*k+j, :]  (j = 0..k-1 in order)
+// Weights are read as 16-byte chunks straight from the slot record (FP4: 32 codes + one E8M0
+// byte; 2-bit affine: 64 codes, scale/bias per group), activations sit in shared memory in a
+// chunk-transposed order so that a warp's lanes hit distinct banks.
+#include "kernels.cuh"
+
+namespace cachalot {
+
+struct BankView {
+  const uint8_t* base;
+  long long record_bytes;
+  long long off[9];
+  int n_slots, hidden, inter, bits, group, scale_dtype;
+};
+
+template <int FMT>
+struct Fmt;
+template <>
+struct Fmt<CACHALOT_BANK_FP4> {
+  static constexpr int CH = 32;  // elements per 16-byte chunk
+};
+template <>
+struct Fmt<CACHALOT_BANK_AFFINE> {
+  static constexpr int CH = 64;  // 2-bit codes per 16-byte chunk
+};
+
+__device__ __forceinline__ float scale_at(const void* p, long long i, int dt) {
+  return dt == CACHALOT_F16 ? __half2float(reinterpret_cast<const __half*>(p)[i])
+                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+// Lane-partial dot product of one weight row with the activation in shared memory.
+//   xs    : activation, element (c*CH + i) stored at xs[i*nch + c]
+//   xsum  : per-chunk sums of the activation (affine only)
+template <int FMT>
+__device__ __forceinline__ float row_dot(const uint8_t* __restrict__ w, const uint8_t* __restrict__ sc,
+                                         const uint8_t* __restrict__ bi, long long row, int K, int group, int sdt,
+                                         const float* __restrict__ xs, const float* __restrict__ xsum,
+                                         const float* __restrict__ lut, int lane) {
+  constexpr int CH = Fmt<FMT>::CH;
+  const int nch = K / CH;
+  const uint8_t* wrow = w + row * (long long)(nch * 16);
+  float acc = 0.f;
+  for (int c = lane; c < nch; c += 32) {
+    uint4 v = ld_stream_u4(wrow + (size_t)c * 16);
+    uint32_t words[4] = {v.x, v.y, v.z, v.w};
+    float part = 0.f;
+    if constexpr (FMT == CACHALOT_BANK_FP4) {
+      float s = e8m0_to_f32(sc[row * nch + c]);
+#pragma unroll
+      for (int wi = 0; wi < 4; ++wi) {
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          uint32_t code = (words[wi] >> (4 * n)) & 15u;
+          part = fmaf(lut[code], xs[(wi * 8 + n) * nch + c], part);
+        }
+      }
+      acc = fmaf(part, s, acc);
+    } else {
+      // groups run over the flattened [N*K] element index, which is the reference's [N, K/group]
+      // layout whenever K is a multiple of the group
+      long long g = (row * (long long)K + (long long)c * CH) / group;
+      float s = scale_at(sc, g, sdt), b = scale_at(bi, g, sdt);
+#pragma unroll
+      for (int wi = 0; wi < 4; ++wi) {
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+          uint32_t code = (words[wi] >> (2 * n)) & 3u;
+          part = fmaf(lut[code], xs[(wi * 16 + n) * nch + c], part);
+        }
+      }
+      acc = fmaf(s, part, acc);
+      acc = fmaf(b, xsum[c], acc);
+    }
+  }
+  return acc;
+}
+
+__device__ __forceinline__ void fill_lut(float* lut, int fmt) {
+  if (threadIdx.x < 16) lut[threadIdx.x] = fmt == CACHALOT_BANK_FP4 ? e2m1_to_f32(threadIdx.x) : (float)threadIdx.x;
+}
+
+// stage `K` activations (read through `get(k)`) chunk-transposed, plus per-chunk sums
+template <int CH, typename F>
+__device__ __forceinline__ void stage(float* xs, float* xsum, int K, F get) {
+  const int nch = K / CH;
+  for (int e = threadIdx.x; e < K; e += blockDim.x) {
+    int c = e / CH, i = e - c * CH;
+    xs[i * nch + c] = get(e);
+  }
+  __syncthreads();
+  if (xsum) {
+    for (int c = threadIdx.x; c < nch; c += blockDim.x) {
+      float s = 0.f;
+      for (int i = 0; i < CH; ++i) s += xs[i * nch + c];
+      xsum[c] = s;
+    }
+    __syncthreads();
+  }
+}
+
+constexpr int WARPS = 8;
+
+// grid = (ceil(I / WARPS), rows*k): one warp per (row r, intermediate index i)
+template <int FMT>
+__global__ void __launch_bounds__(WARPS * 32)
+gate_up_kernel(BankView bank, const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ slots,
+               const float* __restrict__ gate_w, int k, float limit, int numerics, float* __restrict__ hidden,
+               int* __restrict__ status) {
+  extern __shared__ float smem[];
+  constexpr int CH = Fmt<FMT>::CH;
+  const int H = bank.hidden, I = bank.inter;
+  float* xs = smem;
+  float* xsum = FMT == CACHALOT_BANK_AFFINE ? smem + H : nullptr;
+  __shared__ float lut[16];
+  const int r = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int i = blockIdx.x * WARPS + warp;
+  const int slot = slots[r];
+  if (slot < 0 || slot >= bank.n_slots) {  // absent expert: zero rows, never an out-of-range read
+    if (slot >= bank.n_slots && status && threadIdx.x == 0) atomicOr(status, CACHALOT_STATUS_SLOT_RANGE);
+    if (i < I && lane == 0) hidden[(size_t)r * I + i] = 0.f;
+    return;
+  }
+  fill_lut(lut, FMT);
+  const __nv_bfloat16* xr = x + (size_t)(r / k) * H;
+  stage<CH>(xs, xsum, H, [&](int e) { return __bfloat162float(xr[e]); });
+  __syncthreads();
+  if (i >= I) return;
+  const uint8_t* rec = bank.base + (size_t)slot * bank.record_bytes;
+  float g, u;
+  if constexpr (FMT == CACHALOT_BANK_FP4) {
+    g = row_dot<FMT>(rec + bank.off[0], rec + bank.off[1], nullptr, i, H, 32, 0, xs, xsum, lut, lane);
+    u = row_dot<FMT>(rec + bank.off[4], rec + bank.off[5], nullptr, i, H, 32, 0, xs, xsum, lut, lane);
+  } else {
+    g = row_dot<FMT>(rec + bank.off[0], rec + bank.off[1], rec + bank.off[2], i, H, bank.group, bank.scale_dtype, xs, xsum, lut, lane);
+    u = row_dot<FMT>(rec + bank.off[6], rec + bank.off[7], rec + bank.off[8], i, H, bank.group, bank.scale_dtype, xs, xsum, lut, lane);
+  }
+  g = warp_sum(g);
+  u = warp_sum(u);
+  if (lane == 0) {
+    if (numerics == CACHALOT_NUMERICS_BF16) {
+      g = bf16_round(g);
+      u = bf16_round(u);
+    }
+    float h = swiglu(g, u, limit) * gate_w[r];
+    if (numerics == CACHALOT_NUMERICS_BF16) h = bf16_round(h);
+    hidden[(size_t)r * I + i] = h;
+  }
+}
+
+// grid = (ceil(H / WARPS), rows): one warp per (token t, output index n), experts summed j = 0..k-1
+template <int FMT, typename OutT>
+__global__ void __launch_bounds__(WARPS * 32)
+down_kernel(BankView bank, const float* __restrict__ hidden, const int32_t* __restrict__ slots, int k, int numerics,
+            OutT* __restrict__ out) {
+  extern __shared__ float smem[];
+  constexpr int CH = Fmt<FMT>::CH;
+  const int H = bank.hidden, I = bank.inter;
+  float* hs = smem;
+  float* hsum = FMT == CACHALOT_BANK_AFFINE ? smem + I : nullptr;
+  __shared__ float lut[16];
+  const int t = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * WARPS + warp;
+  fill_lut(lut, FMT);
+  float total = 0.f;
+  for (int j = 0; j < k; ++j) {
+    const int r = t * k + j;
+    const int slot = slots[r];
+    if (slot < 0 || slot >= bank.n_slots) continue;  // uniform across the CTA
+    __syncthreads();
+    const float* hr = hidden + (size_t)r * I;
+    stage<CH>(hs, hsum, I, [&](int e) { return hr[e]; });
+    __syncthreads();
+    if (n < H) {
+      const uint8_t* rec = bank.base + (size_t)slot * bank.record_bytes;
+      float y;
+      if constexpr (FMT == CACHALOT_BANK_FP4)
+        y = row_dot<FMT>(rec + bank.off[2], rec + bank.off[3], nullptr, n, I, 32, 0, hs, hsum, lut, lane);
+      else
+        y = row_dot<FMT>(rec + bank.off[3], rec + bank.off[4], rec + bank.off[5], n, I, bank.group, bank.scale_dtype, hs, hsum, lut, lane);
+      y = warp_sum(y);
+      if (numerics == CACHALOT_NUMERICS_BF16) y = bf16_round(y);
+      total += y;
+    }
+  }
+  if (n < H && lane == 0) {
+    if constexpr (sizeof(OutT) == 2)
+      out[(size_t)t * H + n] = __float2bfloat16_rn(total);
+    else
+      out[(size_t)t * H + n] = total;
+  }
+}
+
+static int make_view(const void* bank, const cachalot_bank_desc* d, BankView* v, const char* who) {
+  if (!bank || !d) return fail(CACHALOT_EINVAL, "%s: null bank", who);
+  if (d->hidden <= 0 || d->inter <= 0 || d->n_slots <= 0) return fail(CACHALOT_EINVAL, "%s: bad bank shape", who);
+  int n_t;
+  if (d->format == CACHALOT_BANK_FP4) {
+    n_t = 6;
+    if (d->hidden % 32 || d->inter % 32)
+      return fail(CACHALOT_EINVAL, "%s: FP4 bank needs hidden and inter to be multiples of 32 (got %d, %d)", who, d->hidden, d->inter);
+  } else if (d->format == CACHALOT_BANK_AFFINE) {
+    n_t = 9;
+    if (d->bits != 2) return fail(CACHALOT_EUNSUPPORTED, "%s: affine bank with bits=%d (only 2-bit is built)", who, d->bits);
+    if (d->group != 64 && d->group != 128) return fail(CACHALOT_EUNSUPPORTED, "%s: affine group %d (64 or 128)", who, d->group);
+    if (d->hidden % 64 || d->inter % 64)
+      return fail(CACHALOT_EINVAL, "%s: 2-bit bank needs hidden and inter to be multiples of 64 (got %d, %d)", who, d->hidden, d->inter);
+    if (((long long)d->hidden * d->inter) % d->group) return fail(CACHALOT_EINVAL, "%s: matrix size is not a whole number of groups", who);
+    if (d->scale_dtype != CACHALOT_F16 && d->scale_dtype != CACHALOT_BF16) return fail(CACHALOT_EINVAL, "%s: scale dtype must be f16 or bf16", who);
+  } else {
+    return fail(CACHALOT_EINVAL, "%s: unknown bank format %d", who, d->format);
+  }
+  if (!aligned(bank, 16) || d->record_bytes % 16) return fail(CACHALOT_EALIGN, "%s: bank base and record_bytes must be multiples of 16", who);
+  for (int i = 0; i < n_t; ++i) {
+    if (d->off[i] < 0 || d->off[i] % 16 || d->off[i] >= d->record_bytes)
+      return fail(CACHALOT_EALIGN, "%s: tensor offset %d (%lld) must be a multiple of 16 inside the record", who, i, (long long)d->off[i]);
+    v->off[i] = d->off[i];
+  }
+  v->base = static_cast<const uint8_t*>(bank);
+  v->record_bytes = d->record_bytes;
+  v->n_slots = d->n_slots;
+  v->hidden = d->hidden;
+  v->inter = d->inter;
+  v->bits = d->bits;
+  v->group = d->group;
+  v->scale_dtype = d->scale_dtype;
+  return CACHALOT_OK;
+}
+
+template <int FMT>
+static int launch_decode(const BankView& v, const void* x, const int32_t* slots, const float* gate_w, int rows, int k,
+                         float limit, int numerics, float* hidden, void* out, int out_dtype, int* status,
+                         cudaStream_t stream, bool mx_hidden = false) {
+  constexpr int CH = Fmt<FMT>::CH;
+  const int H = v.hidden, I = v.inter;
+  size_t smem_gu = (size_t)H * 4 + (FMT == CACHALOT_BANK_AFFINE ? (size_t)(H / CH) * 4 : 0);
+  size_t smem_dn = (size_t)I * 4 + (FMT == CACHALOT_BANK_AFFINE ? (size_t)(I / CH) * 4 : 0);
+  if (smem_gu > 200 * 1024 || smem_dn > 200 * 1024) return fail(CACHALOT_EINVAL, "moe_decode: hidden/inter too large for shared memory");
+  static bool attr_done[2] = {false, false};
+  if (!attr_done[FMT]) {
+    cudaFuncSetAttribute(gate_up_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(down_kernel<FMT, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(down_kernel<FMT, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    attr_done[FMT] = true;
+  }
+  dim3 g1((I + WARPS - 1) / WARPS, rows * k);
+  gate_up_kernel<FMT><<<g1, WARPS * 32, smem_gu, stream>>>(v, (const __nv_bfloat16*)x, slots, gate_w, k, limit, numerics, hidden, status);
+  int rc = check_launch("moe_decode gate_up");
+  if (rc) return rc;
+  if (mx_hidden) {
+    rc = launch_mxfp4_roundtrip_f32(hidden, (long long)rows * k, I, stream);
+    if (rc) return rc;
+  }
+  dim3 g2((H + WARPS - 1) / WARPS, rows);
+  if (out_dtype == CACHALOT_BF16)
+    down_kernel<FMT, __nv_bfloat16><<<g2, WARPS * 32, smem_dn, stream>>>(v, hidden, slots, k, numerics, (__nv_bfloat16*)out);
+  else
+    down_kernel<FMT, float><<<g2, WARPS * 32, smem_dn, stream>>>(v, hidden, slots, k, numerics, (float*)out);
+  return check_launch("moe_decode down");
+}
+
+}  // namespace cachalot
+
+using namespace cachalot;
+
+extern "C" size_t cachalot_moe_decode_workspace_bytes(const cachalot_bank_desc* desc, int rows, int k) {
+  if (!desc || rows <= 0 || k <= 0) return 0;
+  return (size_t)rows * k * desc->inter * sizeof(float);
+}
+
+extern "C" int cachalot_moe_decode(const void* bank, const cachalot_bank_desc* desc, const void* x_bf16,
+                                   const int32_t* slots, const float* gate_w, int rows, int k, float swiglu_limit,
+                                   int numerics, void* workspace, size_t workspace_bytes, void* out, int out_dtype,
+                                   int* status, cachalot_stream_t stream) {
+  BankView v;
+  int rc = make_view(bank, desc, &v, "moe_decode");
+  if (rc) return rc;
+  if (!x_bf16 || !slots || !gate_w || !out) return fail(CACHALOT_EINVAL, "moe_decode: null pointer");
+  if (rows < 0 || k <= 0 || k > 64) return fail(CACHALOT_EINVAL, "moe_decode: rows=%d k=%d out of range", rows, k);
+  if ((long long)rows * k > 65535) return fail(CACHALOT_EINVAL, "moe_decode: rows*k=%lld exceeds 65535", (long long)rows * k);
+  if (numerics != CACHALOT_NUMERICS_F32 && numerics != CACHALOT_NUMERICS_BF16) return fail(CACHALOT_EINVAL, "moe_decode: unknown numerics %d", numerics);
+  if (out_dtype != CACHALOT_F32 && out_dtype != CACHALOT_BF16) return fail(CACHALOT_EINVAL, "moe_decode: out dtype must be f32 or bf16");
+  if (rows == 0) return CACHALOT_OK;
+  size_t need = cachalot_moe_decode_workspace_bytes(desc, rows, k);
+  if (!workspace || workspace_bytes < need) return fail(CACHALOT_ESCRATCH, "moe_decode: workspace %zu < %zu bytes", workspace_bytes, need);
+  if (!aligned(workspace, 16) || !aligned(x_bf16, 2) || !aligned(out, 4)) return fail(CACHALOT_EALIGN, "moe_decode: misaligned buffer");
+  if (desc->format == CACHALOT_BANK_FP4)
+    return launch_decode<CACHALOT_BANK_FP4>(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, numerics, (float*)workspace, out, out_dtype, status, (cudaStream_t)stream);
+  return launch_decode<CACHALOT_BANK_AFFINE>(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, numerics, (float*)workspace, out, out_dtype, status, (cudaStream_t)stream);
+}
+
+// ---- prefill -------------------------------------------------------------------------------
+
+namespace cachalot {
+
+// slots[t*k+j] = slot_of_expert[ids-by-row]; the row's expert id is recovered from the grouping:
+// row perm[p] belongs to expert e for offsets[e] <= p < offsets[e+1]
+__global__ void rows_to_slots_kernel(const int32_t* __restrict__ perm, const int32_t* __restrict__ offsets,
+                                     const int32_t* __restrict__ slot_of_expert, int n_experts,
+                                     int32_t* __restrict__ slots) {
+  const int e = blockIdx.x;
+  const int s = slot_of_expert ? slot_of_expert[e] : e;
+  for (int p = offsets[e] + threadIdx.x; p < offsets[e + 1]; p += blockDim.x) slots[perm[p]] = s;
+}
+
+__global__ void fill_i32_kernel(int32_t* p, int n, int32_t v) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = v;
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace cachalot
+
+extern "C" size_t cachalot_moe_prefill_workspace_bytes(const cachalot_bank_desc* desc, int tokens, int k,
+                                                       int mxfp4_act) {
+  if (!desc || tokens <= 0 || k <= 0) return 0;
+  size_t rows = (size_t)tokens * k;
+  size_t b = align_up(rows * desc->inter * sizeof(float), 256);   // hidden
+  b += align_up(rows * sizeof(int32_t), 256);                     // slot per routed row
+  if (mxfp4_act) b += align_up((size_t)tokens * desc->hidden * 2, 256);  // MXFP4-rounded x as bf16
+  return b;
+}
+
+extern "C" int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc* desc, const void* x_bf16,
+                                    const int32_t* perm, const int32_t* offsets, const int32_t* slot_of_expert,
+                                    const float* gate_w, int tokens, int k, int n_experts, float swiglu_limit,
+                                    int mxfp4_act, void* workspace, size_t workspace_bytes, float* out, int* status,
+                                    cachalot_stream_t stream) {
+  BankView v;
+  int rc = make_view(bank, desc, &v, "moe_prefill");
+  if (rc) return rc;
+  if (!x_bf16 || !perm || !offsets || !gate_w || !out) return fail(CACHALOT_EINVAL, "moe_prefill: null pointer");
+  if (tokens < 0 || k <= 0 || n_experts <= 0) return fail(CACHALOT_EINVAL, "moe_prefill: bad shape");
+  if ((long long)tokens * k > 65535) return fail(CACHALOT_EINVAL, "moe_prefill: tokens*k=%lld exceeds 65535 (chunk the prompt)", (long long)tokens * k);
+  if (tokens == 0) return CACHALOT_OK;
+  size_t need = cachalot_moe_prefill_workspace_bytes(desc, tokens, k, mxfp4_act);
+  if (!workspace || workspace_bytes < need) return fail(CACHALOT_ESCRATCH, "moe_prefill: workspace %zu < %zu bytes", workspace_bytes, need);
+  if (!aligned(workspace, 256)) return fail(CACHALOT_EALIGN, "moe_prefill: workspace must be 256-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t rows = (size_t)tokens * k;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  float* hidden = reinterpret_cast<float*>(ws);
+  ws += align_up(rows * desc->inter * sizeof(float), 256);
+  int32_t* slots = reinterpret_cast<int32_t*>(ws);
+  ws += align_up(rows * sizeof(int32_t), 256);
+  const void* x_in = x_bf16;
+  if (mxfp4_act) {
+    __nv_bfloat16* xq = reinterpret_cast<__nv_bfloat16*>(ws);
+    rc = launch_mxfp4_roundtrip_bf16((const __nv_bfloat16*)x_bf16, xq, tokens, desc->hidden, s);
+    if (rc) return rc;
+    x_in = xq;
+  }
+  // rows whose expert id was dropped by the grouping stay at -1 and contribute zeros
+  fill_i32_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, s>>>(slots, (int)rows, -1);
+  rows_to_slots_kernel<<<n_experts, 128, 0, s>>>(perm, offsets, slot_of_expert, n_experts, slots);
+  rc = check_launch("moe_prefill slots");
+  if (rc) return rc;
+  if (desc->format == CACHALOT_BANK_FP4)
+    return launch_decode<CACHALOT_BANK_FP4>(v, x_in, slots, gate_w, tokens, k, swiglu_limit, CACHALOT_NUMERICS_BF16, hidden, out, CACHALOT_F32, status, s, mxfp4_act != 0);
+  return launch_decode<CACHALOT_BANK_AFFINE>(v, x_in, slots, gate_w, tokens, k, swiglu_limit, CACHALOT_NUMERICS_BF16, hidden, out, CACHALOT_F32, status, s, mxfp4_act != 0);
+}

@@ -1,0 +1,178 @@
+// Prefill helpers: expert-major row grouping (a stable counting sort of the routed expert ids)
+// and MXFP4 activation quantisation.
+#include "kernels.cuh"
+
+namespace cachalot {
+
+__global__ void group_count_kernel(const int32_t* __restrict__ ids, int total, int n_experts,
+                                   int32_t* __restrict__ counts, int* __restrict__ status) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  int e = ids[i];
+  if (e < 0 || e >= n_experts) {
+    if (status) atomicOr(status, CACHALOT_STATUS_ID_RANGE);
+    return;
+  }
+  atomicAdd(&counts[e], 1);
+}
+
+// single CTA: exclusive scan of counts[0..E) into offsets[0..E]
+__global__ void group_scan_kernel(const int32_t* __restrict__ counts, int n_experts, int32_t* __restrict__ offsets) {
+  extern __shared__ int32_t sh[];
+  const int t = threadIdx.x, n = blockDim.x;
+  // each thread owns a contiguous span
+  const int per = (n_experts + n - 1) / n;
+  const int lo = min(t * per, n_experts), hi = min(lo + per, n_experts);
+  int sum = 0;
+  for (int e = lo; e < hi; ++e) sum += counts[e];
+  sh[t] = sum;
+  __syncthreads();
+  if (t == 0) {
+    int run = 0;
+    for (int i = 0; i < n; ++i) {
+      int v = sh[i];
+      sh[i] = run;
+      run += v;
+    }
+    offsets[n_experts] = run;
+  }
+  __syncthreads();
+  int run = sh[t];
+  for (int e = lo; e < hi; ++e) {
+    offsets[e] = run;
+    run += counts[e];
+  }
+}
+
+// one CTA per expert: walk the flattened id list in order and append matches, so rows of an
+// expert keep token-major, slot-minor order (what a stable sort gives)
+__global__ void group_place_kernel(const int32_t* __restrict__ ids, int total, const int32_t* __restrict__ offsets,
+                                   int32_t* __restrict__ perm) {
+  __shared__ int warp_count[32];
+  __shared__ int base;
+  const int e = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (threadIdx.x == 0) base = offsets[e];
+  __syncthreads();
+  if (offsets[e + 1] == offsets[e]) return;
+  for (int start = 0; start < total; start += blockDim.x) {
+    int i = start + threadIdx.x;
+    bool hit = i < total && ids[i] == e;
+    unsigned m = __ballot_sync(0xffffffffu, hit);
+    if (lane == 0) warp_count[warp] = __popc(m);
+    __syncthreads();
+    int before = 0, all = 0;
+    for (int w = 0; w < nwarps; ++w) {
+      int c = warp_count[w];
+      if (w < warp) before += c;
+      all += c;
+    }
+    if (hit) perm[base + before + __popc(m & ((1u << lane) - 1u))] = i;
+    __syncthreads();
+    if (threadIdx.x == 0) base += all;
+    __syncthreads();
+  }
+}
+
+// E2M1 nearest with ties to even, as a threshold chain (the reference's explicit table)
+__device__ __forceinline__ uint32_t e2m1_round_code(float v) {
+  float a = fabsf(v);
+  uint32_t mag = a <= 0.25f ? 0u : a < 0.75f ? 1u : a <= 1.25f ? 2u : a < 1.75f ? 3u : a <= 2.5f ? 4u : a < 3.5f ? 5u : a <= 5.0f ? 6u : 7u;
+  return mag | ((__float_as_uint(v) >> 28) & 8u);
+}
+
+// block scale of MXFP4: 2**ceil(log2(max(amax, 6*2**-126) / 6)); returns the exponent
+__device__ __forceinline__ int mxfp4_exponent(float amax) {
+  amax = fmaxf(amax, 6.0f * 1.1754943508222875e-38f);
+  float raw = __fdiv_rn(amax, 6.0f);
+  uint32_t b = __float_as_uint(raw);
+  int e = (int)((b >> 23) & 0xffu);
+  if (e == 0) return -126;  // denormal quotient can only be just below 2**-126
+  return e - 127 + ((b & 0x7fffffu) ? 1 : 0);
+}
+
+__device__ __forceinline__ float pow2f(int e) {  // e in [-127, 127]
+  return e >= -126 ? __uint_as_float((uint32_t)(e + 127) << 23) : __uint_as_float(0x00400000u);
+}
+
+// one warp per (row, 32-block), one lane per element
+__global__ void mxfp4_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ src_rows,
+                                   long long rows, int k, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales) {
+  const int nblk = k / 32;
+  long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= rows * nblk) return;
+  long long r = warp / nblk;
+  int b = (int)(warp - r * nblk);
+  long long src = src_rows ? src_rows[r] : r;
+  float v = __bfloat162float(x[src * k + b * 32 + lane]);
+  int e = mxfp4_exponent(warp_max(fabsf(v)));
+  float q = fminf(fmaxf(__fdiv_rn(v, pow2f(e)), -6.0f), 6.0f);
+  uint32_t code = e2m1_round_code(q);
+  uint32_t hi = __shfl_down_sync(0xffffffffu, code, 1);
+  if ((lane & 1) == 0) codes[r * (k / 2) + b * 16 + (lane >> 1)] = (uint8_t)(code | (hi << 4));
+  if (lane == 0) scales[r * nblk + b] = (uint8_t)(e + 127);
+}
+
+template <typename T>
+__global__ void mxfp4_roundtrip_kernel(const T* __restrict__ in, T* __restrict__ out, long long n_blocks) {
+  long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= n_blocks) return;
+  float v;
+  if constexpr (sizeof(T) == 2) v = __bfloat162float(in[warp * 32 + lane]); else v = in[warp * 32 + lane];
+  int e = mxfp4_exponent(warp_max(fabsf(v)));
+  float s = pow2f(e);
+  float q = fminf(fmaxf(__fdiv_rn(v, s), -6.0f), 6.0f);
+  uint32_t code = e2m1_round_code(q);
+  float y = e2m1_to_f32(code) * s;
+  if (code == 8u || ((code & 7u) == 0u && (code & 8u))) y = -0.0f * s;  // signed zero kept
+  if constexpr (sizeof(T) == 2) out[warp * 32 + lane] = __float2bfloat16_rn(y); else out[warp * 32 + lane] = y;
+}
+
+int launch_mxfp4_roundtrip_f32(float* data, long long rows, int k, cudaStream_t stream) {
+  long long n_blocks = rows * (k / 32);
+  if (n_blocks == 0) return CACHALOT_OK;
+  unsigned blocks = (unsigned)((n_blocks * 32 + 255) / 256);
+  mxfp4_roundtrip_kernel<float><<<blocks, 256, 0, stream>>>(data, data, n_blocks);
+  return check_launch("mxfp4_roundtrip_f32");
+}
+int launch_mxfp4_roundtrip_bf16(const __nv_bfloat16* in, __nv_bfloat16* out, long long rows, int k, cudaStream_t stream) {
+  long long n_blocks = rows * (k / 32);
+  if (n_blocks == 0) return CACHALOT_OK;
+  unsigned blocks = (unsigned)((n_blocks * 32 + 255) / 256);
+  mxfp4_roundtrip_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(in, out, n_blocks);
+  return check_launch("mxfp4_roundtrip_bf16");
+}
+
+}  // namespace cachalot
+
+using namespace cachalot;
+
+extern "C" int cachalot_group_rows(const int32_t* expert_ids, int tokens, int k, int n_experts, int32_t* perm,
+                                   int32_t* offsets, int32_t* counts_scratch, int* status,
+                                   cachalot_stream_t stream) {
+  if (!expert_ids || !perm || !offsets || !counts_scratch) return fail(CACHALOT_EINVAL, "group_rows: null pointer");
+  if (tokens < 0 || k <= 0 || n_experts <= 0) return fail(CACHALOT_EINVAL, "group_rows: bad shape");
+  long long total_ll = (long long)tokens * k;
+  if (total_ll > 0x7fffffff) return fail(CACHALOT_EINVAL, "group_rows: tokens*k too large");
+  int total = (int)total_ll;
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t e = cudaMemsetAsync(counts_scratch, 0, (size_t)(n_experts + 1) * sizeof(int32_t), s);
+  if (e != cudaSuccess) return fail(CACHALOT_ECUDA, "group_rows: memset: %s", cudaGetErrorString(e));
+  if (total > 0) group_count_kernel<<<(total + 255) / 256, 256, 0, s>>>(expert_ids, total, n_experts, counts_scratch, status);
+  group_scan_kernel<<<1, 256, 256 * sizeof(int32_t), s>>>(counts_scratch, n_experts, offsets);
+  if (total > 0) group_place_kernel<<<n_experts, 256, 0, s>>>(expert_ids, total, offsets, perm);
+  return check_launch("group_rows");
+}
+
+extern "C" int cachalot_mxfp4_act_quant(const void* x_bf16, const int32_t* src_rows, int rows, int k, uint8_t* codes,
+                                        uint8_t* scales, cachalot_stream_t stream) {
+  if (!x_bf16 || !codes || !scales) return fail(CACHALOT_EINVAL, "mxfp4_act_quant: null pointer");
+  if (rows < 0 || k <= 0 || k % 32) return fail(CACHALOT_EINVAL, "last dimension %d must be divisible by block_size=32", k);
+  if (rows == 0) return CACHALOT_OK;
+  long long warps = (long long)rows * (k / 32);
+  unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+  mxfp4_quant_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x_bf16, src_rows, rows, k, codes, scales);
+  return check_launch("mxfp4_act_quant");
+}

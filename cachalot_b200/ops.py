@@ -1,0 +1,371 @@
+"""Host-side operators with the reference's names and argument meaning, on CUDA tensors.
+
+Every function here calls the C ABI (libcachalot_b200.so); none has a PyTorch or CPU fallback.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+from .bank import FP4_FORMAT, ExpertFormat, ResidentExpert, SlabBank
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("cachalot_b200 operators take CUDA tensors (there is no CPU path)")
+
+
+# ---- dequantisation ---------------------------------------------------------------------------
+
+def dequantize_fp4_weight(packed: torch.Tensor, scales: torch.Tensor, block_size: int = 32) -> torch.Tensor:
+    """packed uint8 [N, K/2], scales uint8 [N, K/32] -> float32 [N, K] (model/fp4.py:67-109)."""
+    _need_cuda(packed, scales)
+    if block_size != 32:
+        raise NotImplementedError("FP4 banks use per-32 scales")
+    if packed.dim() != 2 or packed.dtype != torch.uint8 or scales.dtype != torch.uint8:
+        raise ValueError(f"packed/scales must be 2-D uint8, got {packed.dtype} {tuple(packed.shape)}")
+    n, k = packed.shape[0], packed.shape[1] * 2
+    if k % block_size:
+        raise ValueError(f"K={k} must be divisible by block_size={block_size}")
+    if tuple(scales.shape) != (n, k // block_size):
+        raise ValueError(f"Scale shape {tuple(scales.shape)} does not match expected {(n, k // block_size)}")
+    packed, scales = packed.contiguous(), scales.contiguous()
+    out = torch.empty((n, k), dtype=torch.float32, device=packed.device)
+    check(lib.cachalot_fp4_dequant(_ptr(packed), _ptr(scales), n, k, _ptr(out), _stream()))
+    return out
+
+
+def dequantize_affine(words: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, *, bits: int, group_size: int) -> torch.Tensor:
+    """words int32/uint32 [N, K*bits/32]; scales/biases f16 or bf16 -> float32 [N, K] = scale*q + bias."""
+    _need_cuda(words, scales, biases)
+    n = words.shape[0]
+    k = words.shape[1] * 32 // bits
+    if scales.dtype not in (torch.float16, torch.bfloat16) or biases.dtype != scales.dtype:
+        raise ValueError("scales and biases must both be float16 or both bfloat16")
+    if scales.numel() != n * k // group_size:
+        raise ValueError(f"{scales.numel()} scales for {n}x{k} at group {group_size}")
+    out = torch.empty((n, k), dtype=torch.float32, device=words.device)
+    sdt = _lib.BF16 if scales.dtype == torch.bfloat16 else _lib.F16
+    check(lib.cachalot_affine_dequant(_ptr(words.contiguous()), _ptr(scales.contiguous()), _ptr(biases.contiguous()),
+                                      n, k, bits, group_size, sdt, _ptr(out), _stream()))
+    return out
+
+
+# ---- routing ----------------------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class RouterResult:
+    """Same fields as the reference's RouterResult (model/router_mlx.py:9-13)."""
+
+    indices: torch.Tensor
+    weights: torch.Tensor
+    scores: torch.Tensor
+
+
+def router_logits(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """fp32 gate logits [rows, E] of bf16 rows x [rows, H] against weight [E, H] (bf16 or f32)."""
+    _need_cuda(x, weight)
+    x2 = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
+    e, h = weight.shape
+    if x2.shape[1] != h:
+        raise ValueError(f"x has {x2.shape[1]} elements, gate expects {h}")
+    if weight.dtype == torch.bfloat16:
+        wdt = _lib.BF16
+    elif weight.dtype == torch.float32:
+        wdt = _lib.F32
+    else:
+        raise ValueError(f"gate weight must be bfloat16 or float32, got {weight.dtype}")
+    out = torch.empty((x2.shape[0], e), dtype=torch.float32, device=x.device)
+    check(lib.cachalot_router_logits(_ptr(x2), _ptr(weight.contiguous()), wdt, x2.shape[0], e, h, _ptr(out), _stream()))
+    return out
+
+
+def _route(logits, bias, table, layer, k, mode, gate_temp, route_scale, norm, weights_bf16, want_scores):
+    rows, e = logits.shape
+    dev = logits.device
+    idx = torch.empty((rows, k), dtype=torch.int32, device=dev)
+    w = torch.empty((rows, k), dtype=torch.float32, device=dev)
+    slots = torch.empty((rows, k), dtype=torch.int32, device=dev)
+    scores = torch.empty((rows, e), dtype=torch.float32, device=dev) if want_scores else None
+    b = None if bias is None else bias.to(torch.float32).contiguous()
+    check(lib.cachalot_route_topk(_ptr(logits), _ptr(b), _ptr(table), layer, rows, e, k, mode, float(gate_temp),
+                                  float(route_scale), int(norm), int(weights_bf16), _ptr(idx), _ptr(w), _ptr(slots),
+                                  _ptr(scores), _stream()))
+    return idx, w, slots, scores
+
+
+def route_topk_fused(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, *, topk: int = 6, gate_temp: float = 1.0,
+                     route_scale: float = 1.5, norm_topk_prob: bool = True) -> RouterResult:
+    """DeepSeek router for one decode token (model/router_fused_metal.py:111-148): indices int32 [k]
+    ascending by selection score, weights float32 [k], scores float32 [E]."""
+    if x.dim() != 1:
+        raise ValueError(f"x must be 1D, got {tuple(x.shape)}")
+    if weight.dim() != 2:
+        raise ValueError(f"weight must be 2D, got {tuple(weight.shape)}")
+    if tuple(bias.shape) != (weight.shape[0],):
+        raise ValueError(f"bias shape {tuple(bias.shape)} != ({weight.shape[0]},)")
+    if not 1 <= topk <= weight.shape[0]:
+        raise ValueError(f"Invalid topk={topk} for {weight.shape[0]} experts")
+    logits = router_logits(x, weight)
+    idx, w, _, scores = _route(logits, bias, None, 0, topk, _lib.ROUTER_SQRT_SOFTPLUS, gate_temp, route_scale,
+                               norm_topk_prob, False, True)
+    return RouterResult(indices=idx[0], weights=w[0], scores=scores[0])
+
+
+route_topk = route_topk_fused
+
+
+def route_topk_rows(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, *, topk: int = 6, gate_temp: float = 1.0,
+                    route_scale: float = 1.5, norm_topk_prob: bool = True) -> RouterResult:
+    """Row-wise router for a prompt chunk (model/moe_prefill_batched.py:128-178): [T,k] outputs."""
+    if x.dim() != 2:
+        raise ValueError(f"x must be 2D, got {tuple(x.shape)}")
+    logits = router_logits(x, weight)
+    idx, w, _, scores = _route(logits, bias, None, 0, topk, _lib.ROUTER_SQRT_SOFTPLUS, gate_temp, route_scale,
+                               norm_topk_prob, False, True)
+    return RouterResult(indices=idx, weights=w, scores=scores)
+
+
+def route_tail(raw: torch.Tensor, bias: torch.Tensor | None, table: torch.Tensor | None, layer: int, k: int, scale: float,
+               *, weights_bf16: bool = True):
+    """Sigmoid routing tail with slot lookup (minimax/gpu_select.py:119-132).  raw float32 [..., E]
+    (rows = leading dims); returns (inds int32 [rows,k], weights float32 [rows,k] rounded to bf16
+    precision by default, slots int32 [rows,k]); no host round trip."""
+    _need_cuda(raw)
+    logits = raw.reshape(-1, raw.shape[-1]).to(torch.float32).contiguous()
+    idx, w, slots, _ = _route(logits, bias, table, layer, k, _lib.ROUTER_SIGMOID, 1.0, scale, True, weights_bf16, False)
+    return idx, w, slots
+
+
+# ---- decode: routed experts -------------------------------------------------------------------
+
+_workspaces: dict = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    key = (device, torch.cuda.current_stream().cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def moe_forward(x: torch.Tensor, slot_ids: torch.Tensor, gate_weights: torch.Tensor, bank: SlabBank, *,
+                swiglu_limit: float = 10.0, numerics: str | None = None, out_dtype=torch.float32,
+                out: torch.Tensor | None = None, status: torch.Tensor | None = None,
+                workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """Routed experts for `rows` tokens: x bf16 [rows,H], slot_ids int32 [rows,k] (bank slots, -1 =
+    absent -> zero contribution), gate_weights float32 [rows,k] -> [rows,H].
+
+    numerics "f32" keeps fp32 between the projections (the FP4 decode op,
+    model/moe_fused_metal.py:189-233); "bf16" rounds g, u, h and each expert's output to bf16 (the
+    affine op, model/expert_affine.py:65-81).  Default: by bank format."""
+    _need_cuda(x, slot_ids, gate_weights)
+    if x.dim() != 2 or x.shape[1] != bank.hidden:
+        raise ValueError(f"x must be [rows, {bank.hidden}], got {tuple(x.shape)}")
+    rows = x.shape[0]
+    if slot_ids.dim() != 2 or slot_ids.shape[0] != rows or tuple(gate_weights.shape) != tuple(slot_ids.shape):
+        raise ValueError(f"slot_ids {tuple(slot_ids.shape)} / gate_weights {tuple(gate_weights.shape)} do not match rows={rows}")
+    k = slot_ids.shape[1]
+    if numerics is None:
+        numerics = "f32" if bank.fmt.kind == "fp4" else "bf16"
+    num = {"f32": _lib.NUMERICS_F32, "bf16": _lib.NUMERICS_BF16}[numerics]
+    xb = x.to(torch.bfloat16).contiguous()
+    slot_ids = slot_ids.to(torch.int32).contiguous()
+    gate_weights = gate_weights.to(torch.float32).contiguous()
+    odt = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}[out_dtype]
+    if out is None:
+        out = torch.empty((rows, bank.hidden), dtype=out_dtype, device=x.device)
+    need = lib.cachalot_moe_decode_workspace_bytes(bank.desc_ptr, rows, k)
+    ws = workspace if workspace is not None else _workspace(x.device, need)
+    check(lib.cachalot_moe_decode(_ptr(bank.slab), bank.desc_ptr, _ptr(xb), _ptr(slot_ids), _ptr(gate_weights), rows, k,
+                                  float(swiglu_limit), num, _ptr(ws), ws.numel(), _ptr(out), odt, _ptr(status), _stream()))
+    return out
+
+
+def _slots_of(experts) -> tuple[SlabBank, torch.Tensor]:
+    if len(experts) == 0:
+        raise ValueError("no experts given")
+    bank = experts[0].bank
+    for e in experts:
+        if not isinstance(e, ResidentExpert) or e.bank is not bank:
+            raise ValueError("experts must be ResidentExpert objects of one bank")
+    return bank, torch.tensor([[e.slot for e in experts]], dtype=torch.int32, device=bank.slab.device)
+
+
+def fused_routed_experts(x: torch.Tensor, experts, router_weights: torch.Tensor, *, hidden_size: int = 5120,
+                         intermediate: int = 2304, swiglu_limit: float = 10.0) -> torch.Tensor:
+    """Top-k routed experts of one decode token over an FP4 bank (model/moe_fused_metal.py:189-233):
+    x [hidden_size] any float dtype, experts = ResidentExpert objects, router_weights float32 [k]
+    -> float32 [hidden_size]."""
+    bank, slots = _slots_of(experts)
+    if bank.fmt.kind != "fp4":
+        raise ValueError("fused_routed_experts needs an FP4 bank; use affine_routed_experts")
+    if (bank.hidden, bank.inter) != (hidden_size, intermediate):
+        raise ValueError(f"bank is {bank.hidden}x{bank.inter}, call says {hidden_size}x{intermediate}")
+    if x.dim() != 1 or x.numel() != hidden_size:
+        raise ValueError(f"x must be 1-D with {hidden_size} elements, got {tuple(x.shape)}")
+    if router_weights.numel() != len(experts):
+        raise ValueError(f"{len(experts)=} does not match {router_weights.numel()=}")
+    return moe_forward(x[None], slots, router_weights.reshape(1, -1), bank, swiglu_limit=swiglu_limit, numerics="f32")[0]
+
+
+def affine_routed_experts(x: torch.Tensor, experts, fmt: ExpertFormat, weights: torch.Tensor,
+                          swiglu_limit: float = 10.0) -> torch.Tensor:
+    """Sum of the routed experts of one decode token over an affine bank
+    (model/expert_affine.py:186-206) -> float32 [hidden]."""
+    bank, slots = _slots_of(experts)
+    if bank.fmt.kind != "affine" or (fmt.bits, fmt.group_size) != (bank.fmt.bits, bank.fmt.group_size):
+        raise ValueError("format does not match the experts' bank")
+    if x.dim() != 1:
+        raise ValueError(f"x must be 1-D, got {tuple(x.shape)}")
+    return moe_forward(x[None], slots, weights.reshape(1, -1), bank, swiglu_limit=swiglu_limit, numerics="bf16")[0]
+
+
+def routed_expert_forward(x: torch.Tensor, *, w1_packed, w1_scales, w2_packed, w2_scales, w3_packed, w3_scales,
+                          weight=None, swiglu_limit: float = 10.0) -> torch.Tensor:
+    """One FP4 expert on loose tensors (model/expert_metal.py:9-64).  The tensors are copied into a
+    one-slot bank first; the slot path (fused_routed_experts / moe_forward) is the fast one."""
+    inter, hidden = w1_packed.reshape(w1_scales.shape[0], -1).shape[0], w1_packed.numel() * 2 // w1_scales.shape[0]
+    bank = SlabBank(FP4_FORMAT, hidden, inter, 1, device=x.device)
+    bank.write_expert(0, {"w1.weight": w1_packed, "w1.scale": w1_scales, "w2.weight": w2_packed, "w2.scale": w2_scales,
+                          "w3.weight": w3_packed, "w3.scale": w3_scales})
+    w = torch.ones(1, 1, dtype=torch.float32, device=x.device) if weight is None else \
+        torch.as_tensor(weight, dtype=torch.float32, device=x.device).reshape(1, 1)
+    slots = torch.zeros((1, 1), dtype=torch.int32, device=x.device)
+    return moe_forward(x.reshape(1, -1), slots, w, bank, swiglu_limit=swiglu_limit, numerics="f32")[0]
+
+
+# ---- FP8 trunk GEMV ---------------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class QuantizedActivation:
+    """Same fields as the reference's (model/fp8_linear_metal.py:22-27); `decoded` is unused here
+    because the GEMV decodes E4M3 in registers."""
+
+    values: torch.Tensor
+    scales: torch.Tensor
+    in_features: int
+    decoded: torch.Tensor | None = None
+    block_size: int = 32
+    scale_rule: str = "e8m0"
+
+
+_RULE = {"e8m0": _lib.SCALE_E8M0, "f32": _lib.SCALE_F32}
+
+
+def quantize_fp8_activation(x: torch.Tensor, block_size: int = 32, scale_rule: str = "e8m0") -> QuantizedActivation:
+    """act_quant (model/fp8_ref.py:27-92).  The reference takes one token (1-D); [rows, K] is the
+    same per row."""
+    _need_cuda(x)
+    if x.dim() not in (1, 2):
+        raise ValueError(f"Decode FP8 activation must be 1D, got {tuple(x.shape)}")
+    k = x.shape[-1]
+    if k % block_size:
+        raise ValueError(f"K={k} must be divisible by block_size={block_size}")
+    x2 = x.reshape(-1, k).to(torch.bfloat16).contiguous()
+    codes = torch.empty(x2.shape, dtype=torch.uint8, device=x.device)
+    scales = torch.empty((x2.shape[0], k // block_size), dtype=torch.float32, device=x.device)
+    check(lib.cachalot_fp8_act_quant(_ptr(x2), x2.shape[0], k, block_size, _RULE[scale_rule], _ptr(codes), _ptr(scales), _stream()))
+    if x.dim() == 1:
+        codes, scales = codes[0], scales[0]
+    return QuantizedActivation(codes, scales, k, None, block_size, scale_rule)
+
+
+def fp8_linear_quantized(x: QuantizedActivation, weight: torch.Tensor, weight_scales: torch.Tensor, *,
+                         out_dtype=torch.bfloat16) -> torch.Tensor:
+    """FP8 GEMV on a quantised activation (model/fp8_linear_metal.py:56-89) -> bf16 [N] / [rows,N]."""
+    if weight.dim() != 2:
+        raise ValueError(f"weight must be 2D, got {tuple(weight.shape)}")
+    n, k = weight.shape
+    if k != x.in_features:
+        raise ValueError(f"weight expects {k} inputs, quantized activation has {x.in_features}")
+    rule = "e8m0" if weight_scales.dtype == torch.uint8 else "f32"
+    if rule != x.scale_rule:
+        raise ValueError(f"activation was quantised with {x.scale_rule!r} scales, weight scales are {rule!r}")
+    expected = (-(-n // x.block_size), k // x.block_size)
+    if tuple(weight_scales.shape) != expected:
+        raise ValueError(f"scale shape {tuple(weight_scales.shape)} != {expected}")
+    codes = x.values.reshape(-1, k)
+    out = torch.empty((codes.shape[0], n), dtype=out_dtype, device=weight.device)
+    odt = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}[out_dtype]
+    check(lib.cachalot_fp8_gemv(_ptr(codes.contiguous()), _ptr(x.scales.contiguous()), _ptr(weight.contiguous()),
+                                _ptr(weight_scales.contiguous()), _RULE[rule], x.block_size, codes.shape[0], n, k,
+                                _ptr(out), odt, _stream()))
+    return out[0] if x.values.dim() == 1 else out
+
+
+def fp8_linear(x: torch.Tensor, weight: torch.Tensor, weight_scales: torch.Tensor, *, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """act_quant + GEMV (model/fp8_linear_metal.py:92-107).  uint8 weight scales select the
+    reference's E8M0 / block-32 form, float32 scales the fp32 / block-(K / scale columns) form."""
+    if weight_scales.dtype == torch.uint8:
+        block, rule = 32, "e8m0"
+    else:
+        block, rule = weight.shape[1] // weight_scales.shape[1], "f32"
+    return fp8_linear_quantized(quantize_fp8_activation(x, block, rule), weight, weight_scales, out_dtype=out_dtype)
+
+
+# ---- prefill ----------------------------------------------------------------------------------
+
+def group_rows(expert_ids: torch.Tensor, n_experts: int, status: torch.Tensor | None = None):
+    """Expert-major grouping of routed rows (model/moe_prefill_grouped.py:201-225): expert_ids int32
+    [T,k] -> (perm int32 [T*k], offsets int32 [E+1])."""
+    _need_cuda(expert_ids)
+    t, k = expert_ids.shape
+    ids = expert_ids.to(torch.int32).contiguous()
+    perm = torch.empty(t * k, dtype=torch.int32, device=ids.device)
+    offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=ids.device)
+    scratch = torch.empty(n_experts + 1, dtype=torch.int32, device=ids.device)
+    check(lib.cachalot_group_rows(_ptr(ids), t, k, n_experts, _ptr(perm), _ptr(offsets), _ptr(scratch), _ptr(status), _stream()))
+    return perm, offsets
+
+
+def quantize_mxfp4(x: torch.Tensor, src_rows: torch.Tensor | None = None):
+    """MXFP4 activation quantisation (model/fp4_act_mlx.py:101-250, block 32 / E8M0): x bf16 [rows,K]
+    -> (codes uint8 [rows,K/2] low nibble first, scale bytes uint8 [rows,K/32])."""
+    _need_cuda(x)
+    k = x.shape[-1]
+    if k % 32:
+        raise ValueError(f"last dimension {k} must be divisible by block_size=32")
+    x2 = x.reshape(-1, k).to(torch.bfloat16).contiguous()
+    rows = x2.shape[0] if src_rows is None else src_rows.numel()
+    codes = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((rows, k // 32), dtype=torch.uint8, device=x.device)
+    src = None if src_rows is None else src_rows.to(torch.int32).contiguous()
+    check(lib.cachalot_mxfp4_act_quant(_ptr(x2), _ptr(src), rows, k, _ptr(codes), _ptr(scales), _stream()))
+    return codes, scales
+
+
+def moe_prefill_grouped(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, bank: SlabBank, *,
+                        layer: int = 0, swiglu_limit: float = 10.0, mxfp4_act: bool = False,
+                        status: torch.Tensor | None = None) -> torch.Tensor:
+    """Expert-major routed experts for a prompt chunk (model/moe_prefill_grouped.py:74-635, routed
+    part): x bf16 [T,H], expert_ids int32 [T,k], weights float32 [T,k] -> float32 [T,H] = per-slot
+    results summed in slot order.  mxfp4_act quantises x and the hidden activation per 32 first."""
+    _need_cuda(x, expert_ids, weights)
+    t, k = expert_ids.shape
+    e = bank.n_experts
+    perm, offsets = group_rows(expert_ids, e, status)
+    slot_of_expert = bank.slot_table[layer].contiguous()
+    xb = x.to(torch.bfloat16).contiguous()
+    out = torch.empty((t, bank.hidden), dtype=torch.float32, device=x.device)
+    need = lib.cachalot_moe_prefill_workspace_bytes(bank.desc_ptr, t, k, int(mxfp4_act))
+    ws = _workspace(x.device, need + 256)
+    base = (ws.data_ptr() + 255) // 256 * 256
+    check(lib.cachalot_moe_prefill(_ptr(bank.slab), bank.desc_ptr, _ptr(xb), _ptr(perm), _ptr(offsets), _ptr(slot_of_expert),
+                                   _ptr(weights.to(torch.float32).contiguous()), t, k, e, float(swiglu_limit), int(mxfp4_act),
+                                   base, ws.numel() - (base - ws.data_ptr()), _ptr(out), _ptr(status), _stream()))
+    return out

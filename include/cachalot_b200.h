@@ -1,0 +1,193 @@
+/*
+ * cachalot_b200 -- C ABI of the B200 (sm_100a) routed-expert MoE / FP8 trunk GEMV kernels.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, launches on the stream
+ * the caller passes (never synchronises, never allocates) and returns 0 on success or a
+ * negative CACHALOT_E* code; cachalot_last_error() gives the message for the calling thread.
+ * Pointers are DEVICE pointers unless the comment says "host".  Conditions only the device
+ * can see (a slot id outside the bank) set bits in the caller's `status` word and the kernel
+ * still returns normally: no trap, no hang.
+ *
+ * Each declaration names the interface of the reference (prooshani/cachalot, paths relative
+ * to its repository root) that it replaces.
+ */
+#ifndef CACHALOT_B200_H
+#define CACHALOT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define CACHALOT_API __attribute__((visibility("default")))
+#else
+#define CACHALOT_API
+#endif
+
+typedef struct CUstream_st* cachalot_stream_t; /* a cudaStream_t */
+
+enum {
+  CACHALOT_OK = 0,
+  CACHALOT_EINVAL = -1,       /* bad shape / null pointer / size not supported */
+  CACHALOT_EALIGN = -2,       /* pointer or offset not aligned as required */
+  CACHALOT_EUNSUPPORTED = -3, /* legal in the reference but not built here */
+  CACHALOT_ECUDA = -4,        /* a CUDA call failed; see cachalot_last_error() */
+  CACHALOT_ESCRATCH = -5      /* workspace too small */
+};
+
+/* bits of the device-side status word */
+enum {
+  CACHALOT_STATUS_SLOT_RANGE = 1, /* a slot id >= n_slots was seen and treated as absent */
+  CACHALOT_STATUS_ID_RANGE = 2    /* an expert id outside [0, E) was seen and dropped */
+};
+
+enum { CACHALOT_BANK_FP4 = 0, CACHALOT_BANK_AFFINE = 1 };
+enum { CACHALOT_F16 = 0, CACHALOT_BF16 = 1, CACHALOT_F32 = 2 };
+/* rounding points of the expert FFN */
+enum {
+  CACHALOT_NUMERICS_F32 = 0, /* decode FP4 op: fp32 everywhere (model/moe_fused_metal.py:101-179) */
+  CACHALOT_NUMERICS_BF16 = 1 /* affine and prefill ops: g,u -> bf16; h -> bf16; each expert's W2 h -> bf16
+                                (model/expert_affine.py:74-81, model/fp4_sgmm_metal.py:203-233) */
+};
+enum { CACHALOT_ROUTER_SQRT_SOFTPLUS = 0, CACHALOT_ROUTER_SIGMOID = 1 };
+enum { CACHALOT_SCALE_E8M0 = 0, CACHALOT_SCALE_F32 = 1 };
+
+/*
+ * An expert bank: n_slots records of record_bytes each in one device allocation; tensor i of a
+ * record starts at byte off[i] (multiple of 16).  This is the device-side form of the
+ * reference's slab slot pool (cache/slots.py:185-251: rows of a [slots, record_bytes] uint8
+ * array with fixed per-tensor offsets) and of its per-expert accessors (cache/resident.py:11-52).
+ *   FP4 bank    off[0..5] = w1.weight, w1.scale, w2.weight, w2.scale, w3.weight, w3.scale
+ *               (names and order of cache/slots.py:30-37); weight = E2M1 nibbles [N, K/2], low
+ *               nibble first; scale = E8M0 bytes [N, K/32] (model/fp4.py:44-109).
+ *   affine bank off[0..8] = w1.weight, w1.scales, w1.biases, w2.*, w3.*; weight = u32 words
+ *               [N, K*bits/32] (little-endian bit stream, benchmarks/quant_affine.py:69-105),
+ *               scales / biases [N, K/group] in scale_dtype (model/expert_affine.py:26-51).
+ * w1 (gate) and w3 (up) are [inter, hidden]; w2 (down) is [hidden, inter].
+ */
+typedef struct {
+  int64_t record_bytes;
+  int64_t off[9];
+  int32_t n_slots;
+  int32_t hidden;
+  int32_t inter;
+  int32_t format;      /* CACHALOT_BANK_* */
+  int32_t bits;        /* affine: 2 (built); FP4: 4 */
+  int32_t group;       /* affine: 128 or 64; FP4: 32 */
+  int32_t scale_dtype; /* affine: CACHALOT_F16 or CACHALOT_BF16 */
+  int32_t reserved;
+} cachalot_bank_desc;
+
+CACHALOT_API const char* cachalot_last_error(void);
+CACHALOT_API int cachalot_version(void);
+
+/* ---- dequantisation (bit-exact against the reference's numpy path) ------------------------ */
+
+/* Replaces model/fp4.py:67-109 dequantize_fp4_weight and the Metal twins
+ * model/fp4_dequant_metal.py:11-65: packed u8 [N,K/2] + scales u8 [N,K/32] -> f32 [N,K]. */
+CACHALOT_API int cachalot_fp4_dequant(const uint8_t* packed, const uint8_t* scales, int n, int k, float* out,
+                         cachalot_stream_t stream);
+
+/* Replaces mx.dequantize as the reference uses it for affine banks (benchmarks/quant_affine.py:
+ * 119-123, 366-367): out = f32(scale)*q + f32(bias), one rounding.  bits in {2,4,8}. */
+CACHALOT_API int cachalot_affine_dequant(const uint32_t* words, const void* scales, const void* biases, int n, int k,
+                            int bits, int group, int scale_dtype, float* out, cachalot_stream_t stream);
+
+/* ---- routing ------------------------------------------------------------------------------ */
+
+/* Replaces the score half of model/router_fused_metal.py:33-58 (router_scores): for each of
+ * `rows` tokens, logits[e] = dot(x, gate_w[e]) in fp32; x is bf16 [rows,H]; gate_w is
+ * [E,H] in w_dtype (CACHALOT_BF16 or CACHALOT_F32).  The non-linearity is applied by
+ * cachalot_route_topk so that both routers share this kernel. */
+CACHALOT_API int cachalot_router_logits(const void* x_bf16, const void* gate_w, int w_dtype, int rows, int n_experts,
+                           int hidden, float* logits, cachalot_stream_t stream);
+
+/* Replaces model/router_fused_metal.py:62-108 + router_mlx.py:16-118 (mode SQRT_SOFTPLUS:
+ * score = sqrt(softplus(logit/gate_temp)); top-k of score+bias, written ascending, ties to the
+ * larger index; weights = score/(sum+1e-20)*route_scale), model/moe_prefill_batched.py:128-178
+ * (the same per row) and minimax/gpu_select.py:80-132 route_tail (mode SIGMOID: strongest first,
+ * ties to the lower index, slot table lookup).  logits f32 [rows,E]; bias f32 [E] or NULL;
+ * slot_table i32 [layers,E] or NULL (then slots = expert ids); outputs indices i32 [rows,k],
+ * weights f32 [rows,k] (rounded to bf16 precision when weights_bf16 != 0, as route_tail does),
+ * slots i32 [rows,k] (may be NULL), scores f32 [rows,E] (may be NULL). E <= 1024, k <= 32. */
+CACHALOT_API int cachalot_route_topk(const float* logits, const float* bias, const int32_t* slot_table, int layer, int rows,
+                        int n_experts, int k, int mode, float gate_temp, float route_scale, int norm_topk_prob,
+                        int weights_bf16, int32_t* indices, float* weights, int32_t* slots, float* scores,
+                        cachalot_stream_t stream);
+
+/* ---- decode: routed experts over bank slots ----------------------------------------------- */
+
+/* Bytes of workspace cachalot_moe_decode needs for `rows` tokens and top-k `k`. */
+CACHALOT_API size_t cachalot_moe_decode_workspace_bytes(const cachalot_bank_desc* desc /* host */, int rows, int k);
+
+/* Replaces model/moe_fused_metal.py:189-233 fused_routed_experts (FP4 bank),
+ * model/expert_affine.py:186-206 affine_routed_experts (affine bank) and the slot-indexed slab
+ * op minimax/gpu_select.py:279-327 SlabExperts: for each of `rows` tokens,
+ *   out[t] = sum_{j<k} W2_s( silu(min(W1_s x, L)) * clip(W3_s x, +-L) * gate_w[t,j] ),  s = slots[t,j]
+ * with the router weight applied before the down projection (model/expert_metal.py:54-56), the
+ * clamp skipped when swiglu_limit <= 0, and a slot < 0 contributing zeros
+ * (minimax/gpu_select.py:265-273).  x bf16 [rows,H]; slots i32 [rows,k]; gate_w f32 [rows,k];
+ * out f32 [rows,H] (or bf16 when out_dtype == CACHALOT_BF16).  The reference runs one token at a
+ * time (model/moe_layer_metal.py:168-171); rows > 1 is the same math per row. */
+CACHALOT_API int cachalot_moe_decode(const void* bank, const cachalot_bank_desc* desc /* host */, const void* x_bf16,
+                        const int32_t* slots, const float* gate_w, int rows, int k, float swiglu_limit,
+                        int numerics, void* workspace, size_t workspace_bytes, void* out, int out_dtype,
+                        int* status, cachalot_stream_t stream);
+
+/* ---- FP8 E4M3 trunk GEMV with act_quant ---------------------------------------------------- */
+
+/* Replaces model/fp8_ref.py:27-92 quantize_activation_fp8 and model/fp8_fused_metal.py:175-233:
+ * per block of `block` (32 or 128) along K: amax = max(|x|, 1e-4); scale = 2^ceil(log2(amax/448))
+ * (CACHALOT_SCALE_E8M0) or amax/448 (CACHALOT_SCALE_F32); codes = E4M3FN(clip(x/scale, +-448)).
+ * x bf16 [rows,K] -> codes u8 [rows,K], scales f32 [rows,K/block]. */
+CACHALOT_API int cachalot_fp8_act_quant(const void* x_bf16, int rows, int k, int block, int scale_rule, uint8_t* codes,
+                           float* scales, cachalot_stream_t stream);
+
+/* Replaces model/fp8_ref.py:95-231 fp8_gemv_reference, model/fp8_gemv_metal.py:163-277 and
+ * model/fp8_fused_metal.py:265-342 (fp8_linear_quantized of model/fp8_linear_metal.py:56-89):
+ *   y[r,n] = sum_kb (sum_{j in kb} a[r,j] w[n,j]) * act_scale[r,kb] * wscale[n/block, kb]
+ * weight u8 [N,K] raw E4M3 (codes 0x7F/0xFF read as 0); w_scales [ceil(N/block), K/block] as E8M0
+ * bytes or f32 by scale_rule; out bf16 [rows,N] (f32 when out_dtype == CACHALOT_F32). */
+CACHALOT_API int cachalot_fp8_gemv(const uint8_t* codes, const float* act_scales, const uint8_t* weight, const void* w_scales,
+                      int scale_rule, int block, int rows, int n, int k, void* out, int out_dtype,
+                      cachalot_stream_t stream);
+
+/* ---- prefill: expert-major grouping, MXFP4 activations, grouped FFN ------------------------ */
+
+/* Replaces the host-side grouping of model/moe_prefill_grouped.py:201-225 (and
+ * glm/experts.py:301-303): a stable sort of the flattened [tokens*k] expert ids.
+ * perm i32 [tokens*k] = flattened (token*k + route slot) ids in expert-major order, offsets
+ * i32 [E+1]; ids outside [0,E) are dropped from perm (offsets[E] < tokens*k) and flagged.
+ * counts_scratch: i32 [E+1] device scratch. */
+CACHALOT_API int cachalot_group_rows(const int32_t* expert_ids, int tokens, int k, int n_experts, int32_t* perm,
+                        int32_t* offsets, int32_t* counts_scratch, int* status, cachalot_stream_t stream);
+
+/* Replaces model/fp4_act_mlx.py:101-250 (block 32, E8M0 scales) as a quantiser that keeps the
+ * codes: x bf16 [rows,K] (row r read from src_rows[r] when src_rows != NULL) ->
+ * codes u8 [rows,K/2] (low nibble first) + scale bytes u8 [rows,K/32]. */
+CACHALOT_API int cachalot_mxfp4_act_quant(const void* x_bf16, const int32_t* src_rows, int rows, int k, uint8_t* codes,
+                             uint8_t* scales, cachalot_stream_t stream);
+
+CACHALOT_API size_t cachalot_moe_prefill_workspace_bytes(const cachalot_bank_desc* desc /* host */, int tokens, int k,
+                                            int mxfp4_act);
+
+/* Replaces the expert loop and combine of model/moe_prefill_grouped.py:384-530 with
+ * model/fp4_sgmm_metal.py:318-333 / model/moe_prefill_batched.py:31-61 /
+ * model/expert_affine.py:84-99 as the per-expert op: rows grouped by (perm, offsets) run through
+ * their expert once, results are kept per route slot and summed in slot order 0..k-1.
+ * x bf16 [tokens,H]; slot_of_expert i32 [E] maps expert id -> bank slot (-1 = absent -> zeros);
+ * gate_w f32 [tokens,k]; mxfp4_act != 0 quantises x and the hidden activation to MXFP4 per 32
+ * first.  out f32 [tokens,H]. */
+CACHALOT_API int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc* desc /* host */, const void* x_bf16,
+                         const int32_t* perm, const int32_t* offsets, const int32_t* slot_of_expert,
+                         const float* gate_w, int tokens, int k, int n_experts, float swiglu_limit, int mxfp4_act,
+                         void* workspace, size_t workspace_bytes, float* out, int* status,
+                         cachalot_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CACHALOT_B200_H */

@@ -1,0 +1,176 @@
+"""GPU parity: routed-expert decode over FP4 and 2-bit affine banks (through the C ABI)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+from oracle import affine, configs, fp4, router  # noqa: E402
+from tests.helpers import bf16_tensor, make_bank, max_rel  # noqa: E402
+
+TOL = 2e-3  # max relative error of layer outputs against the fp32-accumulated oracle
+
+
+def _fp4_expert_out(x, e, w=None, limit=10.0):
+    return fp4.expert_forward(x, e["w1.weight"], e["w1.scale"], e["w2.weight"], e["w2.scale"], e["w3.weight"], e["w3.scale"],
+                              weight=w, swiglu_limit=limit, acc=np.float64)
+
+
+def test_config0_single_fp4_expert_full_size():
+    """x bf16 [1,4096], one FP4 expert 2880x4096, no clamp, no router weight, fp32 accumulation -> bf16."""
+    import cachalot_b200 as cb
+    x, e = configs.config0(seed=0)
+    bank = make_bank([e], cb.FP4_FORMAT, 4096, 2880)
+    slots = torch.zeros((1, 1), dtype=torch.int32, device="cuda")
+    w = torch.ones((1, 1), dtype=torch.float32, device="cuda")
+    got = cb.moe_forward(bf16_tensor(x), slots, w, bank, swiglu_limit=0.0).cpu().numpy()
+    want = _fp4_expert_out(x, e, None, 0.0)
+    assert max_rel(got, want) < TOL
+    got_bf16 = cb.moe_forward(bf16_tensor(x), slots, w, bank, swiglu_limit=0.0, out_dtype=torch.bfloat16).float().cpu().numpy()
+    assert max_rel(got_bf16, want) < 2 ** -8 + TOL
+    # the loose-tensor entry of the reference gives the same numbers
+    t = {k: torch.from_numpy(v).cuda() for k, v in e.items()}
+    loose = cb.routed_expert_forward(bf16_tensor(x)[0], w1_packed=t["w1.weight"], w1_scales=t["w1.scale"], w2_packed=t["w2.weight"],
+                                     w2_scales=t["w2.scale"], w3_packed=t["w3.weight"], w3_scales=t["w3.scale"], weight=None,
+                                     swiglu_limit=0.0).cpu().numpy()
+    assert np.array_equal(loose, got[0])
+
+
+@pytest.mark.parametrize("rows", [1, 3, 8])
+def test_fp4_topk_small_shapes_match_oracle(rows):
+    import cachalot_b200 as cb
+    rng = np.random.default_rng(10 + rows)
+    hidden, inter, n_exp, k = 256, 192, 12, 6
+    experts = [configs.fp4_expert(rng, hidden, inter) for _ in range(n_exp)]
+    bank = make_bank(experts, cb.FP4_FORMAT, hidden, inter)
+    x = configs.round_bf16(rng.standard_normal((rows, hidden)).astype(np.float32) * 4)
+    ids = np.stack([rng.permutation(n_exp)[:k] for _ in range(rows)]).astype(np.int32)
+    w = rng.uniform(0.05, 0.6, (rows, k)).astype(np.float32)
+    got = cb.moe_forward(bf16_tensor(x), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), bank, swiglu_limit=10.0).cpu().numpy()
+    want = np.stack([fp4.routed_topk_forward(x[t], [experts[i] for i in ids[t]], w[t], swiglu_limit=10.0, acc=np.float64) for t in range(rows)])
+    assert max_rel(got, want) < TOL
+
+
+def test_fused_routed_experts_reference_signature():
+    import cachalot_b200 as cb
+    rng = np.random.default_rng(4)
+    hidden, inter = 128, 96
+    experts = [configs.fp4_expert(rng, hidden, inter) for _ in range(6)]
+    bank = make_bank(experts, cb.FP4_FORMAT, hidden, inter)
+    x = configs.round_bf16(rng.standard_normal(hidden).astype(np.float32))
+    w = np.full(6, 0.25, np.float32)
+    res = [bank.expert(0, i) for i in (5, 0, 3, 1, 2, 4)]
+    got = cb.fused_routed_experts(bf16_tensor(x), res, torch.from_numpy(w).cuda(), hidden_size=hidden, intermediate=inter).cpu().numpy()
+    want = fp4.routed_topk_forward(x, [experts[i] for i in (5, 0, 3, 1, 2, 4)], w, acc=np.float64)
+    assert max_rel(got, want) < TOL
+    assert res[0].w1_weight.data_ptr() == bank.slab[5].data_ptr()       # views alias the slot
+    with pytest.raises(ValueError):
+        cb.fused_routed_experts(bf16_tensor(x), res, torch.from_numpy(w[:5]).cuda(), hidden_size=hidden, intermediate=inter)
+    with pytest.raises(KeyError):
+        bank.expert(0, 6)
+
+
+def test_missing_slot_gives_zero_rows_and_leaves_the_others_alone():
+    import cachalot_b200 as cb
+    rng = np.random.default_rng(5)
+    hidden, inter = 128, 96
+    experts = [configs.fp4_expert(rng, hidden, inter) for _ in range(4)]
+    bank = make_bank(experts, cb.FP4_FORMAT, hidden, inter)
+    x = bf16_tensor(rng.standard_normal((1, hidden)).astype(np.float32))
+    w = torch.full((1, 3), 0.3, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    full = cb.moe_forward(x, torch.tensor([[0, 1, 2]], dtype=torch.int32, device="cuda"), w, bank, status=status)
+    two = cb.moe_forward(x, torch.tensor([[0, 2]], dtype=torch.int32, device="cuda"), w[:, :2], bank, status=status)
+    holed = cb.moe_forward(x, torch.tensor([[0, -1, 2]], dtype=torch.int32, device="cuda"), w, bank, status=status)
+    assert torch.equal(holed, two) and not torch.equal(holed, full)
+    assert int(status.item()) == 0
+    none = cb.moe_forward(x, torch.tensor([[-1, -1, -1]], dtype=torch.int32, device="cuda"), w, bank, status=status)
+    assert float(none.abs().max()) == 0.0
+    oob = cb.moe_forward(x, torch.tensor([[0, 4, 2]], dtype=torch.int32, device="cuda"), w, bank, status=status)
+    assert torch.equal(oob, two) and int(status.item()) & 1
+
+
+def test_config1_affine_layer_full_size():
+    """2-bit g128 bank (fp16 scales/biases), sigmoid top-6 routing, batch 1, full shapes; only the
+    routed experts are materialised (the rest of the 384 never enter the arithmetic)."""
+    import cachalot_b200 as cb
+    x, logits, _ = configs.config1(seed=0, materialise=[])
+    inds, w, _ = router.route_tail(logits[0], np.zeros(384, np.float32), np.arange(384, dtype=np.int32)[None], 0, 6, 1.0, weights_bf16=False)
+    ginds, gw, gslots = cb.route_tail(torch.from_numpy(logits).cuda(), None, None, 0, 6, 1.0, weights_bf16=False)
+    assert ginds.cpu().numpy()[0].tolist() == inds.tolist()
+    _, _, experts = configs.config1(seed=0, materialise=inds.tolist())
+    fmt = cb.affine_format(4096, 2880)
+    order = [int(i) for i in inds]
+    bank = make_bank([experts[i] for i in order], fmt, 4096, 2880)
+    slots = torch.arange(6, dtype=torch.int32, device="cuda")[None]
+    got = cb.moe_forward(bf16_tensor(x), slots, gw, bank, swiglu_limit=10.0).cpu().numpy()
+    want = affine.affine_routed_experts(x[0], [experts[i] for i in order], w, bits=2, group_size=128, swiglu_limit=10.0, acc=np.float64)
+    assert max_rel(got[0], want) < TOL
+    res = [cb.ResidentExpert(0, i, s, bank) for s, i in enumerate(order)]
+    again = cb.affine_routed_experts(bf16_tensor(x)[0], res, fmt, gw[0], swiglu_limit=10.0).cpu().numpy()
+    assert np.array_equal(again, got[0])
+
+
+@pytest.mark.parametrize("group,dims", [(128, (256, 320)), (64, (128, 192))])
+def test_affine_small_shapes_batch(group, dims):
+    import cachalot_b200 as cb
+    hidden, inter = dims       # 320 is 2.5 groups of 128: groups run over the flattened matrix
+    rng = np.random.default_rng(20 + group)
+    experts = []
+    for _ in range(5):
+        e = {}
+        for proj, (n, kk) in (("w1", (inter, hidden)), ("w2", (hidden, inter)), ("w3", (inter, hidden))):
+            lv = rng.integers(0, 4, (n, kk), dtype=np.uint8)
+            e[f"{proj}.weight"] = affine.pack_bits(lv, 2)
+            e[f"{proj}.scales"] = rng.uniform(0.002, 0.02, n * kk // group).astype(np.float16)
+            e[f"{proj}.biases"] = (rng.standard_normal(n * kk // group) * 0.01).astype(np.float16)
+        experts.append(e)
+    bank = make_bank(experts, cb.affine_format(hidden, inter, 2, group), hidden, inter)
+    rows, k = 4, 3
+    x = configs.round_bf16(rng.standard_normal((rows, hidden)).astype(np.float32) * 3)
+    ids = np.stack([rng.permutation(5)[:k] for _ in range(rows)]).astype(np.int32)
+    w = rng.uniform(0.1, 0.5, (rows, k)).astype(np.float32)
+    got = cb.moe_forward(bf16_tensor(x), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), bank).cpu().numpy()
+
+    def dense(e, proj, n, kk):
+        q = affine.unpack_bits(e[f"{proj}.weight"], 2, kk).astype(np.float32).reshape(-1)
+        s = np.repeat(e[f"{proj}.scales"].astype(np.float32), group)
+        b = np.repeat(e[f"{proj}.biases"].astype(np.float32), group)
+        return (s * q + b).astype(np.float32).reshape(n, kk)
+
+    from oracle.bf16 import round_bf16
+    want = np.zeros((rows, hidden), np.float32)
+    for t in range(rows):
+        for j in range(k):
+            e = experts[ids[t, j]]
+            g = round_bf16((x[t].astype(np.float64) @ dense(e, "w1", inter, hidden).T.astype(np.float64)).astype(np.float32))
+            u = round_bf16((x[t].astype(np.float64) @ dense(e, "w3", inter, hidden).T.astype(np.float64)).astype(np.float32))
+            h = round_bf16((fp4.swiglu(g, u, 10.0) * w[t, j]).astype(np.float32))
+            want[t] += round_bf16((h.astype(np.float64) @ dense(e, "w2", hidden, inter).T.astype(np.float64)).astype(np.float32))
+    assert max_rel(got, want) < TOL
+
+
+def test_decode_full_size_properties():
+    """Properties at the benchmark's shapes that need no oracle: a zero gate weight removes an expert,
+    rows are independent, and a repeated call is bit-identical (fixed reduction order)."""
+    import cachalot_b200 as cb
+    g = torch.Generator(device="cuda").manual_seed(0)
+    hidden, inter, n_slots, k = 4096, 2880, 12, 6
+    bank = cb.SlabBank(cb.FP4_FORMAT, hidden, inter, n_slots)
+    bank.slab.copy_(torch.randint(0, 256, bank.slab.shape, dtype=torch.uint8, device="cuda", generator=g))
+    for name in ("w1.scale", "w2.scale", "w3.scale"):
+        o, n = bank.offsets[name], bank.tensor_sizes[name]
+        bank.slab[:, o:o + n] = torch.randint(118, 124, (n_slots, n), dtype=torch.uint8, device="cuda", generator=g)
+    x = torch.randn((8, hidden), device="cuda", generator=g).to(torch.bfloat16)
+    slots = torch.stack([torch.randperm(n_slots, device="cuda", generator=g)[:k] for _ in range(8)]).to(torch.int32)
+    w = torch.rand((8, k), device="cuda", generator=g) * 0.3
+    a = cb.moe_forward(x, slots, w, bank)
+    b = cb.moe_forward(x, slots, w, bank)
+    assert torch.equal(a, b) and bool(torch.isfinite(a).all())
+    row3 = cb.moe_forward(x[3:4], slots[3:4], w[3:4], bank)
+    assert torch.equal(row3[0], a[3])
+    w0 = w.clone()
+    w0[:, 2] = 0
+    s_drop = slots.clone()
+    s_drop[:, 2] = -1
+    assert torch.allclose(cb.moe_forward(x, slots, w0, bank), cb.moe_forward(x, s_drop, w, bank), rtol=0, atol=0)
