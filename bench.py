@@ -1,0 +1,406 @@
+"""Benchmark of the routed-expert MoE decode path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--bank affine2|fp4] [--batch B] [--distinct-layers NL]
+
+One step = one decoded token = LAYERS (40) MoE layer passes: per layer the sigmoid top-6 routing
+tail with slot lookup, then the routed experts (gate/up, SwiGLU, down, weighted sum) over the
+resident bank.  The default workload is the 2-bit affine g128 bank, batch 1, 384 experts per
+layer; the bank holds NL distinct layers (default 8, 30.6 GB) that the 40 passes cycle through
+with fresh random routing, so the bytes a pass reads were last touched hundreds of MB ago (the
+working set is far larger than L2).  Prints ONE JSON line (rank 0).
+
+N > 1 shards the experts of every layer over the ranks (expert parallel, replicated input,
+partial outputs summed with an NCCL all-reduce); total work is fixed ("strong" scaling).
+`--impl reference` times the CPU path (the numpy oracle port of the reference's arithmetic)
+on the host cores for the same metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+HIDDEN, INTER, EXPERTS, TOPK, LAYERS = 4096, 2880, 384, 6, 40
+SWIGLU_LIMIT = 10.0
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# capture summarised under profiles/ (None until a capture exists for the workload)
+NCU_TRAFFIC_BYTES = {}
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--bank", default="affine2", choices=["affine2", "fp4"])
+    p.add_argument("--batch", type=int, default=1)
+    p.add_argument("--distinct-layers", type=int, default=8)
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-graph", action="store_true")
+    return p.parse_args()
+
+
+def measured_peak():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+# ---- clocks ---------------------------------------------------------------------------------
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit())
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---- CPU arm --------------------------------------------------------------------------------
+
+def cpu_layer_inputs(bank_kind: str, seed: int = 0):
+    import numpy as np
+    from oracle import configs, router
+
+    rng = np.random.default_rng(seed)
+    x = configs.round_bf16(rng.standard_normal((1, HIDDEN)).astype(np.float32))
+    logits = rng.standard_normal(EXPERTS).astype(np.float32)
+    inds, w, _ = router.route_tail(logits, np.zeros(EXPERTS, np.float32), np.arange(EXPERTS, dtype=np.int32)[None], 0, TOPK, 1.0,
+                                   weights_bf16=False)
+    make = configs.affine_expert if bank_kind == "affine2" else configs.fp4_expert
+    experts = [make(np.random.default_rng([seed, int(e)]), HIDDEN, INTER) for e in inds]
+    return x[0], w, experts
+
+
+def cpu_layer_pass(bank_kind: str, x, w, experts, threads: int):
+    """One MoE layer for one token on the host: the reference's CPU arithmetic (packed bytes ->
+    dequant -> matvec -> SwiGLU -> down), experts spread over `threads` threads."""
+    import numpy as np
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import affine, fp4
+
+    def one(i):
+        e = experts[i]
+        if bank_kind == "affine2":
+            return affine.affine_expert_forward(x, e, bits=2, group_size=128, weight=w[i], swiglu_limit=SWIGLU_LIMIT)
+        return fp4.expert_forward(x, e["w1.weight"], e["w1.scale"], e["w2.weight"], e["w2.scale"], e["w3.weight"], e["w3.scale"],
+                                  weight=w[i], swiglu_limit=SWIGLU_LIMIT)
+
+    if threads > 1:
+        with ThreadPoolExecutor(max_workers=threads) as pool:
+            outs = list(pool.map(one, range(len(experts))))
+    else:
+        outs = [one(i) for i in range(len(experts))]
+    total = np.zeros(HIDDEN, np.float32)
+    for o in outs:
+        total = total + o
+    return total
+
+
+def time_cpu(bank_kind: str, steps: int, warmup: int, threads: int):
+    x, w, experts = cpu_layer_inputs(bank_kind)
+    for _ in range(warmup):
+        cpu_layer_pass(bank_kind, x, w, experts, threads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_layer_pass(bank_kind, x, w, experts, threads)
+    dt = (time.perf_counter() - t0) / steps
+    return dt, 1.0 / (dt * LAYERS)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = min(TOPK, os.cpu_count() or 1)
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 1))
+    dt, tok_s = time_cpu(args.bank, steps, warmup, threads)
+    sample = f"{steps} timed passes of one MoE layer (6 routed experts from packed bytes), batch 1; a token = {LAYERS} passes"
+    line = {
+        "impl": "reference", "metric": "moe_decode_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": dt * LAYERS * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args, None),
+        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, extra):
+    cfg = {
+        "workload": ("decode MoE layer stack: " + ("2-bit affine g128 bank (fp16 scale+bias)" if args.bank == "affine2" else "FP4 E2M1/E8M0 bank")
+                     + f", {EXPERTS} experts/layer, top-{TOPK} sigmoid routing, batch {args.batch}, hidden {HIDDEN}, inter {INTER}, "
+                       f"{LAYERS} layer passes per token over {args.distinct_layers} distinct resident layers"),
+        "bank": args.bank, "batch": args.batch, "layers_per_token": LAYERS, "distinct_layers": args.distinct_layers,
+        "l2": "inputs larger than L2: each pass reads 6 random experts of a multi-GB bank; no flush needed",
+    }
+    if extra:
+        cfg.update(extra)
+    return cfg
+
+
+# ---- GPU arm --------------------------------------------------------------------------------
+
+def fill_bank(bank, gen):
+    import torch
+
+    kind = bank.fmt.kind
+    step = 64
+    for s0 in range(0, bank.n_slots, step):
+        s1 = min(s0 + step, bank.n_slots)
+        for name in bank.fmt.tensor_names:
+            o, n = bank.offsets[name], bank.tensor_sizes[name]
+            region = bank.slab[s0:s1, o:o + n]
+            if name.endswith("weight"):
+                region.copy_(torch.randint(0, 256, (s1 - s0, n), dtype=torch.uint8, device=bank.slab.device, generator=gen))
+            elif kind == "fp4":
+                region.copy_(torch.randint(118, 124, (s1 - s0, n), dtype=torch.uint8, device=bank.slab.device, generator=gen))
+            elif name.endswith("scales"):
+                v = torch.rand((s1 - s0, n // 2), device=bank.slab.device, generator=gen) * 0.018 + 0.002
+                region.view(torch.float16).copy_(v.to(torch.float16))
+            else:
+                v = torch.randn((s1 - s0, n // 2), device=bank.slab.device, generator=gen) * 0.01
+                region.view(torch.float16).copy_(v.to(torch.float16))
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import cachalot_b200 as cb
+    from cachalot_b200 import _lib, ep
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    B, NL, K = args.batch, args.distinct_layers, TOPK
+    fmt = cb.affine_format(HIDDEN, INTER) if args.bank == "affine2" else cb.FP4_FORMAT
+    lo, hi = ep.local_range(EXPERTS, rank, world)
+    n_local = hi - lo
+    bank = cb.SlabBank(fmt, HIDDEN, INTER, NL * n_local, layers=NL, n_experts=EXPERTS, device=dev)
+    table = ep.local_slot_table(NL, EXPERTS, rank, world).to(dev)
+    fill_bank(bank, torch.Generator(device=dev).manual_seed(1234 + rank))
+
+    # replicated inputs: identical seed on every rank
+    P = 16
+    g_in = torch.Generator().manual_seed(7)
+    x_host = torch.randn((P, B, HIDDEN), generator=g_in).to(torch.bfloat16).pin_memory()
+    logits_host = torch.randn((P, LAYERS, B, EXPERTS), generator=g_in).pin_memory()
+    out_host = torch.empty((B, HIDDEN), dtype=torch.float32).pin_memory()
+    x_pool, logits_pool = x_host.to(dev), logits_host.to(dev)
+    x = x_pool[0].clone()
+    logits = logits_pool[0].clone()
+    out = torch.zeros((B, HIDDEN), dtype=torch.float32, device=dev)
+    ws = torch.empty(max(_lib.lib.cachalot_moe_decode_workspace_bytes(bank.desc_ptr, B, K), 1 << 20), dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    slots_all = torch.empty((LAYERS, B, K), dtype=torch.int32, device=dev)
+    w_all = torch.empty((LAYERS, B, K), dtype=torch.float32, device=dev)
+
+    def token_step():
+        for l in range(LAYERS):
+            _, w, slots = cb.route_tail(logits[l], None, table, l % NL, K, 1.0, weights_bf16=False)
+            cb.moe_forward(x, slots, w, bank, swiglu_limit=SWIGLU_LIMIT, out=out, workspace=ws, status=status)
+            if world > 1:
+                dist.all_reduce(out)
+
+    def phase_step(phase):
+        for l in range(LAYERS):
+            cb.moe_forward(x, slots_all[l], w_all[l], bank, swiglu_limit=SWIGLU_LIMIT, out=out, workspace=ws, status=status, phase=phase)
+
+    stream = torch.cuda.Stream(device=dev)
+    use_graph = not args.no_graph
+
+    def make_runner(fn):
+        with torch.cuda.stream(stream):
+            fn()
+            stream.synchronize()
+            if not use_graph:
+                return fn
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                fn()
+            return g.replay
+
+    run_token = make_runner(token_step)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(fn, steps, before=None, after=None):
+        """CUDA-event time of `steps` calls on `stream`, max over ranks (ms)."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for i in range(steps):
+                if before:
+                    before(i)
+                fn()
+                if after:
+                    after(i)
+            e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def feed_device(i):
+        x.copy_(x_pool[i % P], non_blocking=True)
+        logits.copy_(logits_pool[i % P], non_blocking=True)
+
+    def feed_host(i):
+        x.copy_(x_host[i % P], non_blocking=True)
+        logits.copy_(logits_host[i % P], non_blocking=True)
+
+    def read_back(i):
+        out_host.copy_(out, non_blocking=True)
+        stream.synchronize()
+
+    timed(run_token, args.warmup, feed_device)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = timed(run_token, args.steps, feed_device)
+    ms_e2e = timed(run_token, args.steps, feed_host, read_back)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # per-kernel durations: the same 40 passes with routing done beforehand, one launch kind at a time
+    with torch.cuda.stream(stream):
+        distinct = 0
+        for l in range(LAYERS):
+            _, w, slots = cb.route_tail(logits[l], None, table, l % NL, K, 1.0, weights_bf16=False)
+            slots_all[l], w_all[l] = slots, w
+        stream.synchronize()
+        for l in range(LAYERS):
+            s = slots_all[l].reshape(-1)
+            distinct += int(torch.unique(s[s >= 0]).numel())
+    run_gu = make_runner(lambda: phase_step("gate_up"))
+    run_dn = make_runner(lambda: phase_step("down"))
+    reps = max(3, args.steps // 2)
+    timed(run_gu, 2)
+    ms_gu = timed(run_gu, reps) / (reps * LAYERS)
+    timed(run_dn, 2)
+    ms_dn = timed(run_dn, reps) / (reps * LAYERS)
+    st = int(status.item())
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    sizes = bank.tensor_sizes
+    up_bytes = sum(v for n, v in sizes.items() if n.startswith(("w1", "w3")))
+    dn_bytes = sum(v for n, v in sizes.items() if n.startswith("w2"))
+    u_per_layer = distinct / LAYERS          # distinct experts this rank streams per pass (routing of pool entry 0)
+    gu_alg = u_per_layer * up_bytes + B * HIDDEN * 2 + B * K * INTER * 4
+    dn_alg = u_per_layer * dn_bytes + B * K * INTER * 4 + B * HIDDEN * 4
+    peak, peak_kind = measured_peak()
+    gu_gbs = gu_alg / (ms_gu * 1e-3) / 1e9
+    dn_gbs = dn_alg / (ms_dn * 1e-3) / 1e9
+    tok_s = B * args.steps / (ms * 1e-3)
+    tok_s_e2e = B * args.steps / (ms_e2e * 1e-3)
+    layer_bytes = gu_alg + dn_alg
+    hbm_gbs_token = layer_bytes * LAYERS * args.steps / (ms * 1e-3) / 1e9
+
+    line = {
+        "metric": "moe_decode_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None,
+        "dtype": "int2xbf16->f32" if args.bank == "affine2" else "e2m1xbf16->f32", "data": "synthetic",
+        "config": workload_config(args, {"parallelism": f"ep{world}", "cuda_graph": use_graph, "numerics_version": cb.NUMERICS_VERSION}),
+        "clocks": clocks,
+        "e2e": {"value": tok_s_e2e, "unit": "tok/s", "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": int(x_host[0].numel() * 2 + logits_host[0].numel() * 4),
+                "d2h_bytes_per_step": int(out_host.numel() * 4)},
+        "gpu_launches": 3 * LAYERS * args.steps,
+        "hbm": {"token_algorithmic_gbs": hbm_gbs_token, "frac_of_8tbs": hbm_gbs_token / 8000.0, "frac_of_peak": hbm_gbs_token / peak},
+        "roofline": {"kernel": "gate_up (W1,W3 dequant-GEMV + SwiGLU)", "bound": "hbm", "achieved": gu_gbs, "peak": peak,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": gu_gbs / peak, "us_per_launch": ms_gu * 1e3,
+                     "algorithmic_bytes_per_launch": gu_alg, "traffic": NCU_TRAFFIC_BYTES.get((args.bank, B, "gate_up")),
+                     "down": {"achieved": dn_gbs, "frac": dn_gbs / peak, "us_per_launch": ms_dn * 1e3,
+                              "algorithmic_bytes_per_launch": dn_alg, "traffic": NCU_TRAFFIC_BYTES.get((args.bank, B, "down"))}},
+        "status_word": st,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        threads = 1
+        dt, cpu_tok_s = time_cpu(args.bank, 3, 1, threads)
+        line["cpu_baseline"] = {"value": cpu_tok_s, "unit": "tok/s", "cores": threads, "kind": "port",
+                                "sample": f"3 timed passes of one MoE layer (6 routed experts from packed bytes, numpy), {dt:.2f} s each; "
+                                          f"a token = {LAYERS} passes"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -13,7 +13,8 @@ LIB_PATH = _PKG / "libcachalot_b200.so"
 OK, EINVAL, EALIGN, EUNSUPPORTED, ECUDA, ESCRATCH = 0, -1, -2, -3, -4, -5
 BANK_FP4, BANK_AFFINE = 0, 1
 F16, BF16, F32 = 0, 1, 2
-NUMERICS_F32, NUMERICS_BF16 = 0, 1
+NUMERICS_F32, NUMERICS_BF16, NUMERICS_BF16_H32 = 0, 1, 2
+DECODE_ONLY_GATE_UP, DECODE_ONLY_DOWN = 0x100, 0x200
 ROUTER_SQRT_SOFTPLUS, ROUTER_SIGMOID = 0, 1
 SCALE_E8M0, SCALE_F32 = 0, 1
 STATUS_SLOT_RANGE, STATUS_ID_RANGE = 1, 2

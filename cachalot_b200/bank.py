@@ -151,7 +151,8 @@ class SlabBank:
             self.view(slot, name).copy_(src)
 
     def expert(self, layer: int, expert: int) -> "ResidentExpert":
-        slot = int(self.slot_table_host[layer, expert])
+        in_range = 0 <= layer < self.layers and 0 <= expert < self.n_experts
+        slot = int(self.slot_table_host[layer, expert]) if in_range else -1
         if slot < 0:
             raise KeyError(f"Missing expert entry: {(layer, expert)!r}")
         return ResidentExpert(layer, expert, slot, self)

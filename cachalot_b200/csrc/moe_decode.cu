@@ -142,7 +142,7 @@ gate_up_kernel(BankView bank, const __nv_bfloat16* __restrict__ x, const int32_t
   g = warp_sum(g);
   u = warp_sum(u);
   if (lane == 0) {
-    if (numerics == CACHALOT_NUMERICS_BF16) {
+    if (numerics != CACHALOT_NUMERICS_F32) {
       g = bf16_round(g);
       u = bf16_round(u);
     }
@@ -184,7 +184,7 @@ down_kernel(BankView bank, const float* __restrict__ hidden, const int32_t* __re
       else
         y = row_dot<FMT>(rec + bank.off[3], rec + bank.off[4], rec + bank.off[5], n, I, bank.group, bank.scale_dtype, hs, hsum, lut, lane);
       y = warp_sum(y);
-      if (numerics == CACHALOT_NUMERICS_BF16) y = bf16_round(y);
+      if (numerics != CACHALOT_NUMERICS_F32) y = bf16_round(y);
       total += y;
     }
   }
@@ -234,8 +234,11 @@ static int make_view(const void* bank, const cachalot_bank_desc* d, BankView* v,
 
 template <int FMT>
 static int launch_decode(const BankView& v, const void* x, const int32_t* slots, const float* gate_w, int rows, int k,
-                         float limit, int numerics, float* hidden, void* out, int out_dtype, int* status,
+                         float limit, int numerics_flags, float* hidden, void* out, int out_dtype, int* status,
                          cudaStream_t stream, bool mx_hidden = false) {
+  const int numerics = numerics_flags & 0xff;
+  const bool do_gate_up = !(numerics_flags & CACHALOT_DECODE_ONLY_DOWN);
+  const bool do_down = !(numerics_flags & CACHALOT_DECODE_ONLY_GATE_UP);
   constexpr int CH = Fmt<FMT>::CH;
   const int H = v.hidden, I = v.inter;
   size_t smem_gu = (size_t)H * 4 + (FMT == CACHALOT_BANK_AFFINE ? (size_t)(H / CH) * 4 : 0);
@@ -248,14 +251,18 @@ static int launch_decode(const BankView& v, const void* x, const int32_t* slots,
     cudaFuncSetAttribute(down_kernel<FMT, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     attr_done[FMT] = true;
   }
-  dim3 g1((I + WARPS - 1) / WARPS, rows * k);
-  gate_up_kernel<FMT><<<g1, WARPS * 32, smem_gu, stream>>>(v, (const __nv_bfloat16*)x, slots, gate_w, k, limit, numerics, hidden, status);
-  int rc = check_launch("moe_decode gate_up");
-  if (rc) return rc;
+  int rc = CACHALOT_OK;
+  if (do_gate_up) {
+    dim3 g1((I + WARPS - 1) / WARPS, rows * k);
+    gate_up_kernel<FMT><<<g1, WARPS * 32, smem_gu, stream>>>(v, (const __nv_bfloat16*)x, slots, gate_w, k, limit, numerics, hidden, status);
+    rc = check_launch("moe_decode gate_up");
+    if (rc) return rc;
+  }
   if (mx_hidden) {
     rc = launch_mxfp4_roundtrip_f32(hidden, (long long)rows * k, I, stream);
     if (rc) return rc;
   }
+  if (!do_down) return rc;
   dim3 g2((H + WARPS - 1) / WARPS, rows);
   if (out_dtype == CACHALOT_BF16)
     down_kernel<FMT, __nv_bfloat16><<<g2, WARPS * 32, smem_dn, stream>>>(v, hidden, slots, k, numerics, (__nv_bfloat16*)out);
@@ -283,7 +290,8 @@ extern "C" int cachalot_moe_decode(const void* bank, const cachalot_bank_desc* d
   if (!x_bf16 || !slots || !gate_w || !out) return fail(CACHALOT_EINVAL, "moe_decode: null pointer");
   if (rows < 0 || k <= 0 || k > 64) return fail(CACHALOT_EINVAL, "moe_decode: rows=%d k=%d out of range", rows, k);
   if ((long long)rows * k > 65535) return fail(CACHALOT_EINVAL, "moe_decode: rows*k=%lld exceeds 65535", (long long)rows * k);
-  if (numerics != CACHALOT_NUMERICS_F32 && numerics != CACHALOT_NUMERICS_BF16) return fail(CACHALOT_EINVAL, "moe_decode: unknown numerics %d", numerics);
+  if ((numerics & 0xff) > CACHALOT_NUMERICS_BF16_H32 || (numerics & ~0x3ff))
+    return fail(CACHALOT_EINVAL, "moe_decode: unknown numerics %d", numerics);
   if (out_dtype != CACHALOT_F32 && out_dtype != CACHALOT_BF16) return fail(CACHALOT_EINVAL, "moe_decode: out dtype must be f32 or bf16");
   if (rows == 0) return CACHALOT_OK;
   size_t need = cachalot_moe_decode_workspace_bytes(desc, rows, k);
@@ -361,7 +369,8 @@ extern "C" int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc* 
   rows_to_slots_kernel<<<n_experts, 128, 0, s>>>(perm, offsets, slot_of_expert, n_experts, slots);
   rc = check_launch("moe_prefill slots");
   if (rc) return rc;
+  const int num = mxfp4_act ? CACHALOT_NUMERICS_BF16_H32 : CACHALOT_NUMERICS_BF16;
   if (desc->format == CACHALOT_BANK_FP4)
-    return launch_decode<CACHALOT_BANK_FP4>(v, x_in, slots, gate_w, tokens, k, swiglu_limit, CACHALOT_NUMERICS_BF16, hidden, out, CACHALOT_F32, status, s, mxfp4_act != 0);
-  return launch_decode<CACHALOT_BANK_AFFINE>(v, x_in, slots, gate_w, tokens, k, swiglu_limit, CACHALOT_NUMERICS_BF16, hidden, out, CACHALOT_F32, status, s, mxfp4_act != 0);
+    return launch_decode<CACHALOT_BANK_FP4>(v, x_in, slots, gate_w, tokens, k, swiglu_limit, num, hidden, out, CACHALOT_F32, status, s, mxfp4_act != 0);
+  return launch_decode<CACHALOT_BANK_AFFINE>(v, x_in, slots, gate_w, tokens, k, swiglu_limit, num, hidden, out, CACHALOT_F32, status, s, mxfp4_act != 0);
 }

@@ -43,6 +43,8 @@ def dequantize_fp4_weight(packed: torch.Tensor, scales: torch.Tensor, block_size
         raise ValueError(f"Scale shape {tuple(scales.shape)} does not match expected {(n, k // block_size)}")
     packed, scales = packed.contiguous(), scales.contiguous()
     out = torch.empty((n, k), dtype=torch.float32, device=packed.device)
+    if n == 0:
+        return out
     check(lib.cachalot_fp4_dequant(_ptr(packed), _ptr(scales), n, k, _ptr(out), _stream()))
     return out
 
@@ -166,13 +168,14 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
 def moe_forward(x: torch.Tensor, slot_ids: torch.Tensor, gate_weights: torch.Tensor, bank: SlabBank, *,
                 swiglu_limit: float = 10.0, numerics: str | None = None, out_dtype=torch.float32,
                 out: torch.Tensor | None = None, status: torch.Tensor | None = None,
-                workspace: torch.Tensor | None = None) -> torch.Tensor:
+                workspace: torch.Tensor | None = None, phase: str | None = None) -> torch.Tensor:
     """Routed experts for `rows` tokens: x bf16 [rows,H], slot_ids int32 [rows,k] (bank slots, -1 =
     absent -> zero contribution), gate_weights float32 [rows,k] -> [rows,H].
 
     numerics "f32" keeps fp32 between the projections (the FP4 decode op,
     model/moe_fused_metal.py:189-233); "bf16" rounds g, u, h and each expert's output to bf16 (the
-    affine op, model/expert_affine.py:65-81).  Default: by bank format."""
+    affine op, model/expert_affine.py:65-81).  Default: by bank format.  `phase` ("gate_up" or
+    "down") runs only one of the two launches; it exists for per-kernel timing."""
     _need_cuda(x, slot_ids, gate_weights)
     if x.dim() != 2 or x.shape[1] != bank.hidden:
         raise ValueError(f"x must be [rows, {bank.hidden}], got {tuple(x.shape)}")
@@ -182,7 +185,8 @@ def moe_forward(x: torch.Tensor, slot_ids: torch.Tensor, gate_weights: torch.Ten
     k = slot_ids.shape[1]
     if numerics is None:
         numerics = "f32" if bank.fmt.kind == "fp4" else "bf16"
-    num = {"f32": _lib.NUMERICS_F32, "bf16": _lib.NUMERICS_BF16}[numerics]
+    num = {"f32": _lib.NUMERICS_F32, "bf16": _lib.NUMERICS_BF16, "bf16_h32": _lib.NUMERICS_BF16_H32}[numerics]
+    num |= {None: 0, "gate_up": _lib.DECODE_ONLY_GATE_UP, "down": _lib.DECODE_ONLY_DOWN}[phase]
     xb = x.to(torch.bfloat16).contiguous()
     slot_ids = slot_ids.to(torch.int32).contiguous()
     gate_weights = gate_weights.to(torch.float32).contiguous()
@@ -329,6 +333,8 @@ def group_rows(expert_ids: torch.Tensor, n_experts: int, status: torch.Tensor | 
     perm = torch.empty(t * k, dtype=torch.int32, device=ids.device)
     offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=ids.device)
     scratch = torch.empty(n_experts + 1, dtype=torch.int32, device=ids.device)
+    if t * k == 0:
+        return perm, offsets.zero_()
     check(lib.cachalot_group_rows(_ptr(ids), t, k, n_experts, _ptr(perm), _ptr(offsets), _ptr(scratch), _ptr(status), _stream()))
     return perm, offsets
 

@@ -49,9 +49,12 @@ enum { CACHALOT_F16 = 0, CACHALOT_BF16 = 1, CACHALOT_F32 = 2 };
 /* rounding points of the expert FFN */
 enum {
   CACHALOT_NUMERICS_F32 = 0, /* decode FP4 op: fp32 everywhere (model/moe_fused_metal.py:101-179) */
-  CACHALOT_NUMERICS_BF16 = 1 /* affine and prefill ops: g,u -> bf16; h -> bf16; each expert's W2 h -> bf16
-                                (model/expert_affine.py:74-81, model/fp4_sgmm_metal.py:203-233) */
+  CACHALOT_NUMERICS_BF16 = 1, /* affine and prefill ops: g,u -> bf16; h -> bf16; each expert's W2 h -> bf16
+                                 (model/expert_affine.py:74-81, model/fp4_sgmm_metal.py:203-233) */
+  CACHALOT_NUMERICS_BF16_H32 = 2 /* as BF16 but h stays fp32 (it is quantised to MXFP4 next) */
 };
+/* profiling aids, OR-ed into `numerics`: run only one of the two launches of cachalot_moe_decode */
+enum { CACHALOT_DECODE_ONLY_GATE_UP = 0x100, CACHALOT_DECODE_ONLY_DOWN = 0x200 };
 enum { CACHALOT_ROUTER_SQRT_SOFTPLUS = 0, CACHALOT_ROUTER_SIGMOID = 1 };
 enum { CACHALOT_SCALE_E8M0 = 0, CACHALOT_SCALE_F32 = 1 };
 

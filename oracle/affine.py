@@ -64,14 +64,18 @@ def unpack_bits(words: np.ndarray, bits: int, n: int) -> np.ndarray:
 
 
 def dequantize_affine(words, scales, biases, *, bits: int, group_size: int) -> np.ndarray:
-    """words u32 [N, K*bits/32], scales/biases [N, K/group] (f16 or bf16 values held in any float
-    array) -> f32 [N, K] = f32(scale)*q + f32(bias), one float32 rounding (the product is exact)."""
-    s = np.asarray(scales).astype(np.float32)
-    b = np.asarray(biases).astype(np.float32)
-    n, groups = s.shape
-    k = groups * group_size
-    q = unpack_bits(words, bits, k).astype(np.float32).reshape(n, groups, group_size)
-    return (s[:, :, None] * q + b[:, :, None]).astype(np.float32).reshape(n, k)
+    """words u32 [N, K*bits/32]; scales/biases (f16 or bf16 values held in any float array), one
+    per `group_size` consecutive elements of the flattened [N*K] matrix -- shaped [N, K/group]
+    when the group divides K (the reference's layout) or flat [N*K/group] otherwise
+    -> f32 [N, K] = f32(scale)*q + f32(bias), one float32 rounding (the product is exact)."""
+    w = np.asarray(words)
+    n, k = w.shape[0], w.shape[1] * 32 // bits
+    s = np.asarray(scales).astype(np.float32).reshape(-1)
+    b = np.asarray(biases).astype(np.float32).reshape(-1)
+    if (n * k) % group_size or s.size != n * k // group_size or b.size != s.size:
+        raise ValueError(f"{s.size} scales for a {n}x{k} matrix at group {group_size}")
+    q = unpack_bits(w, bits, k).astype(np.float32).reshape(-1, group_size)
+    return (s[:, None] * q + b[:, None]).astype(np.float32).reshape(n, k)
 
 
 def quantize_affine_minmax(w: np.ndarray, *, bits: int, group_size: int, store=np.float16):

@@ -35,9 +35,12 @@ def config0(seed=0, hidden=4096, inter=2880):
 
 
 def affine_matrix(rng, n, k, bits=2, group=128):
+    """codes uniform, fp16 scale ~U(0.002,0.02) and bias ~N(0,0.01) per `group` consecutive
+    elements of the flattened matrix ([N, K/group] when the group divides K, else flat)."""
     levels = rng.integers(0, 1 << bits, (n, k), dtype=np.uint8)
-    scales = rng.uniform(0.002, 0.02, (n, k // group)).astype(np.float16)
-    biases = (rng.standard_normal((n, k // group)) * 0.01).astype(np.float16)
+    shape = (n, k // group) if k % group == 0 else (n * k // group,)
+    scales = rng.uniform(0.002, 0.02, shape).astype(np.float16)
+    biases = (rng.standard_normal(shape) * 0.01).astype(np.float16)
     return pack_bits(levels, bits), scales, biases
 
 
