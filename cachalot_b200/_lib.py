@@ -14,10 +14,10 @@ OK, EINVAL, EALIGN, EUNSUPPORTED, ECUDA, ESCRATCH = 0, -1, -2, -3, -4, -5
 BANK_FP4, BANK_AFFINE = 0, 1
 F16, BF16, F32 = 0, 1, 2
 NUMERICS_F32, NUMERICS_BF16, NUMERICS_BF16_H32 = 0, 1, 2
-DECODE_ONLY_GATE_UP, DECODE_ONLY_DOWN = 0x100, 0x200
+DECODE_ONLY_GATE_UP, DECODE_ONLY_DOWN, DECODE_SIMPLE = 0x100, 0x200, 0x400
 ROUTER_SQRT_SOFTPLUS, ROUTER_SIGMOID = 0, 1
 SCALE_E8M0, SCALE_F32 = 0, 1
-STATUS_SLOT_RANGE, STATUS_ID_RANGE = 1, 2
+STATUS_SLOT_RANGE, STATUS_ID_RANGE, STATUS_SCALE_RANGE = 1, 2, 4
 
 
 class BankDesc(C.Structure):
@@ -33,7 +33,7 @@ class BankDesc(C.Structure):
         ("bits", C.c_int32),
         ("group", C.c_int32),
         ("scale_dtype", C.c_int32),
-        ("reserved", C.c_int32),
+        ("fp4_scale_centre", C.c_int32),
     ]
 
 

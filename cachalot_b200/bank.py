@@ -107,7 +107,24 @@ class SlabBank:
         d.bits, d.group = fmt.bits, fmt.group_size
         sdt = fmt.dtypes.get("w1.scales", "float16")
         d.scale_dtype = _lib.BF16 if sdt == "bfloat16" else _lib.F16
+        d.fp4_scale_centre = 0
         self.desc = d
+
+    def calibrate_scale_centre(self) -> int:
+        """FP4 banks: set the descriptor's scale centre to the middle of the E8M0 bytes actually
+        stored (the tensor-core kernels hold block scales relative to it in f16 and accept
+        centre-14 .. centre+13).  Call once after the bank is filled; returns the centre."""
+        if self.fmt.kind != "fp4":
+            return 0
+        lo, hi = 255, 0
+        for name in ("w1.scale", "w2.scale", "w3.scale"):
+            o, n = self.offsets[name], self.tensor_sizes[name]
+            region = self.slab[:, o:o + n]
+            lo, hi = min(lo, int(region.min())), max(hi, int(region.max()))
+        if hi - lo > 27:
+            raise NotImplementedError(f"FP4 block scales span 2**{lo - 127}..2**{hi - 127}: wider than the 28 binades supported")
+        self.desc.fp4_scale_centre = max(1, min(254, (lo + hi + 1) // 2 + 0))
+        return int(self.desc.fp4_scale_centre)
 
     @property
     def desc_ptr(self):

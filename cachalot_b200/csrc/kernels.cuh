@@ -10,4 +10,42 @@ int launch_mxfp4_roundtrip_f32(float* data, long long rows, int k, cudaStream_t 
 // bf16 [rows,k] -> bf16 [rows,k] round trip (every MXFP4 value is exact in bf16).
 int launch_mxfp4_roundtrip_bf16(const __nv_bfloat16* in, __nv_bfloat16* out, long long rows, int k, cudaStream_t stream);
 
+struct BankView {
+  const uint8_t* base;
+  long long record_bytes;
+  long long off[9];
+  int n_slots, hidden, inter, bits, group, scale_dtype;
+  int format;        // CACHALOT_BANK_*
+  int scale_centre;  // FP4: E8M0 byte the tensor-core path scales relative to
+};
+
+template <int FMT>
+struct Fmt;
+template <>
+struct Fmt<CACHALOT_BANK_FP4> {
+  static constexpr int CH = 32;  // elements per 16-byte chunk
+};
+template <>
+struct Fmt<CACHALOT_BANK_AFFINE> {
+  static constexpr int CH = 64;  // 2-bit codes per 16-byte chunk
+};
+
+
+// Grouping of the routed rows r = token*k + route slot by bank slot, so that a slot's bytes are
+// streamed once for all rows that use it.  Null pointers mean "every row is its own group".
+struct Plan {
+  const int32_t* group_start;  // [n_groups + 1] offsets into order
+  const int32_t* order;        // [rows] row ids sorted by slot (stable)
+  const int32_t* group_slot;   // [n_groups]
+  const int32_t* n_groups;     // device scalar
+};
+
+// Tensor-core decode path (moe_decode_mma.cu).  Returns CACHALOT_EUNSUPPORTED without launching
+// when the shape is outside what it handles, so the caller can use the simple kernels.
+int launch_decode_mma(const BankView& v, const void* x, const int32_t* slots, const float* gate_w, int rows, int k,
+                      float limit, int numerics_flags, void* workspace, void* out, int out_dtype, int* status,
+                      cudaStream_t stream);
+size_t decode_mma_workspace_bytes(int hidden, int inter, int rows, int k);
+bool decode_mma_supported(const BankView& v, int rows, int k);
+
 }  // namespace cachalot

@@ -9,24 +9,6 @@
 
 namespace cachalot {
 
-struct BankView {
-  const uint8_t* base;
-  long long record_bytes;
-  long long off[9];
-  int n_slots, hidden, inter, bits, group, scale_dtype;
-};
-
-template <int FMT>
-struct Fmt;
-template <>
-struct Fmt<CACHALOT_BANK_FP4> {
-  static constexpr int CH = 32;  // elements per 16-byte chunk
-};
-template <>
-struct Fmt<CACHALOT_BANK_AFFINE> {
-  static constexpr int CH = 64;  // 2-bit codes per 16-byte chunk
-};
-
 __device__ __forceinline__ float scale_at(const void* p, long long i, int dt) {
   return dt == CACHALOT_F16 ? __half2float(reinterpret_cast<const __half*>(p)[i])
                             : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
@@ -229,6 +211,9 @@ static int make_view(const void* bank, const cachalot_bank_desc* d, BankView* v,
   v->bits = d->bits;
   v->group = d->group;
   v->scale_dtype = d->scale_dtype;
+  v->format = d->format;
+  v->scale_centre = d->fp4_scale_centre > 0 ? d->fp4_scale_centre : 121;
+  if (v->scale_centre > 254) return fail(CACHALOT_EINVAL, "%s: fp4_scale_centre %d out of range", who, d->fp4_scale_centre);
   return CACHALOT_OK;
 }
 
@@ -277,7 +262,7 @@ using namespace cachalot;
 
 extern "C" size_t cachalot_moe_decode_workspace_bytes(const cachalot_bank_desc* desc, int rows, int k) {
   if (!desc || rows <= 0 || k <= 0) return 0;
-  return (size_t)rows * k * desc->inter * sizeof(float);
+  return decode_mma_workspace_bytes(desc->hidden, desc->inter, rows, k);  // >= the simple kernels' rows*k*inter floats
 }
 
 extern "C" int cachalot_moe_decode(const void* bank, const cachalot_bank_desc* desc, const void* x_bf16,
@@ -290,13 +275,15 @@ extern "C" int cachalot_moe_decode(const void* bank, const cachalot_bank_desc* d
   if (!x_bf16 || !slots || !gate_w || !out) return fail(CACHALOT_EINVAL, "moe_decode: null pointer");
   if (rows < 0 || k <= 0 || k > 64) return fail(CACHALOT_EINVAL, "moe_decode: rows=%d k=%d out of range", rows, k);
   if ((long long)rows * k > 65535) return fail(CACHALOT_EINVAL, "moe_decode: rows*k=%lld exceeds 65535", (long long)rows * k);
-  if ((numerics & 0xff) > CACHALOT_NUMERICS_BF16_H32 || (numerics & ~0x3ff))
+  if ((numerics & 0xff) > CACHALOT_NUMERICS_BF16_H32 || (numerics & ~0x7ff))
     return fail(CACHALOT_EINVAL, "moe_decode: unknown numerics %d", numerics);
   if (out_dtype != CACHALOT_F32 && out_dtype != CACHALOT_BF16) return fail(CACHALOT_EINVAL, "moe_decode: out dtype must be f32 or bf16");
   if (rows == 0) return CACHALOT_OK;
   size_t need = cachalot_moe_decode_workspace_bytes(desc, rows, k);
   if (!workspace || workspace_bytes < need) return fail(CACHALOT_ESCRATCH, "moe_decode: workspace %zu < %zu bytes", workspace_bytes, need);
-  if (!aligned(workspace, 16) || !aligned(x_bf16, 2) || !aligned(out, 4)) return fail(CACHALOT_EALIGN, "moe_decode: misaligned buffer");
+  if (!aligned(workspace, 256) || !aligned(x_bf16, 16) || !aligned(out, 4)) return fail(CACHALOT_EALIGN, "moe_decode: workspace needs 256-byte, x 16-byte alignment");
+  if (!(numerics & CACHALOT_DECODE_SIMPLE) && decode_mma_supported(v, rows, k))
+    return launch_decode_mma(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, numerics, workspace, out, out_dtype, status, (cudaStream_t)stream);
   if (desc->format == CACHALOT_BANK_FP4)
     return launch_decode<CACHALOT_BANK_FP4>(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, numerics, (float*)workspace, out, out_dtype, status, (cudaStream_t)stream);
   return launch_decode<CACHALOT_BANK_AFFINE>(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, numerics, (float*)workspace, out, out_dtype, status, (cudaStream_t)stream);

@@ -168,14 +168,15 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
 def moe_forward(x: torch.Tensor, slot_ids: torch.Tensor, gate_weights: torch.Tensor, bank: SlabBank, *,
                 swiglu_limit: float = 10.0, numerics: str | None = None, out_dtype=torch.float32,
                 out: torch.Tensor | None = None, status: torch.Tensor | None = None,
-                workspace: torch.Tensor | None = None, phase: str | None = None) -> torch.Tensor:
+                workspace: torch.Tensor | None = None, phase: str | None = None, simple: bool = False) -> torch.Tensor:
     """Routed experts for `rows` tokens: x bf16 [rows,H], slot_ids int32 [rows,k] (bank slots, -1 =
     absent -> zero contribution), gate_weights float32 [rows,k] -> [rows,H].
 
     numerics "f32" keeps fp32 between the projections (the FP4 decode op,
     model/moe_fused_metal.py:189-233); "bf16" rounds g, u, h and each expert's output to bf16 (the
     affine op, model/expert_affine.py:65-81).  Default: by bank format.  `phase` ("gate_up" or
-    "down") runs only one of the two launches; it exists for per-kernel timing."""
+    "down") runs only one of the two launches; it exists for per-kernel timing.  `simple` selects
+    the one-warp-per-output kernels instead of the tensor-core ones (a cross-check, any shape)."""
     _need_cuda(x, slot_ids, gate_weights)
     if x.dim() != 2 or x.shape[1] != bank.hidden:
         raise ValueError(f"x must be [rows, {bank.hidden}], got {tuple(x.shape)}")
@@ -187,6 +188,8 @@ def moe_forward(x: torch.Tensor, slot_ids: torch.Tensor, gate_weights: torch.Ten
         numerics = "f32" if bank.fmt.kind == "fp4" else "bf16"
     num = {"f32": _lib.NUMERICS_F32, "bf16": _lib.NUMERICS_BF16, "bf16_h32": _lib.NUMERICS_BF16_H32}[numerics]
     num |= {None: 0, "gate_up": _lib.DECODE_ONLY_GATE_UP, "down": _lib.DECODE_ONLY_DOWN}[phase]
+    if simple:
+        num |= _lib.DECODE_SIMPLE
     xb = x.to(torch.bfloat16).contiguous()
     slot_ids = slot_ids.to(torch.int32).contiguous()
     gate_weights = gate_weights.to(torch.float32).contiguous()
@@ -194,9 +197,11 @@ def moe_forward(x: torch.Tensor, slot_ids: torch.Tensor, gate_weights: torch.Ten
     if out is None:
         out = torch.empty((rows, bank.hidden), dtype=out_dtype, device=x.device)
     need = lib.cachalot_moe_decode_workspace_bytes(bank.desc_ptr, rows, k)
-    ws = workspace if workspace is not None else _workspace(x.device, need)
+    ws = workspace if workspace is not None else _workspace(x.device, need + 256)
+    base = (ws.data_ptr() + 255) // 256 * 256
     check(lib.cachalot_moe_decode(_ptr(bank.slab), bank.desc_ptr, _ptr(xb), _ptr(slot_ids), _ptr(gate_weights), rows, k,
-                                  float(swiglu_limit), num, _ptr(ws), ws.numel(), _ptr(out), odt, _ptr(status), _stream()))
+                                  float(swiglu_limit), num, base, ws.numel() - (base - ws.data_ptr()), _ptr(out), odt,
+                                  _ptr(status), _stream()))
     return out
 
 

@@ -41,7 +41,8 @@ enum {
 /* bits of the device-side status word */
 enum {
   CACHALOT_STATUS_SLOT_RANGE = 1, /* a slot id >= n_slots was seen and treated as absent */
-  CACHALOT_STATUS_ID_RANGE = 2    /* an expert id outside [0, E) was seen and dropped */
+  CACHALOT_STATUS_ID_RANGE = 2,   /* an expert id outside [0, E) was seen and dropped */
+  CACHALOT_STATUS_SCALE_RANGE = 4 /* an FP4 block scale outside the window around fp4_scale_centre was clamped */
 };
 
 enum { CACHALOT_BANK_FP4 = 0, CACHALOT_BANK_AFFINE = 1 };
@@ -55,6 +56,9 @@ enum {
 };
 /* profiling aids, OR-ed into `numerics`: run only one of the two launches of cachalot_moe_decode */
 enum { CACHALOT_DECODE_ONLY_GATE_UP = 0x100, CACHALOT_DECODE_ONLY_DOWN = 0x200 };
+/* OR-ed into `numerics`: use the simple one-warp-per-output kernels (any shape; the cross-check of the
+ * tensor-core kernels, as the reference checks its fused kernels against the unfused loop) */
+enum { CACHALOT_DECODE_SIMPLE = 0x400 };
 enum { CACHALOT_ROUTER_SQRT_SOFTPLUS = 0, CACHALOT_ROUTER_SIGMOID = 1 };
 enum { CACHALOT_SCALE_E8M0 = 0, CACHALOT_SCALE_F32 = 1 };
 
@@ -81,7 +85,8 @@ typedef struct {
   int32_t bits;        /* affine: 2 (built); FP4: 4 */
   int32_t group;       /* affine: 128 or 64; FP4: 32 */
   int32_t scale_dtype; /* affine: CACHALOT_F16 or CACHALOT_BF16 */
-  int32_t reserved;
+  int32_t fp4_scale_centre; /* FP4: an E8M0 byte near the middle of the bank's scale range (0 = 121);
+                               scales must lie within [centre-14, centre+13], else CACHALOT_STATUS_SCALE_RANGE */
 } cachalot_bank_desc;
 
 CACHALOT_API const char* cachalot_last_error(void);

@@ -152,7 +152,9 @@ def test_affine_small_shapes_batch(group, dims):
 
 def test_decode_full_size_properties():
     """Properties at the benchmark's shapes that need no oracle: a zero gate weight removes an expert,
-    rows are independent, and a repeated call is bit-identical (fixed reduction order)."""
+    rows are independent (a row alone and in a batch agree to fp32 rounding: the batch shares each
+    expert's bytes between rows, which changes the operand prescale but not the math), and a
+    repeated call is bit-identical (fixed reduction order)."""
     import cachalot_b200 as cb
     g = torch.Generator(device="cuda").manual_seed(0)
     hidden, inter, n_slots, k = 4096, 2880, 12, 6
@@ -168,9 +170,59 @@ def test_decode_full_size_properties():
     b = cb.moe_forward(x, slots, w, bank)
     assert torch.equal(a, b) and bool(torch.isfinite(a).all())
     row3 = cb.moe_forward(x[3:4], slots[3:4], w[3:4], bank)
-    assert torch.equal(row3[0], a[3])
+    assert float((row3[0] - a[3]).abs().max()) <= 1e-5 * float(a[3].abs().max())
     w0 = w.clone()
     w0[:, 2] = 0
     s_drop = slots.clone()
     s_drop[:, 2] = -1
-    assert torch.allclose(cb.moe_forward(x, slots, w0, bank), cb.moe_forward(x, s_drop, w, bank), rtol=0, atol=0)
+    zero_w, dropped = cb.moe_forward(x, slots, w0, bank), cb.moe_forward(x, s_drop, w, bank)
+    assert float((zero_w - dropped).abs().max()) <= 1e-5 * float(dropped.abs().max())
+
+
+@pytest.mark.parametrize("kind,rows", [("fp4", 1), ("fp4", 5), ("fp4", 16), ("affine", 1), ("affine", 7), ("affine", 64)])
+def test_tensor_core_kernels_equal_simple_kernels(kind, rows):
+    """The tensor-core decode kernels against the one-warp-per-output kernels on the same bank and
+    routing, at the benchmark's shapes (the reference checks its fused kernels against the unfused
+    loop the same way); batches above one exercise the grouping of rows by expert."""
+    import cachalot_b200 as cb
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    hidden, inter, n_slots, k = 4096, 2880, 40, 6
+    fmt = cb.FP4_FORMAT if kind == "fp4" else cb.affine_format(hidden, inter)
+    bank = cb.SlabBank(fmt, hidden, inter, n_slots)
+    from bench import fill_bank
+    fill_bank(bank, g)
+    x = (torch.randn((rows, hidden), device="cuda", generator=g) * 2).to(torch.bfloat16)
+    slots = torch.stack([torch.randperm(n_slots, device="cuda", generator=g)[:k] for _ in range(rows)]).to(torch.int32)
+    if rows > 1:
+        slots[1, 3] = -1
+    w = torch.rand((rows, k), device="cuda", generator=g) * 0.3
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    fast = cb.moe_forward(x, slots, w, bank, status=status)
+    slow = cb.moe_forward(x, slots, w, bank, simple=True)
+    assert int(status.item()) == 0
+    scale = float(slow.abs().max())
+    assert float((fast - slow).abs().max()) / scale < (2e-3 if kind == "affine" else 2e-5)
+    again = cb.moe_forward(x, slots, w, bank)
+    assert torch.equal(fast, again)
+
+
+def test_fp4_scale_window_and_calibration():
+    import cachalot_b200 as cb
+    rng = np.random.default_rng(9)
+    hidden, inter = 256, 192
+    e = configs.fp4_expert(rng, hidden, inter)
+    for name in ("w1.scale", "w2.scale", "w3.scale"):
+        e[name] = rng.integers(90, 100, e[name].shape, dtype=np.uint8)       # 2**-37 .. 2**-28
+    bank = make_bank([e], cb.FP4_FORMAT, hidden, inter)
+    x = configs.round_bf16(rng.standard_normal((1, hidden)).astype(np.float32) * 1e6)
+    slots = torch.zeros((1, 1), dtype=torch.int32, device="cuda")
+    w = torch.ones((1, 1), device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cb.moe_forward(bf16_tensor(x), slots, w, bank, swiglu_limit=0.0, status=status)
+    assert int(status.item()) & 4                                             # default centre 121 does not cover them
+    assert 90 <= bank.calibrate_scale_centre() <= 100
+    status.zero_()
+    got = cb.moe_forward(bf16_tensor(x), slots, w, bank, swiglu_limit=0.0, status=status).cpu().numpy()
+    assert int(status.item()) == 0
+    want = _fp4_expert_out(x, e, None, 0.0)
+    assert max_rel(got, want) < TOL
