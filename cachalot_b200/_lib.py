@@ -8,7 +8,9 @@ import ctypes as C
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
-LIB_PATH = _PKG / "libcachalot_b200.so"
+import os
+
+LIB_PATH = Path(os.environ.get("CACHALOT_B200_LIB", _PKG / "libcachalot_b200.so"))  # override: development builds
 
 OK, EINVAL, EALIGN, EUNSUPPORTED, ECUDA, ESCRATCH = 0, -1, -2, -3, -4, -5
 BANK_FP4, BANK_AFFINE = 0, 1

@@ -15,7 +15,7 @@ from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
-LIB = PKG / "libcachalot_b200.so"
+LIB = Path(os.environ.get("CACHALOT_B200_LIB", PKG / "libcachalot_b200.so"))
 OBJ_DIR = PKG / "csrc" / "build"
 
 NVCC_FLAGS = [
@@ -54,6 +54,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     nvcc = _nvcc()
     OBJ_DIR.mkdir(exist_ok=True)
     extra = ["-Xptxas", "-v"] if verbose else []
+    extra += os.environ.get("CACHALOT_NVCC_EXTRA", "").split()  # development switches (-D...)
 
     def compile_one(src: Path) -> Path:
         obj = OBJ_DIR / (src.stem + ".o")

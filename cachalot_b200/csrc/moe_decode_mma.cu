@@ -59,8 +59,9 @@ __device__ __forceinline__ void fp4_word(uint32_t w, uint32_t mul, uint32_t (&h)
 
 // 2-bit: sixteen codes of a word -> eight f16x2 (field f in the low half, field f+8 in the high
 // half), value 1024 + q * 4**pos with pos = {2,3,2,3,4,2,3,4}[f]
-__device__ __forceinline__ void q2_word(uint32_t w, uint32_t (&h)[8]) {
-  const uint32_t M = 0x64006400u;
+// M = 0x64006400 arrives through a kernel parameter so that it lives in a register: (x & imm) | reg is
+// one LOP3, whereas with two immediates each field would cost two instructions.
+__device__ __forceinline__ void q2_word(uint32_t w, uint32_t M, uint32_t (&h)[8]) {
   const uint32_t s1 = w << 4, s2 = w >> 6;
   h[0] = (s1 & 0x00300030u) | M;
   h[1] = (s1 & 0x00C000C0u) | M;
@@ -105,12 +106,13 @@ __device__ __forceinline__ Wv<WORDS> ld_words(const uint8_t* p) {
   return r;
 }
 
-// One chunk of one weight matrix for rows g and g+8 of the tile: T += A(16 x KCH) * B(KCH x 8).
+// One chunk of one weight matrix for rows g and g+8 of the tile: D = C + A(16 x KCH) * B(KCH x 8).
 // xq: the lane's B operand (XQ x uint4).  FP4: mula/mulb are the f16x2 scale multipliers.
 template <int FMT, int KCH>
-__device__ __forceinline__ void chunk_mma(float (&T)[4], const Wv<Geo<FMT, KCH>::WORDS>& ra,
+__device__ __forceinline__ void chunk_mma(float (&D)[4], const float (&C)[4], const Wv<Geo<FMT, KCH>::WORDS>& ra,
                                           const Wv<Geo<FMT, KCH>::WORDS>& rb, uint32_t mula, uint32_t mulb,
                                           const uint4 (&xq)[Geo<FMT, KCH>::XQ]) {
+  // affine: mula carries the 0x64006400 magic
   using G = Geo<FMT, KCH>;
 #pragma unroll
   for (int wd = 0; wd < G::WORDS; ++wd) {
@@ -119,28 +121,25 @@ __device__ __forceinline__ void chunk_mma(float (&T)[4], const Wv<Geo<FMT, KCH>:
       fp4_word(ra.w[wd], mula, ha);
       fp4_word(rb.w[wd], mulb, hb);
       const uint4 q = xq[wd];  // 8 activations = this word's 8 codes
-      mma16816(T, ha[0], hb[0], ha[1], hb[1], q.x, q.y, T);
-      mma16816(T, ha[2], hb[2], ha[3], hb[3], q.z, q.w, T);
+      if (wd == 0)
+        mma16816(D, ha[0], hb[0], ha[1], hb[1], q.x, q.y, C);
+      else
+        mma16816(D, ha[0], hb[0], ha[1], hb[1], q.x, q.y, D);
+      mma16816(D, ha[2], hb[2], ha[3], hb[3], q.z, q.w, D);
     } else {
       uint32_t ha[8], hb[8];
-      q2_word(ra.w[wd], ha);
-      q2_word(rb.w[wd], hb);
+      q2_word(ra.w[wd], mula, ha);
+      q2_word(rb.w[wd], mula, hb);
       const uint4 q0 = xq[2 * wd], q1 = xq[2 * wd + 1];  // 16 activations, permuted and pre-divided
-      mma16816(T, ha[0], hb[0], ha[1], hb[1], q0.x, q0.y, T);
-      mma16816(T, ha[2], hb[2], ha[3], hb[3], q0.z, q0.w, T);
-      mma16816(T, ha[4], hb[4], ha[5], hb[5], q1.x, q1.y, T);
-      mma16816(T, ha[6], hb[6], ha[7], hb[7], q1.z, q1.w, T);
+      if (wd == 0)
+        mma16816(D, ha[0], hb[0], ha[1], hb[1], q0.x, q0.y, C);
+      else
+        mma16816(D, ha[0], hb[0], ha[1], hb[1], q0.x, q0.y, D);
+      mma16816(D, ha[2], hb[2], ha[3], hb[3], q0.z, q0.w, D);
+      mma16816(D, ha[4], hb[4], ha[5], hb[5], q1.x, q1.y, D);
+      mma16816(D, ha[6], hb[6], ha[7], hb[7], q1.z, q1.w, D);
     }
   }
-}
-
-__device__ __forceinline__ uint32_t fp4_scale_mul(uint32_t sbyte, int centre, int& flag) {
-  int e = (int)sbyte - centre + 15;
-  if (e < 1 || e > 28) {  // 6 * 2**13 is the largest product f16 holds
-    flag = 1;
-    e = min(max(e, 1), 28);
-  }
-  return ((uint32_t)e << 10) * 0x00010001u;
 }
 
 // ---- activation staging --------------------------------------------------------------------
@@ -154,7 +153,8 @@ __device__ __forceinline__ uint32_t fp4_scale_mul(uint32_t sbyte, int centre, in
 // load16(row, k, float (&v)[16]) reads 16 consecutive source values.  Contains __syncthreads.
 template <int FMT, int KCH, int NWARPS, typename Load16>
 __device__ __forceinline__ void stage_rows(uint8_t* hi, uint8_t* lo, int xrow, int ncol, int K, Load16 load16,
-                                           float* inv_p, float* xs, float* xj, int nch, float* wmax /*[MAX_COLS*NWARPS]*/) {
+                                           float* inv_p, float* xsj /* (xs, -1024 xj) per column and chunk */, int nch,
+                                           float* wmax /*[MAX_COLS*NWARPS]*/) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nreg = K / 16;
   const int wpc = NWARPS / ncol;                 // warps per row (ncol <= MAX_COLS <= NWARPS)
@@ -252,8 +252,7 @@ __device__ __forceinline__ void stage_rows(uint8_t* hi, uint8_t* lo, int xrow, i
           jsum += __shfl_xor_sync(0xffffffffu, jsum, o);
         }
         if (valid && (lane & (KCH / 16 - 1)) == 0) {
-          xs[c * nch + reg / (KCH / 16)] = sum;
-          xj[c * nch + reg / (KCH / 16)] = jsum;
+          reinterpret_cast<float2*>(xsj)[c * nch + reg / (KCH / 16)] = make_float2(sum, -1024.f * jsum);
         }
       }
     }
@@ -316,18 +315,28 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // the loop.  A CTA takes a contiguous range of units, stages the activation rows of a group once
 // (skipped when the same single row is already staged, as in batch 1 where every group shares the
 // token) and hands tiles to its warps round-robin.  A warp issues the first PF chunks of its unit
-// before the staging barrier so that the weight stream starts at once.
+// and the copy of the unit's scales before the staging barrier, so the weight stream starts at once.
 
 constexpr int ST_WARPS = 8;
 
 template <int FMT, int KCH>
 struct Pf {  // chunks in flight per warp
-  static constexpr int N = (FMT == CACHALOT_BANK_FP4 ? 512 : 1024) / KCH;
+#ifndef CB_PF_DIV
+#define CB_PF_DIV 1
+#endif
+#ifndef CB_MINB
+#define CB_MINB 2
+#endif
+  static constexpr int N = (FMT == CACHALOT_BANK_FP4 ? 512 : 1024) / KCH / CB_PF_DIV;
 };
 
 struct StSmem {
-  int xrow, sc_warp, sc_half;  // bytes per operand row; per-warp scale area; affine: bytes of the scale half of it
-  int off_hi, off_lo, off_invp, off_xs, off_xj, off_wmax, off_sc, total;
+  int xrow;     // bytes per operand row
+  int n_raw;    // affine: raw scale halves per warp (the raw biases follow at raw_half); FP4: raw scale bytes
+  int raw_half; // affine: bytes of the raw scale array
+  int sc_warp;  // bytes of a warp's scale area: raw copy, then converted values
+  int off_cv;   // offset of the converted values inside the warp area
+  int off_hi, off_lo, off_invp, off_xsj, off_wmax, off_sc, total;
 };
 __host__ __device__ inline StSmem st_layout(int fmt, int K, int kch, int cols, bool hilo) {
   StSmem s;
@@ -336,17 +345,21 @@ __host__ __device__ inline StSmem st_layout(int fmt, int K, int kch, int cols, b
   s.off_hi = p, p += cols * s.xrow;
   s.off_lo = p, p += hilo ? cols * s.xrow : 0;
   s.off_invp = p, p += MAX_COLS * 4;
+  p = (p + 15) & ~15;
   const int nch = K / kch;
-  s.off_xs = p, p += (fmt == CACHALOT_BANK_AFFINE ? cols * nch * 4 : 0);
-  s.off_xj = p, p += (fmt == CACHALOT_BANK_AFFINE ? cols * nch * 4 : 0);
+  s.off_xsj = p, p += (fmt == CACHALOT_BANK_AFFINE ? cols * nch * 8 : 0);  // float2 (xs, -1024 xj) per column and chunk
   s.off_wmax = p, p += MAX_COLS * ST_WARPS * 4;
   p = (p + 15) & ~15;
   if (fmt == CACHALOT_BANK_FP4) {
-    s.sc_half = 0;
-    s.sc_warp = 16 * (K / 32) + 32;
+    s.n_raw = 16 * (K / 32);
+    s.raw_half = 0;
+    s.off_cv = (s.n_raw + 15) & ~15;
+    s.sc_warp = s.off_cv + s.n_raw * 2;  // one f16 multiplier per (tile row, block)
   } else {
-    s.sc_half = ((16 * K / 128 + 8) * 2 + 31) & ~15;  // up to two runs of 8 rows, each 16-byte aligned
-    s.sc_warp = 2 * s.sc_half;
+    s.n_raw = 16 * K / 128 + 16;  // two runs of 8 rows, or one of 16, each 16-byte aligned with a spare group
+    s.raw_half = (s.n_raw * 2 + 15) & ~15;
+    s.off_cv = 2 * s.raw_half;
+    s.sc_warp = s.off_cv + 16 * nch * 8;  // float2 (scale, bias) per (tile row, chunk)
   }
   s.sc_warp = (s.sc_warp + 15) & ~15;
   s.off_sc = p, p += ST_WARPS * s.sc_warp;
@@ -354,15 +367,17 @@ __host__ __device__ inline StSmem st_layout(int fmt, int K, int kch, int cols, b
   return s;
 }
 
-template <int FMT, int KCH, int PHASE, bool HILO, typename OutT>
-__global__ void __launch_bounds__(ST_WARPS * 32, 2)
+template <int FMT, int KCH, int PHASE, bool HILO, bool ONECOL, typename OutT>
+__global__ void __launch_bounds__(ST_WARPS * 32, CB_MINB)
 stream_kernel(BankView bank, const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ slots,
               const float* __restrict__ gate_w, Plan plan, int R, int k, int cols, float limit, int numerics,
               float* __restrict__ hidden, float* __restrict__ ybuf, int* __restrict__ counters, OutT* __restrict__ out,
-              int* __restrict__ status) {
+              int* __restrict__ status, uint32_t magic /* 0x64006400, see q2_word */) {
   using G = Geo<FMT, KCH>;
   constexpr int PF = Pf<FMT, KCH>::N;
   constexpr int TILE = PHASE == 0 ? 8 : 16;  // outputs per unit
+  constexpr int CHUNK_BYTES = KCH / (FMT == CACHALOT_BANK_FP4 ? 2 : 4);
+  constexpr int XSTEP = (KCH / 32) * SEG_BYTES;  // operand bytes per chunk
   extern __shared__ __align__(16) uint8_t smem[];
   const int H = bank.hidden, I = bank.inter;
   const int K = PHASE == 0 ? H : I;   // reduction length
@@ -379,13 +394,11 @@ stream_kernel(BankView bank, const __nv_bfloat16* __restrict__ x, const int32_t*
   if (u_end <= u_begin) return;
   const StSmem L = st_layout(FMT, K, KCH, cols, HILO);
   float* invp = reinterpret_cast<float*>(smem + L.off_invp);
-  float* xs = reinterpret_cast<float*>(smem + L.off_xs);
-  float* xj = reinterpret_cast<float*>(smem + L.off_xj);
+  float2* xsj = reinterpret_cast<float2*>(smem + L.off_xsj);
   float* wmax = reinterpret_cast<float*>(smem + L.off_wmax);
   uint8_t* my_sc = smem + L.off_sc + warp * L.sc_warp;
   const int nch = K / KCH;
   const int row_bytes = FMT == CACHALOT_BANK_FP4 ? K / 2 : K / 4;
-  const int chunk_bytes = KCH / (FMT == CACHALOT_BANK_FP4 ? 2 : 4);
   // tensors of the record: weight / scale (/ bias) of the A rows 0..7 and 8..15
   const int tA = PHASE == 0 ? 0 : (FMT == CACHALOT_BANK_FP4 ? 2 : 3);
   const int tB = PHASE == 0 ? (FMT == CACHALOT_BANK_FP4 ? 4 : 6) : tA;
@@ -414,26 +427,24 @@ stream_kernel(BankView bank, const __nv_bfloat16* __restrict__ x, const int32_t*
       const int src0 = PHASE == 0 ? r0 / k : r0;  // source row of column 0 (token for gate/up, routed row for down)
 
       Wv<G::WORDS> bufa[PF], bufb[PF];
-      size_t rowa = 0, rowb = 0;
+      const uint8_t* pa = nullptr;
+      const uint8_t* pb = nullptr;
+      int n_a = 0;         // affine: pairs in the first run (the second run starts there)
+      long long gf = 0;    // affine: first flattened group of the tile
       int tile = tile_lo + warp;
-      auto row_offsets = [&](int tl) {
-        if constexpr (PHASE == 0) {
-          rowa = rowb = (size_t)(tl * 8 + g) * row_bytes;
-        } else {
-          rowa = (size_t)(tl * 16 + g) * row_bytes, rowb = (size_t)(tl * 16 + g + 8) * row_bytes;
-        }
-      };
-      auto load = [&](int c, Wv<G::WORDS>& a, Wv<G::WORDS>& b) {
-        const size_t o = (size_t)c * chunk_bytes + lane_off;
-        a = ld_words<G::WORDS>(WA + rowa + o);
-        b = ld_words<G::WORDS>(WB + rowb + o);
-      };
-      // issue: the first PF chunks and the tile's scales
+      // issue: the first PF chunks of the unit, and the copy of its raw scales
       auto issue = [&](int tl) {
-        row_offsets(tl);
+        const long long ra = PHASE == 0 ? (long long)tl * 8 + g : (long long)tl * 16 + g;
+        const long long rb = PHASE == 0 ? ra : ra + 8;
+        pa = WA + ra * row_bytes + lane_off;
+        pb = WB + rb * row_bytes + lane_off;
 #pragma unroll
-        for (int j = 0; j < PF; ++j)
-          if (j < nch) load(j, bufa[j], bufb[j]);
+        for (int j = 0; j < PF; ++j) {
+          if (j < nch) {
+            bufa[j] = ld_words<G::WORDS>(pa + j * CHUNK_BYTES);
+            bufb[j] = ld_words<G::WORDS>(pb + j * CHUNK_BYTES);
+          }
+        }
         __syncwarp();  // the previous unit's scale reads are done
         if constexpr (FMT == CACHALOT_BANK_FP4) {
           const int per_row = K / 32;
@@ -444,18 +455,18 @@ stream_kernel(BankView bank, const __nv_bfloat16* __restrict__ x, const int32_t*
             warp_copy_async(my_sc, rec + bank.off[tA + 1] + (size_t)tl * 16 * per_row, 16 * per_row, lane);
           }
         } else {
-          // groups of 128 over the flattened matrix: rows [row0, row0 + n) touch groups [lo, hi]
-          auto run = [&](int tensor, long long row0, int nrows, int dst_half) {
-            const long long glo = (row0 * K) >> 7, ghi = (((row0 + nrows) * (long long)K - 1) >> 7);
-            const int n = (int)(ghi - glo + 1);
-            warp_copy_async(my_sc + dst_half, rec + bank.off[tensor + 1] + glo * 2, n * 2, lane);
-            warp_copy_async(my_sc + L.sc_half + dst_half, rec + bank.off[tensor + 2] + glo * 2, n * 2, lane);
-          };
+          // groups of 128 over the flattened matrix: rows [row0, row0 + n) touch groups [glo, ghi]
+          const long long row0 = (long long)tl * TILE;
+          const int nrows = PHASE == 0 ? 8 : 16;
+          const long long glo = (row0 * K) >> 7, ghi = ((row0 + nrows) * (long long)K - 1) >> 7;
+          gf = glo;
+          n_a = (int)(ghi - glo + 1);
+          warp_copy_async(my_sc, rec + bank.off[tA + 1] + glo * 2, n_a * 2, lane);
+          warp_copy_async(my_sc + L.raw_half, rec + bank.off[tA + 2] + glo * 2, n_a * 2, lane);
           if constexpr (PHASE == 0) {
-            run(tA, (long long)tl * 8, 8, 0);
-            run(tB, (long long)tl * 8, 8, L.sc_half / 2 & ~15);
-          } else {
-            run(tA, (long long)tl * 16, 16, 0);
+            const int o2 = (n_a * 2 + 15) & ~15;
+            warp_copy_async(my_sc + o2, rec + bank.off[tB + 1] + glo * 2, n_a * 2, lane);
+            warp_copy_async(my_sc + L.raw_half + o2, rec + bank.off[tB + 2] + glo * 2, n_a * 2, lane);
           }
         }
       };
@@ -464,6 +475,7 @@ stream_kernel(BankView bank, const __nv_bfloat16* __restrict__ x, const int32_t*
 
       if (!absent && !(ncol == 1 && staged_row == src0)) {
         __syncthreads();  // every warp is done with the previous operand rows
+        float* xs_tmp = reinterpret_cast<float*>(xsj);  // filled as [col][chunk] pairs below
         if constexpr (PHASE == 0) {
           stage_rows<FMT, KCH, ST_WARPS>(
               smem + L.off_hi, nullptr, L.xrow, ncol, K,
@@ -471,7 +483,7 @@ stream_kernel(BankView bank, const __nv_bfloat16* __restrict__ x, const int32_t*
                 const int r = plan.order ? plan.order[tc + c] : tc + c;
                 load16_bf16(x + (size_t)(r / k) * K + kk, v);
               },
-              invp, xs, xj, nch, wmax);
+              invp, xs_tmp, nch, wmax);
         } else {
           stage_rows<FMT, KCH, ST_WARPS>(
               smem + L.off_hi, HILO ? smem + L.off_lo : nullptr, L.xrow, ncol, K,
@@ -479,7 +491,7 @@ stream_kernel(BankView bank, const __nv_bfloat16* __restrict__ x, const int32_t*
                 const int r = plan.order ? plan.order[tc + c] : tc + c;
                 load16_f32(hidden + (size_t)r * K + kk, v);
               },
-              invp, xs, xj, nch, wmax);
+              invp, xs_tmp, nch, wmax);
         }
         staged_row = ncol == 1 ? src0 : -1;
       }
@@ -503,67 +515,99 @@ stream_kernel(BankView bank, const __nv_bfloat16* __restrict__ x, const int32_t*
           have = false;
           cp_async_wait_all();
           __syncwarp();
-          const uint8_t* xrow = smem + L.off_hi + g * L.xrow;
-          // affine: first group of each 8/16-row run, to turn a flattened group index into an offset
-          long long gfa = 0, gfb = 0;
-          int sc_b = 0;
-          if constexpr (FMT == CACHALOT_BANK_AFFINE) {
-            if constexpr (PHASE == 0) {
-              gfa = gfb = ((long long)tile * 8 * K) >> 7;
-              sc_b = L.sc_half / 2 & ~15;
-            } else {
-              gfa = gfb = ((long long)tile * 16 * K) >> 7;
+          // convert the raw scales once per unit into one entry per (tile row, chunk)
+          if constexpr (FMT == CACHALOT_BANK_FP4) {
+            const uint32_t* raw = reinterpret_cast<const uint32_t*>(my_sc);
+            uint2* cvw = reinterpret_cast<uint2*>(my_sc + L.off_cv);
+            for (int i = lane; i < L.n_raw / 4; i += 32) {
+              const uint32_t w = raw[i];
+              uint32_t m[4];
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                int e = (int)((w >> (8 * b)) & 0xffu) - bank.scale_centre + 15;
+                if (e < 1 || e > 28) range_flag = 1, e = min(max(e, 1), 28);  // 6 * 2**13 is the largest product f16 holds
+                m[b] = (uint32_t)e << 10;
+              }
+              cvw[i] = make_uint2(m[0] | (m[1] << 16), m[2] | (m[3] << 16));
+            }
+          } else {
+            const uint16_t* S = reinterpret_cast<const uint16_t*>(my_sc);
+            const uint16_t* Bv = reinterpret_cast<const uint16_t*>(my_sc + L.raw_half);
+            float2* cvw = reinterpret_cast<float2*>(my_sc + L.off_cv);
+            const bool f16s = bank.scale_dtype == CACHALOT_F16;
+            const int o2 = ((n_a * 2 + 15) & ~15) / 2;  // the second run (up rows) in the raw arrays
+            const long long row0 = (long long)tile * TILE;
+            for (int i = lane; i < 16 * nch; i += 32) {
+              const int lr = i / nch, c = i - lr * nch;  // tile row 0..15 (PHASE 0: 0..7 gate, 8..15 up), chunk
+              const long long row = PHASE == 0 ? row0 + (lr & 7) : row0 + lr;
+              const int src = (int)(((row * K + (long long)c * KCH) >> 7) - gf) + ((PHASE == 0 && lr >= 8) ? o2 : 0);
+              const uint16_t sv = S[src], bv = Bv[src];
+              float2 v;
+              if (f16s) {
+                v.x = __half2float(__ushort_as_half(sv)), v.y = __half2float(__ushort_as_half(bv));
+              } else {
+                v.x = __uint_as_float((uint32_t)sv << 16), v.y = __uint_as_float((uint32_t)bv << 16);
+              }
+              cvw[i] = v;
             }
           }
-          const long long ea = (long long)(PHASE == 0 ? tile * 8 + g : tile * 16 + g) * K;
-          const long long eb = (long long)(PHASE == 0 ? tile * 8 + g : tile * 16 + g + 8) * K;
-          auto compute = [&](int c, const Wv<G::WORDS>& wa, const Wv<G::WORDS>& wb) {
-            uint4 xq[G::XQ], xl[G::XQ];
-#pragma unroll
-            for (int q = 0; q < G::XQ; ++q) {
-              const int o = xoff(c * KCH + t * G::LANE_K) + q * 16;
-              xq[q] = g < ncol ? *reinterpret_cast<const uint4*>(xrow + o) : make_uint4(0, 0, 0, 0);
-              if constexpr (HILO)
-                xl[q] = g < ncol ? *reinterpret_cast<const uint4*>(xrow + (L.off_lo - L.off_hi) + o) : make_uint4(0, 0, 0, 0);
-            }
-            if constexpr (FMT == CACHALOT_BANK_FP4) {
-              const int per_row = K / 32;
-              const int sb = (c * KCH + t * G::LANE_K) >> 5;
-              const uint32_t ma = fp4_scale_mul(my_sc[g * per_row + sb], bank.scale_centre, range_flag);
-              const uint32_t mb = fp4_scale_mul(my_sc[(g + 8) * per_row + sb], bank.scale_centre, range_flag);
-              chunk_mma<FMT, KCH>(acc, wa, wb, ma, mb, xq);
-              if constexpr (HILO) chunk_mma<FMT, KCH>(acc, wa, wb, ma, mb, xl);
-            } else {
-              float T[4] = {0.f, 0.f, 0.f, 0.f};
-              chunk_mma<FMT, KCH>(T, wa, wb, 0, 0, xq);
-              const int ia = (int)(((ea + (long long)c * KCH) >> 7) - gfa), ib = (int)(((eb + (long long)c * KCH) >> 7) - gfb);
-              const uint16_t* S = reinterpret_cast<const uint16_t*>(my_sc);
-              const uint16_t* Bv = reinterpret_cast<const uint16_t*>(my_sc + L.sc_half);
-              const uint32_t pa = (uint32_t)S[ia] | ((uint32_t)Bv[ia] << 16);
-              const uint32_t pb = (uint32_t)S[sc_b / 2 + ib] | ((uint32_t)Bv[sc_b / 2 + ib] << 16);
-              uint32_t va = pa, vb = pb;
-              const bool f16s = bank.scale_dtype == CACHALOT_F16;
-              const float2 sa = f16s ? __half22float2(*reinterpret_cast<__half2*>(&va)) : __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&va));
-              const float2 sb = f16s ? __half22float2(*reinterpret_cast<__half2*>(&vb)) : __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&vb));
-              const int c0 = 2 * t, c1 = 2 * t + 1;
-              const float xs0 = c0 < ncol ? xs[c0 * nch + c] : 0.f, xs1 = c1 < ncol ? xs[c1 * nch + c] : 0.f;
-              const float xj0 = c0 < ncol ? xj[c0 * nch + c] : 0.f, xj1 = c1 < ncol ? xj[c1 * nch + c] : 0.f;
-              acc[0] += sa.x * (T[0] - 1024.f * xj0) + sa.y * xs0;
-              acc[1] += sa.x * (T[1] - 1024.f * xj1) + sa.y * xs1;
-              acc[2] += sb.x * (T[2] - 1024.f * xj0) + sb.y * xs0;
-              acc[3] += sb.x * (T[3] - 1024.f * xj1) + sb.y * xs1;
-            }
-          };
+          __syncwarp();
+
+          // Per-lane pointers of the chunk loop; every address inside it is pointer + constant.
+          // Operand columns at or beyond ncol are never stored and columns do not mix in the MMA, so
+          // their lanes simply read the last valid row.
+          const int brow = min(g, ncol - 1);
+          const uint8_t* xp = smem + L.off_hi + brow * L.xrow + xoff(t * G::LANE_K);
+          const float2* cva = reinterpret_cast<const float2*>(my_sc + L.off_cv) + g * nch;
+          const float2* cvb = cva + 8 * nch;
+          const float2* z0p = xsj + min(2 * t, ncol - 1) * nch;
+          const float2* z1p = xsj + min(2 * t + 1, ncol - 1) * nch;
+          const uint16_t* mula_p = reinterpret_cast<const uint16_t*>(my_sc + L.off_cv) + g * (K / 32) + ((t * G::LANE_K) >> 5);
+          const uint16_t* mulb_p = mula_p + 8 * (K / 32);
+          const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
+
           for (int c0 = 0; c0 < nch; c0 += PF) {
+            pa += PF * CHUNK_BYTES, pb += PF * CHUNK_BYTES;  // now the addresses of chunk c0 + PF
 #pragma unroll
             for (int j = 0; j < PF; ++j) {
-              const int c = c0 + j;
-              if (c < nch) {
-                const Wv<G::WORDS> wa = bufa[j], wb = bufb[j];
-                if (c + PF < nch) load(c + PF, bufa[j], bufb[j]);
-                compute(c, wa, wb);
+              if (c0 + j < nch) {
+                uint4 xq[G::XQ];
+#pragma unroll
+                for (int q = 0; q < G::XQ; ++q) xq[q] = *reinterpret_cast<const uint4*>(xp + j * XSTEP + q * 16);
+                if constexpr (FMT == CACHALOT_BANK_FP4) {
+                  const uint32_t ma = (uint32_t)mula_p[j * (KCH / 32)] * 0x00010001u;
+                  const uint32_t mb = (uint32_t)mulb_p[j * (KCH / 32)] * 0x00010001u;
+                  chunk_mma<FMT, KCH>(acc, acc, bufa[j], bufb[j], ma, mb, xq);
+                  if constexpr (HILO) {
+                    uint4 xl[G::XQ];
+#pragma unroll
+                    for (int q = 0; q < G::XQ; ++q)
+                      xl[q] = *reinterpret_cast<const uint4*>(xp + (L.off_lo - L.off_hi) + j * XSTEP + q * 16);
+                    chunk_mma<FMT, KCH>(acc, acc, bufa[j], bufb[j], ma, mb, xl);
+                  }
+                } else {
+                  float T[4];
+                  chunk_mma<FMT, KCH>(T, zero4, bufa[j], bufb[j], magic, 0, xq);
+                  const float2 sa = cva[j], sb = cvb[j];
+                  const float2 z0 = z0p[j];
+                  acc[0] = fmaf(sa.x, T[0] + z0.y, fmaf(sa.y, z0.x, acc[0]));
+                  acc[2] = fmaf(sb.x, T[2] + z0.y, fmaf(sb.y, z0.x, acc[2]));
+                  if constexpr (!ONECOL) {
+                    const float2 z1 = z1p[j];
+                    acc[1] = fmaf(sa.x, T[1] + z1.y, fmaf(sa.y, z1.x, acc[1]));
+                    acc[3] = fmaf(sb.x, T[3] + z1.y, fmaf(sb.y, z1.x, acc[3]));
+                  }
+                }
+                // the words of chunk c0 + j are consumed: refill the slot with chunk c0 + j + PF
+                if (c0 + j + PF < nch) {
+                  bufa[j] = ld_words<G::WORDS>(pa + j * CHUNK_BYTES);
+                  bufb[j] = ld_words<G::WORDS>(pb + j * CHUNK_BYTES);
+                }
               }
             }
+            xp += PF * XSTEP;
+            cva += PF, cvb += PF, z0p += PF, z1p += PF;
+            mula_p += PF * (KCH / 32), mulb_p += PF * (KCH / 32);
           }
         }
         // epilogue: this lane holds rows g, g+8 x columns 2t, 2t+1
@@ -572,7 +616,7 @@ stream_kernel(BankView bank, const __nv_bfloat16* __restrict__ x, const int32_t*
         if constexpr (PHASE == 0) {
           if (!absent) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
+            for (int e = 0; e < (ONECOL ? 1 : 2); ++e) {
               const int col = 2 * t + e;
               if (col < ncol) {
                 const float post = invp[col] * post_fmt;
@@ -590,7 +634,7 @@ stream_kernel(BankView bank, const __nv_bfloat16* __restrict__ x, const int32_t*
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int col = 2 * t + (e & 1), row = g + (e >> 1) * 8;
-            if (col < ncol) {
+            if (col < ncol && !(ONECOL && (e & 1))) {
               float y = absent ? 0.f : acc[e] * invp[col] * post_fmt;
               if (numerics != CACHALOT_NUMERICS_F32) y = bf16_round(y);
               const int r = plan.order ? plan.order[tc + col] : tc + col;
@@ -731,12 +775,16 @@ static int launch_fmt(const BankView& v, const void* x, const int32_t* slots, co
   };
 #define CACHALOT_ST(KCHV, PH, HL, OT, KK)                                                                              \
   do {                                                                                                                \
-    auto kern = stream_kernel<FMT, KCHV, PH, HL, OT>;                                                                 \
+    if (cols == 1) CACHALOT_ST1(KCHV, PH, HL, true, OT, KK); else CACHALOT_ST1(KCHV, PH, HL, false, OT, KK);           \
+  } while (0)
+#define CACHALOT_ST1(KCHV, PH, HL, OC, OT, KK)                                                                         \
+  do {                                                                                                                \
+    auto kern = stream_kernel<FMT, KCHV, PH, HL, OC, OT>;                                                             \
     const StSmem L = st_layout(FMT, KK, KCHV, cols, HL);                                                              \
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);                              \
     kern<<<grid_for((long long)R * ((PH) == 0 ? I / 8 : H / 16)), ST_WARPS * 32, L.total, stream>>>(                  \
         v, (const __nv_bfloat16*)x, slots, gate_w, plan, R, k, cols, limit, numerics, hidden, ybuf, counters,          \
-        (OT*)out, status);                                                                                            \
+        (OT*)out, status, 0x64006400u);                                                                                          \
   } while (0)
   int rc = CACHALOT_OK;
   if (do_gate_up) {
@@ -759,6 +807,7 @@ static int launch_fmt(const BankView& v, const void* x, const int32_t* slots, co
     else { if (hilo) CACHALOT_ST(64, 1, true, float, I); else CACHALOT_ST(64, 1, false, float, I); }
   }
 #undef CACHALOT_ST
+#undef CACHALOT_ST1
   return check_launch("moe_decode down (mma)");
 }
 
