@@ -5,6 +5,8 @@
 // Weights are read as 16-byte chunks straight from the slot record (FP4: 32 codes + one E8M0
 // byte; 2-bit affine: 64 codes, scale/bias per group), activations sit in shared memory in a
 // chunk-transposed order so that a warp's lanes hit distinct banks.
+#include <mutex>
+
 #include "kernels.cuh"
 
 namespace cachalot {
@@ -360,4 +362,58 @@ extern "C" int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc* 
   if (desc->format == CACHALOT_BANK_FP4)
     return launch_decode<CACHALOT_BANK_FP4>(v, x_in, slots, gate_w, tokens, k, swiglu_limit, num, hidden, out, CACHALOT_F32, status, s, mxfp4_act != 0);
   return launch_decode<CACHALOT_BANK_AFFINE>(v, x_in, slots, gate_w, tokens, k, swiglu_limit, num, hidden, out, CACHALOT_F32, status, s, mxfp4_act != 0);
+}
+
+// ---- decode with built-in scratch (no allocation anywhere) ------------------------------------
+
+namespace cachalot {
+namespace {
+
+constexpr size_t STATIC_SCRATCH_BYTES = (size_t)4 << 20;
+// Scratch of cachalot_moe_decode_static.  Every GPU that loads the library carries these 4 MiB
+// until the process exits.  In host code this name is only a handle for the runtime's symbol
+// table; the device address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char static_scratch[STATIC_SCRATCH_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+void* static_scratch_addr[MAX_DEVICES];  // per device ordinal; null until that device's first call
+std::mutex static_scratch_mu;
+
+}  // namespace
+}  // namespace cachalot
+
+extern "C" size_t cachalot_moe_decode_static_scratch_bytes(void) { return STATIC_SCRATCH_BYTES; }
+
+extern "C" int cachalot_moe_decode_static(const void* bank, const cachalot_bank_desc* desc, const void* x_bf16,
+                                          const int32_t* slots, const float* gate_w, int rows, int k,
+                                          float swiglu_limit, int numerics, void* out, int out_dtype, int* status,
+                                          cachalot_stream_t stream) {
+  if (!desc) return fail(CACHALOT_EINVAL, "moe_decode_static: null bank descriptor");
+  if (rows > 0 && k > 0) {
+    const size_t need = cachalot_moe_decode_workspace_bytes(desc, rows, k);
+    if (need > STATIC_SCRATCH_BYTES)
+      return fail(CACHALOT_ESCRATCH,
+                  "moe_decode_static: rows=%d k=%d needs %zu bytes of scratch but the built-in scratch holds %zu; "
+                  "call cachalot_moe_decode with a workspace of your own",
+                  rows, k, need, STATIC_SCRATCH_BYTES);
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(CACHALOT_ECUDA, "moe_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= MAX_DEVICES) return fail(CACHALOT_EUNSUPPORTED, "moe_decode_static: device ordinal %d", dev);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(static_scratch_mu);
+    scratch = static_scratch_addr[dev];
+    if (!scratch) {  // set-up, once per device, with that device current
+      e = cudaGetSymbolAddress(&scratch, static_scratch);
+      if (e != cudaSuccess || !scratch)
+        return fail(CACHALOT_ECUDA, "moe_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      static_scratch_addr[dev] = scratch;
+    }
+  }
+  // Nothing in the scratch has to start at zero: the kernels reset their own arrival counters at
+  // the start of every call and overwrite every intermediate they later read.
+  return cachalot_moe_decode(bank, desc, x_bf16, slots, gate_w, rows, k, swiglu_limit, numerics, scratch,
+                             STATIC_SCRATCH_BYTES, out, out_dtype, status, stream);
 }

@@ -145,6 +145,26 @@ CACHALOT_API int cachalot_moe_decode(const void* bank, const cachalot_bank_desc*
                         int numerics, void* workspace, size_t workspace_bytes, void* out, int out_dtype,
                         int* status, cachalot_stream_t stream);
 
+/* No counterpart in the reference.  The same computation as cachalot_moe_decode for callers that
+ * must not allocate device memory and have no workspace to hand over: an embedding whose memory
+ * pool already owns all of HBM (a cudaMalloc there fails, or forces a device-wide
+ * synchronisation in the middle of a token), a plugin slot whose signature has no room for a
+ * scratch pointer, or a real-time decode loop that may not call into the allocator.  The scratch is
+ * a 4 MiB array that is part of the library image: every GPU that loads the library holds it until
+ * the process exits.  A call whose cachalot_moe_decode_workspace_bytes(desc, rows, k) exceeds
+ * cachalot_moe_decode_static_scratch_bytes() is refused with CACHALOT_ESCRATCH and nothing is
+ * launched (decode batches of a few tokens fit; larger ones need the caller's own workspace).  The
+ * entry point calls no cudaMalloc, cudaFree or other allocating routine.
+ *   - The first call on each device looks the array's device address up (with that device
+ *     current); make that first call outside any stream capture.
+ *   - All calls on one device share the one array: two calls that can overlap on the GPU
+ *     (different streams without an ordering between them) race.  Calls on one stream are safe.
+ *   - The array keeps the previous call's intermediates; no call depends on them. */
+CACHALOT_API size_t cachalot_moe_decode_static_scratch_bytes(void);
+CACHALOT_API int cachalot_moe_decode_static(const void* bank, const cachalot_bank_desc* desc /* host */, const void* x_bf16,
+                               const int32_t* slots, const float* gate_w, int rows, int k, float swiglu_limit,
+                               int numerics, void* out, int out_dtype, int* status, cachalot_stream_t stream);
+
 /* ---- FP8 E4M3 trunk GEMV with act_quant ---------------------------------------------------- */
 
 /* Replaces model/fp8_ref.py:27-92 quantize_activation_fp8 and model/fp8_fused_metal.py:175-233:
