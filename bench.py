@@ -326,7 +326,7 @@ def run_ours(args):
     ms_e2e = timed(run_token, args.steps, feed_host, read_back)
     clocks = sampler.stop() if rank == 0 else None
 
-    # per-kernel durations: the same 40 passes with routing done beforehand, one launch kind at a time
+    # per-kernel durations: the same 40 passes with routing done beforehand
     with torch.cuda.stream(stream):
         distinct = 0
         for l in range(LAYERS):
@@ -336,13 +336,20 @@ def run_ours(args):
         for l in range(LAYERS):
             s = slots_all[l].reshape(-1)
             distinct += int(torch.unique(s[s >= 0]).numel())
-    run_gu = make_runner(lambda: phase_step("gate_up"))
-    run_dn = make_runner(lambda: phase_step("down"))
+    fused = B == 1          # one token: gate/up, SwiGLU and down run as ONE launch per layer
     reps = max(3, args.steps // 2)
-    timed(run_gu, 2)
-    ms_gu = timed(run_gu, reps) / (reps * LAYERS)
-    timed(run_dn, 2)
-    ms_dn = timed(run_dn, reps) / (reps * LAYERS)
+    if fused:
+        run_layers = make_runner(lambda: phase_step(None))
+        timed(run_layers, 2)
+        ms_layer = timed(run_layers, reps) / (reps * LAYERS)
+        ms_gu = ms_dn = None
+    else:
+        run_gu = make_runner(lambda: phase_step("gate_up"))
+        run_dn = make_runner(lambda: phase_step("down"))
+        timed(run_gu, 2)
+        ms_gu = timed(run_gu, reps) / (reps * LAYERS)
+        timed(run_dn, 2)
+        ms_dn = timed(run_dn, reps) / (reps * LAYERS)
     st = int(status.item())
 
     if rank != 0:
@@ -357,12 +364,26 @@ def run_ours(args):
     gu_alg = u_per_layer * up_bytes + B * HIDDEN * 2 + B * K * INTER * 4
     dn_alg = u_per_layer * dn_bytes + B * K * INTER * 4 + B * HIDDEN * 4
     peak, peak_kind = measured_peak()
-    gu_gbs = gu_alg / (ms_gu * 1e-3) / 1e9
-    dn_gbs = dn_alg / (ms_dn * 1e-3) / 1e9
     tok_s = B * args.steps / (ms * 1e-3)
     tok_s_e2e = B * args.steps / (ms_e2e * 1e-3)
-    layer_bytes = gu_alg + dn_alg
+    layer_bytes = u_per_layer * (up_bytes + dn_bytes) + B * HIDDEN * 2 + B * HIDDEN * 4
     hbm_gbs_token = layer_bytes * LAYERS * args.steps / (ms * 1e-3) / 1e9
+    if fused:
+        gbs = layer_bytes / (ms_layer * 1e-3) / 1e9
+        roofline = {"kernel": "fused_decode_kernel (W1,W3 dequant-GEMV + SwiGLU + W2 dequant-GEMV + sum over experts, one launch per layer)",
+                    "bound": "hbm", "achieved": gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": gbs / peak,
+                    "us_per_launch": ms_layer * 1e3, "algorithmic_bytes_per_launch": layer_bytes,
+                    "traffic": NCU_TRAFFIC_BYTES.get((args.bank, B, "fused"))}
+        launches = 2 * LAYERS * args.steps          # routing tail + fused experts per layer
+    else:
+        gu_gbs = gu_alg / (ms_gu * 1e-3) / 1e9
+        dn_gbs = dn_alg / (ms_dn * 1e-3) / 1e9
+        roofline = {"kernel": "gate_up (W1,W3 dequant-GEMV + SwiGLU)", "bound": "hbm", "achieved": gu_gbs, "peak": peak,
+                    "peak_kind": peak_kind, "unit": "GB/s", "frac": gu_gbs / peak, "us_per_launch": ms_gu * 1e3,
+                    "algorithmic_bytes_per_launch": gu_alg, "traffic": NCU_TRAFFIC_BYTES.get((args.bank, B, "gate_up")),
+                    "down": {"achieved": dn_gbs, "frac": dn_gbs / peak, "us_per_launch": ms_dn * 1e3,
+                             "algorithmic_bytes_per_launch": dn_alg, "traffic": NCU_TRAFFIC_BYTES.get((args.bank, B, "down"))}}
+        launches = 4 * LAYERS * args.steps          # routing tail, row grouping, gate/up, down per layer
 
     line = {
         "metric": "moe_decode_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
@@ -374,13 +395,9 @@ def run_ours(args):
         "e2e": {"value": tok_s_e2e, "unit": "tok/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": int(x_host[0].numel() * 2 + logits_host[0].numel() * 4),
                 "d2h_bytes_per_step": int(out_host.numel() * 4)},
-        "gpu_launches": 3 * LAYERS * args.steps,
+        "gpu_launches": launches,
         "hbm": {"token_algorithmic_gbs": hbm_gbs_token, "frac_of_8tbs": hbm_gbs_token / 8000.0, "frac_of_peak": hbm_gbs_token / peak},
-        "roofline": {"kernel": "gate_up (W1,W3 dequant-GEMV + SwiGLU)", "bound": "hbm", "achieved": gu_gbs, "peak": peak,
-                     "peak_kind": peak_kind, "unit": "GB/s", "frac": gu_gbs / peak, "us_per_launch": ms_gu * 1e3,
-                     "algorithmic_bytes_per_launch": gu_alg, "traffic": NCU_TRAFFIC_BYTES.get((args.bank, B, "gate_up")),
-                     "down": {"achieved": dn_gbs, "frac": dn_gbs / peak, "us_per_launch": ms_dn * 1e3,
-                              "algorithmic_bytes_per_launch": dn_alg, "traffic": NCU_TRAFFIC_BYTES.get((args.bank, B, "down"))}},
+        "roofline": roofline,
         "status_word": st,
     }
     if world == 1 and not args.no_cpu_baseline:

@@ -48,4 +48,12 @@ int launch_decode_mma(const BankView& v, const void* x, const int32_t* slots, co
 size_t decode_mma_workspace_bytes(int hidden, int inter, int rows, int k);
 bool decode_mma_supported(const BankView& v, int rows, int k);
 
+
+// Single-launch decode for one token (moe_decode_fused.cu).  Same contract as launch_decode_mma.
+int launch_decode_fused(const BankView& v, const void* x, const int32_t* slots, const float* gate_w, int rows, int k,
+                        float limit, int numerics_flags, void* workspace, void* out, int out_dtype, int* status,
+                        cudaStream_t stream);
+size_t decode_fused_workspace_bytes(int hidden, int inter, int rows, int k);
+bool decode_fused_supported(const BankView& v, int rows, int k);
+
 }  // namespace cachalot

@@ -264,7 +264,9 @@ using namespace cachalot;
 
 extern "C" size_t cachalot_moe_decode_workspace_bytes(const cachalot_bank_desc* desc, int rows, int k) {
   if (!desc || rows <= 0 || k <= 0) return 0;
-  return decode_mma_workspace_bytes(desc->hidden, desc->inter, rows, k);  // >= the simple kernels' rows*k*inter floats
+  const size_t a = decode_mma_workspace_bytes(desc->hidden, desc->inter, rows, k);  // >= the simple kernels' rows*k*inter floats
+  const size_t b = decode_fused_workspace_bytes(desc->hidden, desc->inter, rows, k);
+  return a > b ? a : b;
 }
 
 extern "C" int cachalot_moe_decode(const void* bank, const cachalot_bank_desc* desc, const void* x_bf16,
@@ -277,13 +279,16 @@ extern "C" int cachalot_moe_decode(const void* bank, const cachalot_bank_desc* d
   if (!x_bf16 || !slots || !gate_w || !out) return fail(CACHALOT_EINVAL, "moe_decode: null pointer");
   if (rows < 0 || k <= 0 || k > 64) return fail(CACHALOT_EINVAL, "moe_decode: rows=%d k=%d out of range", rows, k);
   if ((long long)rows * k > 65535) return fail(CACHALOT_EINVAL, "moe_decode: rows*k=%lld exceeds 65535", (long long)rows * k);
-  if ((numerics & 0xff) > CACHALOT_NUMERICS_BF16_H32 || (numerics & ~0x7ff))
+  if ((numerics & 0xff) > CACHALOT_NUMERICS_BF16_H32 || (numerics & ~0xfff))
     return fail(CACHALOT_EINVAL, "moe_decode: unknown numerics %d", numerics);
   if (out_dtype != CACHALOT_F32 && out_dtype != CACHALOT_BF16) return fail(CACHALOT_EINVAL, "moe_decode: out dtype must be f32 or bf16");
   if (rows == 0) return CACHALOT_OK;
   size_t need = cachalot_moe_decode_workspace_bytes(desc, rows, k);
   if (!workspace || workspace_bytes < need) return fail(CACHALOT_ESCRATCH, "moe_decode: workspace %zu < %zu bytes", workspace_bytes, need);
   if (!aligned(workspace, 256) || !aligned(x_bf16, 16) || !aligned(out, 4)) return fail(CACHALOT_EALIGN, "moe_decode: workspace needs 256-byte, x 16-byte alignment");
+  if (!(numerics & (CACHALOT_DECODE_SIMPLE | CACHALOT_DECODE_UNFUSED | CACHALOT_DECODE_ONLY_GATE_UP | CACHALOT_DECODE_ONLY_DOWN)) &&
+      decode_fused_supported(v, rows, k))
+    return launch_decode_fused(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, numerics, workspace, out, out_dtype, status, (cudaStream_t)stream);
   if (!(numerics & CACHALOT_DECODE_SIMPLE) && decode_mma_supported(v, rows, k))
     return launch_decode_mma(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, numerics, workspace, out, out_dtype, status, (cudaStream_t)stream);
   if (desc->format == CACHALOT_BANK_FP4)

@@ -1,0 +1,795 @@
+// Decode-time routed experts for ONE token in ONE launch (cooperative, one CTA per SM).
+//
+//   phase 0 : hidden[j, i] = silu(min(g,L)) * clip(u,+-L) * gate_w[j]     g = W1_j x, u = W3_j x
+//   grid barrier
+//   phase 1 : out[n]       = sum_j W2_j[n, :] . hidden[j, :]               j in routing order
+//
+// The kernel is a stream of weight bytes: HBM -> cp.async.bulk (one copy per tile of 8 or 16
+// weight rows, 8..23 KB) -> a ring of shared-memory stages -> registers -> mma.sync.  Warps 0 and 1
+// issue the copies and run ahead of the consumers by the depth of the ring; they keep issuing the
+// down-projection rows while the CTA waits at the grid barrier, so HBM stays busy across it.
+// Warps 3..11 each own a slice of the reduction dimension of every stage (their activation
+// operand stays in registers); warp 2 adds the nine partial sums of a stage, applies SwiGLU / the
+// sum over experts and writes the results.
+//
+//   unit, phase 0 : 8 rows of W1 (MMA rows 0..7) + the same 8 rows of W3 (MMA rows 8..15) of one expert
+//   unit, phase 1 : 16 rows of W2 of one expert; a CTA owns whole 16-row output tiles and walks
+//                   the experts in routing order, so the sum over experts needs no atomics.
+//
+// A lane (g = lane/4, t = lane%4) reads 16 contiguous bytes of rows g and g+8 per step, so a quad
+// covers 64 contiguous bytes of a row: four "sub-blocks" that each have their own scale (FP4: a
+// 32-code E8M0 block; 2-bit: 64 codes, half a scale group).  The MMA would add the four
+// sub-blocks up; to keep them apart the activation operand of lane t is placed in operand column
+// 2t (and 2t+1) and is zero in the others, so accumulator column 2t holds exactly the partial sum
+// of the codes lane t loaded, and the scale is applied per sub-block in fp32 afterwards.
+//
+//   2-bit bank : codes stay packed: w & (0x03030303 << 2c) puts codes c, c+4, c+8, c+12 of a word
+//                into the four u8 lanes of an IMMA operand (m16n8k32, u8 x s8 -> s32, exact) scaled
+//                by 4**c; the four classes c have their own accumulators and are combined as
+//                integers.  Activations are fixed point per sub-block: X = rint(x * 2**e),
+//                |X| < 2**14, X = 256*hi + lo in operand columns 2t and 2t+1.
+//                acc += s * 2**-e * (256*T_hi + T_lo) + b * sum(x).
+//   FP4 bank   : E2M1 byte -> f16x2 (cvt.rn.f16x2.e2m1x2), HMMA m16n8k16 with f16 activations
+//                scaled per sub-block by 2**e;  acc += 2**(scale-127) * 2**-e * T.
+#include "kernels.cuh"
+
+namespace cachalot {
+namespace {
+
+constexpr int NPROD = 4;                          // producer warps (one issuing lane each; a lane's copies do not overlap)
+constexpr int KMAX = 8;                           // routed experts per token
+constexpr int MAX_TILES = 8;                      // phase-1 output tiles one CTA may own
+constexpr uint32_t WAIT_LIMIT = 1u << 20;         // polls before a wait gives up and flags an error
+constexpr int SMEM_LIMIT = 227 * 1024;
+
+template <int FMT>
+struct Fm {
+  static constexpr int NCW = FMT == CACHALOT_BANK_FP4 ? 3 : 5;         // consumer warps (each holds one ring stage while it works)
+  static constexpr int NTHREADS = (NPROD + NCW) * 32;
+  static constexpr int STEP = FMT == CACHALOT_BANK_FP4 ? 128 : 256;    // codes of a row per step (64 B)
+  static constexpr int SUB = FMT == CACHALOT_BANK_FP4 ? 32 : 64;       // codes per sub-block (16 B)
+};
+
+#ifdef CB_FUSED_TRACE
+__device__ unsigned long long fused_trace[256][16];
+__device__ __forceinline__ unsigned long long gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define TRACE(slot) do { if (lane == 0) fused_trace[blockIdx.x][slot] = gtimer(); } while (0)
+#define CYC_DECL long long cyc_a = 0, cyc_b = 0, cyc_c = 0, cyc_t = 0
+#define CYC_START do { cyc_t = clock64(); } while (0)
+#define CYC_ADD(acc) do { long long n_ = clock64(); acc += n_ - cyc_t; cyc_t = n_; } while (0)
+#define CYC_STORE(slot, acc) do { if (lane == 0) fused_trace[blockIdx.x][slot] = (unsigned long long)(acc); } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#define CYC_DECL do { } while (0)
+#define CYC_START do { } while (0)
+#define CYC_ADD(acc) do { } while (0)
+#define CYC_STORE(slot, acc) do { } while (0)
+#endif
+
+// Grid barrier word (sense reversal on the top bit, so it needs no reset): every device that loads
+// the library has its own copy, zero at load.  A launch uses it once; two launches cannot be at
+// their barrier at the same time because a launch holds every SM until it has passed its own.
+__device__ unsigned grid_bar_word;
+
+struct Geo {
+  int K[2];           // reduction length: hidden, inter
+  int nsteps[2];      // steps along K (the last may be partial)
+  int row_bytes[2];   // bytes of a weight row in the bank
+  int sc_bytes[2];    // bytes of one scale (or bias) array of a unit
+  int skew[2];        // bytes between the two 4-row halves of an 8-row tile in a stage (bank-conflict skew)
+  int sc_off[2];      // offset of the scale arrays inside a stage
+  int act_stride[2];  // bytes of one operand row (padded to whole steps)
+  int unit_bytes[2];  // bytes copied per unit
+  int tiles0;         // inter / 8
+  int tiles1;         // hidden / 16
+  int stage_bytes, nst;
+  int off_ring, off_act, off_pe, off_part, off_bar, total;
+  int balance;        // 1: split phase-0 units by bytes so that every CTA streams the same total
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* b, int n) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(n));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(smem_u32(b)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false after WAIT_LIMIT polls (the caller flags the error and carries on).
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try(b, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+
+__device__ __forceinline__ void imma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void hmma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// four E2M1 bytes (8 codes) -> four f16x2 (low nibble in the low half)
+__device__ __forceinline__ void fp4_word(uint32_t w, uint32_t (&h)[4]) {
+  asm("{\n"
+      ".reg .b8 b0, b1, b2, b3;\n"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
+      "}\n"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+      : "r"(w));
+}
+
+// One arrival per CTA; returns false when the other CTAs do not show up within the wait limit.
+__device__ __forceinline__ bool grid_barrier(unsigned* word, unsigned n_ctas, bool master) {
+  __threadfence();
+  const unsigned inc = master ? 0x80000000u - (n_ctas - 1u) : 1u;
+  const unsigned old = atomicAdd(word, inc);
+  bool ok = false;
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    unsigned cur;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(cur) : "l"(word) : "memory");
+    if ((old ^ cur) & 0x80000000u) {
+      ok = true;
+      break;
+    }
+  }
+  __threadfence();
+  return ok;
+}
+
+// split of the phase-0 units and phase-1 tiles over the CTAs
+__device__ __forceinline__ void cta_ranges(const Geo& G, int np, int b, int nb, int& u0, int& u1, int& t0, int& t1) {
+  const long long U0 = (long long)np * G.tiles0;
+  t0 = (int)((long long)G.tiles1 * b / nb);
+  t1 = (int)((long long)G.tiles1 * (b + 1) / nb);
+  if (!G.balance) {
+    u0 = (int)(U0 * b / nb);
+    u1 = (int)(U0 * (b + 1) / nb);
+    return;
+  }
+  const long long b0 = G.unit_bytes[0], b1 = (long long)np * G.unit_bytes[1];
+  const long long T = U0 * b0 + (long long)G.tiles1 * b1;
+  auto f = [&](int bb, int tt) {
+    long long v = (T * bb / nb - (long long)tt * b1 + b0 / 2) / b0;
+    return (int)(v < 0 ? 0 : (v > U0 ? U0 : v));
+  };
+  u0 = f(b, t0);
+  u1 = b + 1 == nb ? (int)U0 : f(b + 1, t1);
+  if (u1 < u0) u1 = u0;
+}
+
+__device__ __forceinline__ void unpack16_bf16(const uint4 a, const uint4 b, float (&v)[16]) {
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+// Converts one 16-element block of an activation row into operand form and stores it.  Operand
+// rows are laid out per step so that the eight lanes that load real data in one LDS.128 read 128
+// (FP4: 64) contiguous bytes:
+//   2-bit : step c = 512 B = [q 0..3][t 0..3][hi | lo][16 B]; the 16 values of (sub-block 4c+t,
+//           16-block q) are s8 in the 4x4-transposed order [0,4,8,12 | 1,5,9,13 | 2,6,10,14 | 3,7,11,15]
+//           (byte i of word c is code 4i+c of a weight word)
+//   FP4   : step c = 256 B = [q 0..3][t 0..3][16 B]; (sub-block 4c+t, chunk q) holds 8 f16 in natural order
+// and, for the first block of a sub-block, pexs = (2**-e [/64 for the 2-bit class sum], sum of x).
+// The lanes that share a sub-block (4 for 2-bit, 2 for FP4) are adjacent and call this together.
+template <int FMT>
+__device__ __forceinline__ void convert_block(uint8_t* act_row, float2* pexs_row, int b, bool valid, float (&v)[16]) {
+  constexpr int LPS = Fm<FMT>::SUB / 16;  // lanes per sub-block
+  float amax = 0.f, sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i])), sum += v[i];
+#pragma unroll
+  for (int o = LPS >> 1; o > 0; o >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  }
+  // 2**e * amax in [2**13, 2**14) (2-bit) or [2**10, 2**11) (FP4)
+  const int ex = (int)((__float_as_uint(amax) >> 23) & 0xffu);
+  int e = 0;
+  if (ex > 0 && ex < 255) e = (FMT == CACHALOT_BANK_FP4 ? 10 : 13) - (ex - 127);
+  e = min(max(e, -100), 100);
+  const float P = __uint_as_float((uint32_t)(e + 127) << 23);
+  if (!valid) return;
+  if constexpr (FMT == CACHALOT_BANK_FP4) {
+    uint32_t pk[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      __half2 h = __floats2half2_rn(v[2 * i] * P, v[2 * i + 1] * P);
+      pk[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    const int sub = b >> 1, q0 = (b & 1) * 2;
+    uint8_t* dst = act_row + (sub >> 2) * 256 + (sub & 3) * 16 + q0 * 64;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    *reinterpret_cast<uint4*>(dst + 64) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+    if ((b & (LPS - 1)) == 0) pexs_row[sub] = make_float2(__uint_as_float((uint32_t)(127 - e) << 23), sum);
+  } else {
+    int hi[16], lo[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int X = __float2int_rn(v[i] * P);
+      hi[i] = (X + 128) >> 8;
+      lo[i] = X - hi[i] * 256;
+    }
+    uint32_t ph[4], pl[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {  // word c = elements c, c+4, c+8, c+12
+      ph[c] = __byte_perm(__byte_perm(hi[c], hi[c + 4], 0x0040), __byte_perm(hi[c + 8], hi[c + 12], 0x0040), 0x5410);
+      pl[c] = __byte_perm(__byte_perm(lo[c], lo[c + 4], 0x0040), __byte_perm(lo[c + 8], lo[c + 12], 0x0040), 0x5410);
+    }
+    const int sub = b >> 2, q = b & 3;
+    uint8_t* dst = act_row + (sub >> 2) * 512 + q * 128 + (sub & 3) * 32;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+    *reinterpret_cast<uint4*>(dst + 16) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+    // the class sum of the IMMA accumulators carries a factor 64
+    if (q == 0) pexs_row[sub] = make_float2(__uint_as_float((uint32_t)(127 - e - 6) << 23), sum);
+  }
+}
+
+// d = a * b (no accumulator input: the first MMA of a chain)
+__device__ __forceinline__ void imma_u8s8_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void hmma_f16_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+template <int SDT>
+__device__ __forceinline__ float scale_f32(uint16_t raw) {
+  if constexpr (SDT == CACHALOT_F16) return __half2float(__ushort_as_half(raw));
+  return __uint_as_float((uint32_t)raw << 16);
+}
+
+// One step (64 bytes of rows g and g+8 per quad) of the 2-bit bank.  pb: the lane's operand bytes
+// (64 B: four 16-element blocks in 4x4-transposed order), pxs = (2**-e / 64, sum x) of its sub-block.
+template <int SDT, bool GUARD>
+__device__ __forceinline__ void step_affine(float& accA, float& accB, const uint8_t* pa, const uint8_t* pbrow, const uint8_t* pb,
+                                            const float2* ppx, const uint16_t* psA, const uint16_t* psB, int arr, bool valid) {
+  const uint4 va = *reinterpret_cast<const uint4*>(pa);
+  const uint4 vb = *reinterpret_cast<const uint4*>(pbrow);
+  uint4 b[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) b[q] = (!GUARD || valid) ? *reinterpret_cast<const uint4*>(pb + q * 128) : make_uint4(0, 0, 0, 0);
+  const float2 pxs = (!GUARD || valid) ? *ppx : make_float2(0.f, 0.f);
+  const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+  const uint32_t bw[4][4] = {{b[0].x, b[0].y, b[0].z, b[0].w}, {b[1].x, b[1].y, b[1].z, b[1].w},
+                             {b[2].x, b[2].y, b[2].z, b[2].w}, {b[3].x, b[3].y, b[3].z, b[3].w}};
+  int T[4][4];
+#pragma unroll
+  for (int cl = 0; cl < 4; ++cl) {
+    const uint32_t M = 0x03030303u << (2 * cl);
+    imma_u8s8_z(T[cl], wa[0] & M, wb[0] & M, wa[1] & M, wb[1] & M, bw[0][cl], bw[1][cl]);
+    imma_u8s8(T[cl], wa[2] & M, wb[2] & M, wa[3] & M, wb[3] & M, bw[2][cl], bw[3][cl]);
+  }
+  // 64 * (T0 + T1/4 + T2/16 + T3/64) per accumulator element, then 256*hi + lo
+  int R[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) R[i] = ((T[0][i] * 4 + T[1][i]) * 4 + T[2][i]) * 4 + T[3][i];
+  const float fa = (float)(R[0] * 256 + R[1]) * pxs.x;
+  const float fb = (float)(R[2] * 256 + R[3]) * pxs.x;
+  float sa = scale_f32<SDT>(psA[0]), ba = scale_f32<SDT>(psA[arr]);
+  float sb = scale_f32<SDT>(psB[0]), bb = scale_f32<SDT>(psB[arr]);
+  if (GUARD && !valid) sa = ba = sb = bb = 0.f;  // entries past the row: whatever was read is discarded
+  accA = fmaf(sa, fa, fmaf(ba, pxs.y, accA));
+  accB = fmaf(sb, fb, fmaf(bb, pxs.y, accB));
+}
+
+template <bool GUARD>
+__device__ __forceinline__ void step_fp4(float& accA, float& accB, const uint8_t* pa, const uint8_t* pbrow, const uint8_t* pb,
+                                         const float2* ppx, const uint8_t* psA, const uint8_t* psB, bool valid) {
+  const uint4 va = *reinterpret_cast<const uint4*>(pa);
+  const uint4 vb = *reinterpret_cast<const uint4*>(pbrow);
+  uint4 b[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) b[q] = (!GUARD || valid) ? *reinterpret_cast<const uint4*>(pb + q * 64) : make_uint4(0, 0, 0, 0);
+  const float pe = (!GUARD || valid) ? ppx->x : 0.f;
+  const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+  const uint32_t bw[4][4] = {{b[0].x, b[0].y, b[0].z, b[0].w}, {b[1].x, b[1].y, b[1].z, b[1].w},
+                             {b[2].x, b[2].y, b[2].z, b[2].w}, {b[3].x, b[3].y, b[3].z, b[3].w}};
+  float T[4];
+#pragma unroll
+  for (int wd = 0; wd < 4; ++wd) {
+    uint32_t ha[4], hb[4];
+    fp4_word(wa[wd], ha);
+    fp4_word(wb[wd], hb);
+    if (wd == 0)
+      hmma_f16_z(T, ha[0], hb[0], ha[1], hb[1], bw[wd][0], bw[wd][1]);
+    else
+      hmma_f16(T, ha[0], hb[0], ha[1], hb[1], bw[wd][0], bw[wd][1]);
+    hmma_f16(T, ha[2], hb[2], ha[3], hb[3], bw[wd][2], bw[wd][3]);
+  }
+  float sa = e8m0_to_f32(*psA), sb = e8m0_to_f32(*psB);
+  if (GUARD && !valid) sa = sb = 0.f;  // entries past the row: whatever was read is discarded
+  accA = fmaf(T[0], sa * pe, accA);
+  accB = fmaf(T[2], sb * pe, accB);
+}
+
+// One unit of one consumer warp: the lane's partial sums of MMA rows g and g+8 over the whole
+// reduction (its own sub-block of every step).  stage: the unit's 16 rows then its scale arrays;
+// act_row / pexs_row: the operand row (activation in operand form, per sub-block constants);
+// zeros: 64 zero bytes for the lanes whose operand column belongs to another lane's sub-block.
+template <int FMT, int PHASE, int SDT>
+__device__ __forceinline__ float2 unit_dot(const uint8_t* stage, const Geo& G, const uint8_t* act_row, const float2* pexs_row,
+                                           const uint8_t* zeros, int g, int t) {
+  constexpr int SUB = Fm<FMT>::SUB, STEP = Fm<FMT>::STEP;
+  const int K = G.K[PHASE];
+  const int rb = G.row_bytes[PHASE];
+  const int full = K / STEP;  // whole steps; one more, partial, when K is not a multiple of STEP
+  const int nsub = K / SUB;
+  // MMA row g is row wr = (g >> 1) + 4 * (g & 1) of its 8-row tile: the two rows a quarter-warp
+  // reads in one LDS come from different 4-row halves, which sit `skew` bytes apart modulo 128
+  const int wr = (g >> 1) + 4 * (g & 1);
+  const int half = 4 * rb + G.skew[PHASE];
+  const uint8_t* pa = stage + (g & 1) * half + (g >> 1) * rb + t * 16;
+  const uint8_t* pbrow = pa + 2 * half;  // 4 * rb + skew + 4 * rb + skew
+  const uint8_t* sc = stage + G.sc_off[PHASE];
+  // the lane's operand column g carries its own sub-block only: 2-bit g = 2t (hi), 2t+1 (lo); FP4 g = 2t
+  const bool mine = FMT == CACHALOT_BANK_FP4 ? (g == 2 * t) : ((g >> 1) == t);
+  const uint8_t* pb = mine ? act_row + (FMT == CACHALOT_BANK_FP4 ? t * 16 : t * 32 + (g & 1) * 16) : zeros;
+  const int bstep = mine ? (FMT == CACHALOT_BANK_FP4 ? 256 : 512) : 0;
+  const float2* ppx = pexs_row + t;
+  float accA = 0.f, accB = 0.f;
+
+  if constexpr (FMT == CACHALOT_BANK_AFFINE) {
+    // scale / bias entries of the two rows at the lane's sub-block of step 0; +2 entries per step
+    const uint16_t* S = reinterpret_cast<const uint16_t*>(sc);
+    const int arr = G.sc_bytes[PHASE] / 2;
+    int ia, ib;
+    if constexpr (PHASE == 0) {
+      ia = wr * (K >> 7) + (t >> 1);  // rows are whole groups (hidden is a multiple of 128)
+      ib = 2 * arr + ia;              // [s1 | b1 | s3 | b3]
+    } else {
+      ia = (wr * K + t * 64) >> 7;    // groups run over the flattened [16, K] tile
+      ib = ((wr + 8) * K + t * 64) >> 7;
+    }
+    const uint16_t* psA = S + ia;
+    const uint16_t* psB = S + ib;
+#pragma unroll 4
+    for (int c = 0; c < full; ++c) {
+      step_affine<SDT, false>(accA, accB, pa, pbrow, pb, ppx, psA, psB, arr, true);
+      pa += 64, pbrow += 64, pb += bstep, ppx += 4, psA += 2, psB += 2;
+    }
+    if (full * STEP < K) step_affine<SDT, true>(accA, accB, pa, pbrow, pb, ppx, psA, psB, arr, full * 4 + t < nsub);
+  } else {
+    const int nblk = K >> 5;  // E8M0 bytes per row: [rows 0..15][K/32]
+    const uint8_t* psA = sc + wr * nblk + t;
+    const uint8_t* psB = psA + 8 * nblk;
+#pragma unroll 4
+    for (int c = 0; c < full; ++c) {
+      step_fp4<false>(accA, accB, pa, pbrow, pb, ppx, psA, psB, true);
+      pa += 64, pbrow += 64, pb += bstep, ppx += 4, psA += 4, psB += 4;
+    }
+    if (full * STEP < K) step_fp4<true>(accA, accB, pa, pbrow, pb, ppx, psA, psB, full * 4 + t < nsub);
+  }
+  return make_float2(accA, accB);
+}
+
+template <int FMT, int SDT, typename OutT>
+__global__ void __launch_bounds__(Fm<FMT>::NTHREADS, 1)
+fused_decode_kernel(BankView bank, Geo G, const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ slots,
+                    const float* __restrict__ gate_w, int k, float limit, int numerics, float* __restrict__ hidden,
+                    OutT* __restrict__ out, int* __restrict__ status) {
+  constexpr int SUB = Fm<FMT>::SUB, NCW = Fm<FMT>::NCW, NCT = NCW * 32;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ int s_route[KMAX];   // routing position of the p-th present expert
+  __shared__ int s_slot[KMAX];    // its bank slot
+  __shared__ float s_gw[KMAX];    // its router weight
+  __shared__ int s_np;
+  uint8_t* ring = smem + G.off_ring;
+  uint8_t* act = smem + G.off_act;
+  float2* pexs = reinterpret_cast<float2*>(smem + G.off_pe);
+  float* ybuf = reinterpret_cast<float*>(smem + G.off_part);  // [tiles of this CTA][KMAX][16]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + G.off_bar);
+  uint64_t* empty = full + 16;
+  const uint8_t* zeros = smem + G.off_bar + 256;  // 512 zero bytes
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int H = bank.hidden, I = bank.inter;
+  int err = 0;
+  if (threadIdx.x < 128) reinterpret_cast<uint32_t*>(smem + G.off_bar + 256)[threadIdx.x] = 0u;
+
+  // consumers fetch their part of x before anything else (up to XB 16-element blocks per thread)
+  constexpr int XB = 4;
+  const int tid = threadIdx.x - NPROD * 32;
+  uint4 xa[XB], xb[XB];
+  if (warp >= NPROD) {
+#pragma unroll
+    for (int j = 0; j < XB; ++j) {
+      const int b = tid + j * NCT;
+      xa[j] = xb[j] = make_uint4(0, 0, 0, 0);
+      if (b < H / 16) {
+        xa[j] = *reinterpret_cast<const uint4*>(x + b * 16);
+        xb[j] = *reinterpret_cast<const uint4*>(x + b * 16 + 8);
+      }
+    }
+  }
+  // warp 0: the present experts in routing order; its lane 0: the barriers
+  if (warp == 0) {
+    int my_slot = -1;
+    if (lane < k) my_slot = slots[lane];
+    const bool present = my_slot >= 0 && my_slot < bank.n_slots;
+    const unsigned pmask = __ballot_sync(0xffffffffu, present);
+    if (present) {
+      const int p = __popc(pmask & ((1u << lane) - 1u));
+      s_route[p] = lane, s_slot[p] = my_slot, s_gw[p] = gate_w[lane];
+    }
+    const bool oob = lane < k && my_slot >= bank.n_slots;
+    if (__any_sync(0xffffffffu, oob) && lane == 0 && blockIdx.x == 0 && status) atomicOr(status, CACHALOT_STATUS_SLOT_RANGE);
+    if (lane == 0) {
+      s_np = __popc(pmask);
+      for (int s = 0; s < G.nst; ++s) mbar_init(&full[s], NPROD), mbar_init(&empty[s], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+  }
+  __syncthreads();
+  if (warp == NPROD) TRACE(0);
+  const int np = s_np;
+  int u_begin, u_end, t_begin, t_end;
+  cta_ranges(G, np, blockIdx.x, gridDim.x, u_begin, u_end, t_begin, t_end);
+  const int n0 = u_end - u_begin;         // phase-0 units of this CTA
+  const int n1 = (t_end - t_begin) * np;  // phase-1 units of this CTA
+
+  if (warp < NPROD) {
+    // ---------------- producers: four rows (and one scale array) of every unit per warp ----------------
+    const bool fp4 = FMT == CACHALOT_BANK_FP4;
+    const int t_w1 = 0, t_w3 = fp4 ? 4 : 6, t_w2 = fp4 ? 2 : 3;
+    const int n_sc = fp4 ? 1 : 2;  // scale arrays per matrix
+    if (lane == 0) {
+      int idx = 0;
+      uint32_t phase_bit = 0;
+      int p = n0 > 0 ? u_begin / G.tiles0 : 0, tile = n0 > 0 ? u_begin - p * G.tiles0 : 0;
+      for (int i = 0; i < n0 + n1; ++i) {
+        const int phase = i < n0 ? 0 : 1;
+        if (i == n0) p = 0, tile = t_begin;
+        if (i >= G.nst && !mbar_wait(&empty[idx], phase_bit ^ 1)) {
+          err = 1;  // the consumers stopped releasing stages: give up on the rest of the stream
+          break;
+        }
+        const uint8_t* rec = bank.base + (size_t)s_slot[p] * bank.record_bytes;
+        uint8_t* dst = ring + (size_t)idx * G.stage_bytes;
+        const int rb = G.row_bytes[phase], sb = G.sc_bytes[phase];
+        uint8_t* sdst = dst + G.sc_off[phase];
+        uint64_t* bar = &full[idx];
+        // warp w copies four rows: phase 0 = half (w & 1) of W1 (w < 2) or W3; phase 1 = rows 4w..4w+3 of W2;
+        // and scale array w of the unit, if there is one
+        const uint8_t* src;
+        uint8_t* rdst;
+        int n_arr;         // scale arrays of the unit
+        const uint8_t* ssrc = nullptr;
+        if (phase == 0) {
+          // stage: [W1 rows 0-3 | skew | W1 rows 4-7 | skew | W3 rows 0-3 | skew | W3 rows 4-7 | skew | scale arrays]
+          const int tw = warp < 2 ? t_w1 : t_w3;
+          src = rec + bank.off[tw] + (size_t)tile * 8 * rb + (size_t)(warp & 1) * 4 * rb;
+          rdst = dst + warp * (4 * rb + G.skew[0]);
+          n_arr = 2 * n_sc;
+          if (warp < n_arr) {  // arrays in stage order: W1's, then W3's
+            const int m = warp / n_sc, a = warp - m * n_sc;
+            ssrc = rec + bank.off[(m == 0 ? t_w1 : t_w3) + 1 + a] + (size_t)tile * sb;
+          }
+        } else {
+          src = rec + bank.off[t_w2] + (size_t)tile * 16 * rb + (size_t)warp * 4 * rb;
+          rdst = dst + warp * 4 * rb;
+          n_arr = n_sc;
+          if (warp < n_arr) ssrc = rec + bank.off[t_w2 + 1 + warp] + (size_t)tile * sb;
+        }
+        mbar_expect_tx(bar, (uint32_t)(4 * rb + (ssrc ? sb : 0)));
+        bulk_g2s(rdst, src, (uint32_t)(4 * rb), bar);
+        if (ssrc) bulk_g2s(sdst + warp * sb, ssrc, (uint32_t)sb, bar);
+        if (phase == 0) {
+          if (++tile == G.tiles0) tile = 0, ++p;
+        } else {
+          if (++p == np) p = 0, ++tile;
+        }
+        if (++idx == G.nst) idx = 0, phase_bit ^= 1;
+      }
+      if (err && status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
+    }
+    if (warp < 2) TRACE(9 + warp);
+  } else {
+    // ---------------- consumers: warp cw takes units cw, cw + NCW, ... of the CTA's stream ----------------
+    const int cw = warp - NPROD;
+#pragma unroll
+    for (int j = 0; j < XB; ++j) {
+      const int b = tid + j * NCT;
+      if (j * NCT < H / 16) {  // warp-uniform: the lanes of a sub-block convert together
+        float v[16];
+        unpack16_bf16(xa[j], xb[j], v);
+        convert_block<FMT>(act, pexs, b < H / 16 ? b : 0, b < H / 16, v);
+      }
+    }
+    named_bar_sync(1, NCT);
+    if (cw == 0) TRACE(1);
+
+    // -------- phase 0 --------
+    CYC_DECL;
+    CYC_START;
+    for (int i = cw; i < n0; i += NCW) {
+      const int idx = i % G.nst;
+      const uint32_t par = (uint32_t)(i / G.nst) & 1u;
+      if (!err && !mbar_wait(&full[idx], par)) err = 1;
+      CYC_ADD(cyc_a);
+      if (cw == 0 && i == 0) TRACE(2);
+      float2 r = unit_dot<FMT, 0, SDT>(ring + (size_t)idx * G.stage_bytes, G, act, pexs, zeros, g, t);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[idx]);
+      r.x += __shfl_xor_sync(0xffffffffu, r.x, 1), r.y += __shfl_xor_sync(0xffffffffu, r.y, 1);
+      r.x += __shfl_xor_sync(0xffffffffu, r.x, 2), r.y += __shfl_xor_sync(0xffffffffu, r.y, 2);
+      if (t == 0) {
+        const int u = u_begin + i;
+        const int p = u / G.tiles0, tile = u - p * G.tiles0;
+        float gv = r.x, uv = r.y;
+        if (numerics != CACHALOT_NUMERICS_F32) gv = bf16_round(gv), uv = bf16_round(uv);
+        float h = swiglu(gv, uv, limit) * s_gw[p];
+        if (numerics == CACHALOT_NUMERICS_BF16) h = bf16_round(h);
+        hidden[(size_t)s_route[p] * I + tile * 8 + (g >> 1) + 4 * (g & 1)] = h;
+      }
+      CYC_ADD(cyc_b);
+    }
+    if (cw == 0) { TRACE(3); CYC_STORE(11, cyc_a); CYC_STORE(12, cyc_b); }
+
+    // -------- grid barrier: every CTA's hidden rows are written --------
+    named_bar_sync(1, NCT);
+    if (cw == 0) {
+      TRACE(4);
+      if (lane == 0) {
+        if (!grid_barrier(&grid_bar_word, gridDim.x, blockIdx.x == 0)) err = 2;
+      }
+      __syncwarp();
+      TRACE(5);
+    }
+    named_bar_sync(1, NCT);
+
+    // phase 1 operand: the hidden rows of the present experts (operand row p = p-th present expert)
+    const int row_stride1 = G.act_stride[1];
+    const int nsub1 = I / SUB;
+    {
+      const int nblk = I / 16, total = np * nblk;
+      for (int base = 0; base < total; base += 2 * NCT) {
+        // two blocks per thread, both loads issued before either is used
+        float4 q[2][4];
+        int rr[2], bbk[2];
+        bool ok[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int idx = base + h * NCT + tid;
+          ok[h] = idx < total;
+          rr[h] = ok[h] ? idx / nblk : 0;
+          bbk[h] = ok[h] ? idx - rr[h] * nblk : 0;
+          if (ok[h]) {
+            const float4* src = reinterpret_cast<const float4*>(hidden + (size_t)s_route[rr[h]] * I + bbk[h] * 16);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) q[h][i] = __ldcg(src + i);  // written by other CTAs in this launch: read from L2
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) q[h][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float v[16];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) v[4 * i] = q[h][i].x, v[4 * i + 1] = q[h][i].y, v[4 * i + 2] = q[h][i].z, v[4 * i + 3] = q[h][i].w;
+          convert_block<FMT>(act + (size_t)rr[h] * row_stride1, pexs + rr[h] * nsub1, bbk[h], ok[h], v);
+        }
+      }
+    }
+    named_bar_sync(1, NCT);
+    if (cw == 0) TRACE(6);
+
+    // -------- phase 1: unit q of the CTA = (tile t_begin + q / np, expert q % np) --------
+    CYC_START;
+    for (int q = cw; q < n1; q += NCW) {
+      const int i = n0 + q;
+      const int idx = i % G.nst;
+      const uint32_t par = (uint32_t)(i / G.nst) & 1u;
+      const int tl = q / np, p = q - tl * np;
+      if (!err && !mbar_wait(&full[idx], par)) err = 1;
+      CYC_ADD(cyc_c);
+      float2 r = unit_dot<FMT, 1, SDT>(ring + (size_t)idx * G.stage_bytes, G, act + (size_t)p * row_stride1, pexs + p * nsub1, zeros, g, t);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[idx]);
+      r.x += __shfl_xor_sync(0xffffffffu, r.x, 1), r.y += __shfl_xor_sync(0xffffffffu, r.y, 1);
+      r.x += __shfl_xor_sync(0xffffffffu, r.x, 2), r.y += __shfl_xor_sync(0xffffffffu, r.y, 2);
+      if (t == 0) {
+        float y0 = r.x, y1 = r.y;
+        if (numerics != CACHALOT_NUMERICS_F32) y0 = bf16_round(y0), y1 = bf16_round(y1);
+        const int wr = (g >> 1) + 4 * (g & 1);  // the weight row of MMA row g
+        ybuf[(tl * KMAX + p) * 16 + wr] = y0;
+        ybuf[(tl * KMAX + p) * 16 + wr + 8] = y1;
+      }
+    }
+    if (cw == 0) { TRACE(7); CYC_STORE(13, cyc_c); }
+    named_bar_sync(1, NCT);
+    // sum over the experts in routing order
+    for (int o = tid; o < (t_end - t_begin) * 16; o += NCT) {
+      const int tl = o >> 4, r = o & 15;
+      float tot = 0.f;
+      for (int p = 0; p < np; ++p) tot += ybuf[(tl * KMAX + p) * 16 + r];
+      if constexpr (sizeof(OutT) == 2)
+        out[(t_begin + tl) * 16 + r] = __float2bfloat16_rn(tot);
+      else
+        out[(t_begin + tl) * 16 + r] = tot;
+    }
+    if (cw == 0) TRACE(8);
+    if (err && lane == 0 && status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
+  }
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+template <int FMT>
+bool make_geo_fmt(const BankView& v, int k, Geo* out) {
+  Geo G = {};
+  constexpr bool fp4 = FMT == CACHALOT_BANK_FP4;
+  constexpr int STEP = Fm<FMT>::STEP, SUB = Fm<FMT>::SUB;
+  G.K[0] = v.hidden, G.K[1] = v.inter;
+  for (int p = 0; p < 2; ++p) {
+    if (G.K[p] % SUB) return false;
+    G.nsteps[p] = (G.K[p] + STEP - 1) / STEP;
+    G.row_bytes[p] = fp4 ? G.K[p] / 2 : G.K[p] / 4;
+  }
+  if (!fp4 && v.hidden % 128) return false;  // phase 0 indexes scale groups per row
+  if (v.inter % 8 || v.hidden % 16) return false;
+  if (v.hidden > 16 * 4 * Fm<FMT>::NCW * 32) return false;  // x is staged in at most four 16-element blocks per thread
+  G.tiles0 = v.inter / 8, G.tiles1 = v.hidden / 16;
+  int n_sc[2];
+  if (fp4) {
+    G.sc_bytes[0] = 8 * (v.hidden / 32), n_sc[0] = 2;
+    G.sc_bytes[1] = 16 * (v.inter / 32), n_sc[1] = 1;
+  } else {
+    if ((16 * (long long)v.inter) % 128) return false;
+    G.sc_bytes[0] = 8 * (v.hidden / 128) * 2, n_sc[0] = 4;
+    G.sc_bytes[1] = (16 * v.inter / 128) * 2, n_sc[1] = 2;
+  }
+  int st[2];
+  for (int p = 0; p < 2; ++p) {
+    if (G.sc_bytes[p] % 16 || G.row_bytes[p] % 16) return false;
+    G.unit_bytes[p] = 16 * G.row_bytes[p] + n_sc[p] * G.sc_bytes[p];
+    G.act_stride[p] = G.nsteps[p] * (fp4 ? 256 : 512);
+  }
+  // phase 0 copies an 8-row tile as two 4-row halves; when a row is a multiple of 128 bytes the second half
+  // is shifted by 64 bytes so that the two rows a quarter-warp reads together fall into different banks
+  G.skew[0] = G.row_bytes[0] % 128 == 0 ? 64 : 0;
+  G.skew[1] = 0;  // one copy for all 16 rows
+  for (int p = 0; p < 2; ++p) {
+    G.sc_off[p] = 16 * G.row_bytes[p] + 4 * G.skew[p];
+    st[p] = G.sc_off[p] + n_sc[p] * G.sc_bytes[p] + 64;  // a partial last step reads up to 48 bytes past a row's end
+  }
+  G.stage_bytes = (int)align_up((size_t)(st[0] > st[1] ? st[0] : st[1]), 128);
+  // operand area: phase 0 one row of hidden, phase 1 k rows of inter
+  const int act0 = G.act_stride[0], act1 = k * G.act_stride[1];
+  const int act = (int)align_up((size_t)(act0 > act1 ? act0 : act1), 128);
+  const int pe0 = (v.hidden / SUB) * 8, pe1 = k * (v.inter / SUB) * 8;
+  const int pe = (int)align_up((size_t)(pe0 > pe1 ? pe0 : pe1), 128);
+  int p = 0;
+  G.off_bar = p, p += 1024;  // mbarriers (256 B) + 512 zero bytes
+  G.off_act = p, p += act;
+  G.off_pe = p, p += pe;
+  G.off_part = p, p += MAX_TILES * KMAX * 16 * 4;  // per-expert results of the CTA's output tiles
+  G.off_ring = p;
+  const int room = SMEM_LIMIT - 256 /* static shared */ - p;
+  G.nst = room / G.stage_bytes;
+  if (G.nst > 16) G.nst = 16;
+  if (G.nst < 2) return false;
+  G.total = p + G.nst * G.stage_bytes;
+  *out = G;
+  return true;
+}
+
+bool make_geo(const BankView& v, int k, Geo* out) {
+  return v.format == CACHALOT_BANK_FP4 ? make_geo_fmt<CACHALOT_BANK_FP4>(v, k, out) : make_geo_fmt<CACHALOT_BANK_AFFINE>(v, k, out);
+}
+
+}  // namespace
+
+bool decode_fused_supported(const BankView& v, int rows, int k) {
+  if (rows != 1 || k < 1 || k > KMAX) return false;
+  if (v.format == CACHALOT_BANK_AFFINE && (v.group != 128 || v.bits != 2)) return false;
+  Geo G;
+  return make_geo(v, k, &G);
+}
+
+// hidden [k, inter] f32
+size_t decode_fused_workspace_bytes(int hidden, int inter, int rows, int k) {
+  (void)hidden;
+  return align_up((size_t)rows * k * inter * sizeof(float), 256);
+}
+
+template <int FMT>
+static int launch_fused_fmt(const BankView& v, const Geo& G, const void* x, const int32_t* slots, const float* gate_w, int k,
+                            float limit, int numerics, void* workspace, void* out, int out_dtype, int* status,
+                            cudaStream_t stream) {
+  float* hidden = static_cast<float*>(workspace);
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    return fail(CACHALOT_ECUDA, "moe_decode (fused): cannot read the SM count");
+  const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+  Geo Gl = G;
+  // the byte-balanced split needs every CTA's share to be larger than the phase-1 tiles it owns
+  {
+    const long long U0 = (long long)k * G.tiles0, b0 = G.unit_bytes[0], b1 = (long long)k * G.unit_bytes[1];
+    const long long T = U0 * b0 + (long long)G.tiles1 * b1;
+    const long long max_tiles = (G.tiles1 + sms - 1) / sms;
+    Gl.balance = (T / sms >= max_tiles * b1 + 2 * b0) ? 1 : 0;
+    if (max_tiles > MAX_TILES) return CACHALOT_EUNSUPPORTED;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)sms);
+  cfg.blockDim = dim3(Fm<FMT>::NTHREADS);
+  cfg.dynamicSmemBytes = (size_t)G.total;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident: the grid barrier cannot starve
+  at[0].val.cooperative = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaSuccess;
+  auto go = [&](auto kern, auto* outp) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT - 256);
+    if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, v, Gl, xb, slots, gate_w, k, limit, numerics, hidden, outp, status);
+  };
+  const bool bf16_scales = FMT == CACHALOT_BANK_AFFINE && v.scale_dtype == CACHALOT_BF16;
+  if (out_dtype == CACHALOT_BF16) {
+    if (bf16_scales) go(fused_decode_kernel<FMT, CACHALOT_BF16, __nv_bfloat16>, (__nv_bfloat16*)out);
+    else go(fused_decode_kernel<FMT, CACHALOT_F16, __nv_bfloat16>, (__nv_bfloat16*)out);
+  } else {
+    if (bf16_scales) go(fused_decode_kernel<FMT, CACHALOT_BF16, float>, (float*)out);
+    else go(fused_decode_kernel<FMT, CACHALOT_F16, float>, (float*)out);
+  }
+  if (e != cudaSuccess) return fail(CACHALOT_ECUDA, "moe_decode (fused): %s", cudaGetErrorString(e));
+  return check_launch("moe_decode (fused)");
+}
+
+int launch_decode_fused(const BankView& v, const void* x, const int32_t* slots, const float* gate_w, int rows, int k,
+                        float limit, int numerics_flags, void* workspace, void* out, int out_dtype, int* status,
+                        cudaStream_t stream) {
+  Geo G;
+  if (rows != 1 || !make_geo(v, k, &G)) return CACHALOT_EUNSUPPORTED;
+  const int numerics = numerics_flags & 0xff;
+  if (v.format == CACHALOT_BANK_FP4)
+    return launch_fused_fmt<CACHALOT_BANK_FP4>(v, G, x, slots, gate_w, k, limit, numerics, workspace, out, out_dtype, status, stream);
+  return launch_fused_fmt<CACHALOT_BANK_AFFINE>(v, G, x, slots, gate_w, k, limit, numerics, workspace, out, out_dtype, status, stream);
+}
+
+}  // namespace cachalot
+
+#ifdef CB_FUSED_TRACE
+extern "C" __attribute__((visibility("default"))) int cachalot_debug_fused_trace(unsigned long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, cachalot::fused_trace, sizeof(unsigned long long) * 256 * 16);
+}
+#endif

@@ -168,7 +168,8 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
 def moe_forward(x: torch.Tensor, slot_ids: torch.Tensor, gate_weights: torch.Tensor, bank: SlabBank, *,
                 swiglu_limit: float = 10.0, numerics: str | None = None, out_dtype=torch.float32,
                 out: torch.Tensor | None = None, status: torch.Tensor | None = None,
-                workspace: torch.Tensor | None = None, phase: str | None = None, simple: bool = False) -> torch.Tensor:
+                workspace: torch.Tensor | None = None, phase: str | None = None, simple: bool = False,
+                unfused: bool = False) -> torch.Tensor:
     """Routed experts for `rows` tokens: x bf16 [rows,H], slot_ids int32 [rows,k] (bank slots, -1 =
     absent -> zero contribution), gate_weights float32 [rows,k] -> [rows,H].
 
@@ -176,7 +177,9 @@ def moe_forward(x: torch.Tensor, slot_ids: torch.Tensor, gate_weights: torch.Ten
     model/moe_fused_metal.py:189-233); "bf16" rounds g, u, h and each expert's output to bf16 (the
     affine op, model/expert_affine.py:65-81).  Default: by bank format.  `phase` ("gate_up" or
     "down") runs only one of the two launches; it exists for per-kernel timing.  `simple` selects
-    the one-warp-per-output kernels instead of the tensor-core ones (a cross-check, any shape)."""
+    the one-warp-per-output kernels instead of the tensor-core ones (a cross-check, any shape);
+    `unfused` selects the two-launch tensor-core kernels where the single-launch kernel (one token)
+    would run."""
     _need_cuda(x, slot_ids, gate_weights)
     if x.dim() != 2 or x.shape[1] != bank.hidden:
         raise ValueError(f"x must be [rows, {bank.hidden}], got {tuple(x.shape)}")
@@ -190,6 +193,8 @@ def moe_forward(x: torch.Tensor, slot_ids: torch.Tensor, gate_weights: torch.Ten
     num |= {None: 0, "gate_up": _lib.DECODE_ONLY_GATE_UP, "down": _lib.DECODE_ONLY_DOWN}[phase]
     if simple:
         num |= _lib.DECODE_SIMPLE
+    if unfused:
+        num |= _lib.DECODE_UNFUSED
     xb = x.to(torch.bfloat16).contiguous()
     slot_ids = slot_ids.to(torch.int32).contiguous()
     gate_weights = gate_weights.to(torch.float32).contiguous()

@@ -42,7 +42,8 @@ enum {
 enum {
   CACHALOT_STATUS_SLOT_RANGE = 1, /* a slot id >= n_slots was seen and treated as absent */
   CACHALOT_STATUS_ID_RANGE = 2,   /* an expert id outside [0, E) was seen and dropped */
-  CACHALOT_STATUS_SCALE_RANGE = 4 /* an FP4 block scale outside the window around fp4_scale_centre was clamped */
+  CACHALOT_STATUS_SCALE_RANGE = 4, /* an FP4 block scale outside the window around fp4_scale_centre was clamped */
+  CACHALOT_STATUS_WAIT_EXPIRED = 8 /* a bounded device-side wait ran out (the result of that call is not valid) */
 };
 
 enum { CACHALOT_BANK_FP4 = 0, CACHALOT_BANK_AFFINE = 1 };
@@ -59,6 +60,8 @@ enum { CACHALOT_DECODE_ONLY_GATE_UP = 0x100, CACHALOT_DECODE_ONLY_DOWN = 0x200 }
 /* OR-ed into `numerics`: use the simple one-warp-per-output kernels (any shape; the cross-check of the
  * tensor-core kernels, as the reference checks its fused kernels against the unfused loop) */
 enum { CACHALOT_DECODE_SIMPLE = 0x400 };
+/* OR-ed into `numerics`: use the two-launch tensor-core kernels even where the single-launch kernel applies */
+enum { CACHALOT_DECODE_UNFUSED = 0x800 };
 enum { CACHALOT_ROUTER_SQRT_SOFTPLUS = 0, CACHALOT_ROUTER_SIGMOID = 1 };
 enum { CACHALOT_SCALE_E8M0 = 0, CACHALOT_SCALE_F32 = 1 };
 
