@@ -44,7 +44,10 @@ constexpr int SMEM_LIMIT = 227 * 1024;
 
 template <int FMT>
 struct Fm {
-  static constexpr int NCW = FMT == CACHALOT_BANK_FP4 ? 3 : 5;         // consumer warps (each holds one ring stage while it works)
+  // consumer warps work in pairs: the two warps of a pair split the reduction of one unit in halves and
+  // share its ring stage.  An even number of pairs puts two consumer warps on every scheduler of the SM.
+  static constexpr int NPAIR = FMT == CACHALOT_BANK_FP4 ? 2 : 4;
+  static constexpr int NCW = 2 * NPAIR;
   static constexpr int NTHREADS = (NPROD + NCW) * 32;
   static constexpr int STEP = FMT == CACHALOT_BANK_FP4 ? 128 : 256;    // codes of a row per step (64 B)
   static constexpr int SUB = FMT == CACHALOT_BANK_FP4 ? 32 : 64;       // codes per sub-block (16 B)
@@ -86,7 +89,7 @@ struct Geo {
   int unit_bytes[2];  // bytes copied per unit
   int tiles0;         // inter / 8
   int tiles1;         // hidden / 16
-  int stage_bytes, nst;
+  int stage_bytes[2], nst[2];  // ring geometry per phase (the same memory, cut into stages of the phase's unit size)
   int off_ring, off_act, off_pe, off_part, off_bar, total;
   int balance;        // 1: split phase-0 units by bytes so that every CTA streams the same total
 };
@@ -345,24 +348,27 @@ __device__ __forceinline__ void step_fp4(float& accA, float& accB, const uint8_t
 // zeros: 64 zero bytes for the lanes whose operand column belongs to another lane's sub-block.
 template <int FMT, int PHASE, int SDT>
 __device__ __forceinline__ float2 unit_dot(const uint8_t* stage, const Geo& G, const uint8_t* act_row, const float2* pexs_row,
-                                           const uint8_t* zeros, int g, int t) {
+                                           const uint8_t* zeros, int g, int t, int part) {
   constexpr int SUB = Fm<FMT>::SUB, STEP = Fm<FMT>::STEP;
   const int K = G.K[PHASE];
   const int rb = G.row_bytes[PHASE];
   const int full = K / STEP;  // whole steps; one more, partial, when K is not a multiple of STEP
   const int nsub = K / SUB;
+  // part 0 takes the first half of the whole steps, part 1 the rest and the partial step
+  const int c_begin = part ? (full + 1) / 2 : 0, c_end = part ? full : (full + 1) / 2;
+  const bool tail = part && full * STEP < K;
   // MMA row g is row wr = (g >> 1) + 4 * (g & 1) of its 8-row tile: the two rows a quarter-warp
   // reads in one LDS come from different 4-row halves, which sit `skew` bytes apart modulo 128
   const int wr = (g >> 1) + 4 * (g & 1);
   const int half = 4 * rb + G.skew[PHASE];
-  const uint8_t* pa = stage + (g & 1) * half + (g >> 1) * rb + t * 16;
+  const uint8_t* pa = stage + (g & 1) * half + (g >> 1) * rb + t * 16 + c_begin * 64;
   const uint8_t* pbrow = pa + 2 * half;  // 4 * rb + skew + 4 * rb + skew
   const uint8_t* sc = stage + G.sc_off[PHASE];
   // the lane's operand column g carries its own sub-block only: 2-bit g = 2t (hi), 2t+1 (lo); FP4 g = 2t
   const bool mine = FMT == CACHALOT_BANK_FP4 ? (g == 2 * t) : ((g >> 1) == t);
-  const uint8_t* pb = mine ? act_row + (FMT == CACHALOT_BANK_FP4 ? t * 16 : t * 32 + (g & 1) * 16) : zeros;
   const int bstep = mine ? (FMT == CACHALOT_BANK_FP4 ? 256 : 512) : 0;
-  const float2* ppx = pexs_row + t;
+  const uint8_t* pb = (mine ? act_row + (FMT == CACHALOT_BANK_FP4 ? t * 16 : t * 32 + (g & 1) * 16) : zeros) + c_begin * bstep;
+  const float2* ppx = pexs_row + t + c_begin * 4;
   float accA = 0.f, accB = 0.f;
 
   if constexpr (FMT == CACHALOT_BANK_AFFINE) {
@@ -377,24 +383,24 @@ __device__ __forceinline__ float2 unit_dot(const uint8_t* stage, const Geo& G, c
       ia = (wr * K + t * 64) >> 7;    // groups run over the flattened [16, K] tile
       ib = ((wr + 8) * K + t * 64) >> 7;
     }
-    const uint16_t* psA = S + ia;
-    const uint16_t* psB = S + ib;
+    const uint16_t* psA = S + ia + 2 * c_begin;
+    const uint16_t* psB = S + ib + 2 * c_begin;
 #pragma unroll 4
-    for (int c = 0; c < full; ++c) {
+    for (int c = c_begin; c < c_end; ++c) {
       step_affine<SDT, false>(accA, accB, pa, pbrow, pb, ppx, psA, psB, arr, true);
       pa += 64, pbrow += 64, pb += bstep, ppx += 4, psA += 2, psB += 2;
     }
-    if (full * STEP < K) step_affine<SDT, true>(accA, accB, pa, pbrow, pb, ppx, psA, psB, arr, full * 4 + t < nsub);
+    if (tail) step_affine<SDT, true>(accA, accB, pa, pbrow, pb, ppx, psA, psB, arr, full * 4 + t < nsub);
   } else {
     const int nblk = K >> 5;  // E8M0 bytes per row: [rows 0..15][K/32]
-    const uint8_t* psA = sc + wr * nblk + t;
+    const uint8_t* psA = sc + wr * nblk + t + 4 * c_begin;
     const uint8_t* psB = psA + 8 * nblk;
 #pragma unroll 4
-    for (int c = 0; c < full; ++c) {
+    for (int c = c_begin; c < c_end; ++c) {
       step_fp4<false>(accA, accB, pa, pbrow, pb, ppx, psA, psB, true);
       pa += 64, pbrow += 64, pb += bstep, ppx += 4, psA += 4, psB += 4;
     }
-    if (full * STEP < K) step_fp4<true>(accA, accB, pa, pbrow, pb, ppx, psA, psB, full * 4 + t < nsub);
+    if (tail) step_fp4<true>(accA, accB, pa, pbrow, pb, ppx, psA, psB, full * 4 + t < nsub);
   }
   return make_float2(accA, accB);
 }
@@ -414,16 +420,18 @@ fused_decode_kernel(BankView bank, Geo G, const __nv_bfloat16* __restrict__ x, c
   uint8_t* act = smem + G.off_act;
   float2* pexs = reinterpret_cast<float2*>(smem + G.off_pe);
   float* ybuf = reinterpret_cast<float*>(smem + G.off_part);  // [tiles of this CTA][KMAX][16]
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + G.off_bar);
-  uint64_t* empty = full + 16;
-  const uint8_t* zeros = smem + G.off_bar + 256;  // 512 zero bytes
+  // mbarriers: full / empty per ring stage and phase (the ring is re-cut into smaller stages for phase 1)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + G.off_bar);
+  uint64_t* full0 = bars, *empty0 = bars + 16, *full1 = bars + 32, *empty1 = bars + 48;
+  const uint8_t* zeros = smem + G.off_bar + 512;  // 512 zero bytes
+  float2* xch = reinterpret_cast<float2*>(smem + G.off_bar + 1024);  // [NPAIR][2][8] partial sums between the warps of a pair
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int H = bank.hidden, I = bank.inter;
   int err = 0;
-  if (threadIdx.x < 128) reinterpret_cast<uint32_t*>(smem + G.off_bar + 256)[threadIdx.x] = 0u;
+  if (threadIdx.x < 128) reinterpret_cast<uint32_t*>(smem + G.off_bar + 512)[threadIdx.x] = 0u;
 
   // consumers fetch their part of x before anything else (up to XB 16-element blocks per thread)
-  constexpr int XB = 4;
+  constexpr int XB = 3;
   const int tid = threadIdx.x - NPROD * 32;
   uint4 xa[XB], xb[XB];
   if (warp >= NPROD) {
@@ -451,7 +459,10 @@ fused_decode_kernel(BankView bank, Geo G, const __nv_bfloat16* __restrict__ x, c
     if (__any_sync(0xffffffffu, oob) && lane == 0 && blockIdx.x == 0 && status) atomicOr(status, CACHALOT_STATUS_SLOT_RANGE);
     if (lane == 0) {
       s_np = __popc(pmask);
-      for (int s = 0; s < G.nst; ++s) mbar_init(&full[s], NPROD), mbar_init(&empty[s], 1);
+      for (int s = 0; s < 16; ++s) {
+        mbar_init(&full0[s], NPROD), mbar_init(&empty0[s], 2);
+        mbar_init(&full1[s], NPROD), mbar_init(&empty1[s], 2);
+      }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
   }
@@ -462,6 +473,7 @@ fused_decode_kernel(BankView bank, Geo G, const __nv_bfloat16* __restrict__ x, c
   cta_ranges(G, np, blockIdx.x, gridDim.x, u_begin, u_end, t_begin, t_end);
   const int n0 = u_end - u_begin;         // phase-0 units of this CTA
   const int n1 = (t_end - t_begin) * np;  // phase-1 units of this CTA
+  const int nst0 = G.nst[0], nst1 = G.nst[1];
 
   if (warp < NPROD) {
     // ---------------- producers: four rows (and one scale array) of every unit per warp ----------------
@@ -469,59 +481,73 @@ fused_decode_kernel(BankView bank, Geo G, const __nv_bfloat16* __restrict__ x, c
     const int t_w1 = 0, t_w3 = fp4 ? 4 : 6, t_w2 = fp4 ? 2 : 3;
     const int n_sc = fp4 ? 1 : 2;  // scale arrays per matrix
     if (lane == 0) {
-      int idx = 0;
-      uint32_t phase_bit = 0;
-      int p = n0 > 0 ? u_begin / G.tiles0 : 0, tile = n0 > 0 ? u_begin - p * G.tiles0 : 0;
-      for (int i = 0; i < n0 + n1; ++i) {
-        const int phase = i < n0 ? 0 : 1;
-        if (i == n0) p = 0, tile = t_begin;
-        if (i >= G.nst && !mbar_wait(&empty[idx], phase_bit ^ 1)) {
-          err = 1;  // the consumers stopped releasing stages: give up on the rest of the stream
-          break;
-        }
-        const uint8_t* rec = bank.base + (size_t)s_slot[p] * bank.record_bytes;
-        uint8_t* dst = ring + (size_t)idx * G.stage_bytes;
-        const int rb = G.row_bytes[phase], sb = G.sc_bytes[phase];
-        uint8_t* sdst = dst + G.sc_off[phase];
-        uint64_t* bar = &full[idx];
-        // warp w copies four rows: phase 0 = half (w & 1) of W1 (w < 2) or W3; phase 1 = rows 4w..4w+3 of W2;
-        // and scale array w of the unit, if there is one
-        const uint8_t* src;
-        uint8_t* rdst;
-        int n_arr;         // scale arrays of the unit
-        const uint8_t* ssrc = nullptr;
-        if (phase == 0) {
+      // phase 0
+      {
+        const int rb = G.row_bytes[0], sb = G.sc_bytes[0];
+        const int tw = warp < 2 ? t_w1 : t_w3;
+        const int n_arr = 2 * n_sc;  // arrays in stage order: W1's, then W3's
+        int p = n0 > 0 ? u_begin / G.tiles0 : 0, tile = n0 > 0 ? u_begin - p * G.tiles0 : 0;
+        for (int i = 0; i < n0 && !err; ++i) {
+          const int idx = i % nst0;
+          if (i >= nst0 && !mbar_wait(&empty0[idx], (uint32_t)((i / nst0) - 1) & 1u)) {
+            err = 1;  // the consumers stopped releasing stages: give up on the rest of the stream
+            break;
+          }
+          const uint8_t* rec = bank.base + (size_t)s_slot[p] * bank.record_bytes;
+          uint8_t* dst = ring + (size_t)idx * G.stage_bytes[0];
+          uint64_t* bar = &full0[idx];
           // stage: [W1 rows 0-3 | skew | W1 rows 4-7 | skew | W3 rows 0-3 | skew | W3 rows 4-7 | skew | scale arrays]
-          const int tw = warp < 2 ? t_w1 : t_w3;
-          src = rec + bank.off[tw] + (size_t)tile * 8 * rb + (size_t)(warp & 1) * 4 * rb;
-          rdst = dst + warp * (4 * rb + G.skew[0]);
-          n_arr = 2 * n_sc;
-          if (warp < n_arr) {  // arrays in stage order: W1's, then W3's
+          const uint8_t* src = rec + bank.off[tw] + (size_t)tile * 8 * rb + (size_t)(warp & 1) * 4 * rb;
+          const uint8_t* ssrc = nullptr;
+          if (warp < n_arr) {
             const int m = warp / n_sc, a = warp - m * n_sc;
             ssrc = rec + bank.off[(m == 0 ? t_w1 : t_w3) + 1 + a] + (size_t)tile * sb;
           }
-        } else {
-          src = rec + bank.off[t_w2] + (size_t)tile * 16 * rb + (size_t)warp * 4 * rb;
-          rdst = dst + warp * 4 * rb;
-          n_arr = n_sc;
-          if (warp < n_arr) ssrc = rec + bank.off[t_w2 + 1 + warp] + (size_t)tile * sb;
-        }
-        mbar_expect_tx(bar, (uint32_t)(4 * rb + (ssrc ? sb : 0)));
-        bulk_g2s(rdst, src, (uint32_t)(4 * rb), bar);
-        if (ssrc) bulk_g2s(sdst + warp * sb, ssrc, (uint32_t)sb, bar);
-        if (phase == 0) {
+          mbar_expect_tx(bar, (uint32_t)(4 * rb + (ssrc ? sb : 0)));
+          bulk_g2s(dst + warp * (4 * rb + G.skew[0]), src, (uint32_t)(4 * rb), bar);
+          if (ssrc) bulk_g2s(dst + G.sc_off[0] + warp * sb, ssrc, (uint32_t)sb, bar);
           if (++tile == G.tiles0) tile = 0, ++p;
-        } else {
+        }
+      }
+      // phase 1: the ring is cut into nst1 stages of the smaller unit.  Before a stage is first used, the
+      // phase-0 stages it overlaps must have been released by their last phase-0 unit.
+      {
+        const int rb = G.row_bytes[1], sb = G.sc_bytes[1];
+        const int S0 = G.stage_bytes[0], S1 = G.stage_bytes[1];
+        int p = 0, tile = t_begin;
+        for (int q = 0; q < n1 && !err; ++q) {
+          const int idx = q % nst1;
+          if (q >= nst1) {
+            if (!mbar_wait(&empty1[idx], (uint32_t)((q / nst1) - 1) & 1u)) err = 1;
+          } else {
+            const int s_lo = idx * S1 / S0, s_hi = ((idx + 1) * S1 - 1) / S0;
+            for (int s0 = s_lo; s0 <= s_hi && s0 < nst0 && !err; ++s0) {
+              if (s0 >= n0) continue;                                 // never used in phase 0
+              const int i_last = s0 + ((n0 - 1 - s0) / nst0) * nst0;  // last phase-0 unit in that stage
+              if (!mbar_wait(&empty0[s0], (uint32_t)(i_last / nst0) & 1u)) err = 1;
+            }
+          }
+          if (err) break;
+          const uint8_t* rec = bank.base + (size_t)s_slot[p] * bank.record_bytes;
+          uint8_t* dst = ring + (size_t)idx * S1;
+          uint64_t* bar = &full1[idx];
+          const uint8_t* src = rec + bank.off[t_w2] + (size_t)tile * 16 * rb + (size_t)warp * 4 * rb;
+          const uint8_t* ssrc = warp < n_sc ? rec + bank.off[t_w2 + 1 + warp] + (size_t)tile * sb : nullptr;
+          mbar_expect_tx(bar, (uint32_t)(4 * rb + (ssrc ? sb : 0)));
+          bulk_g2s(dst + warp * 4 * rb, src, (uint32_t)(4 * rb), bar);
+          if (ssrc) bulk_g2s(dst + G.sc_off[1] + warp * sb, ssrc, (uint32_t)sb, bar);
           if (++p == np) p = 0, ++tile;
         }
-        if (++idx == G.nst) idx = 0, phase_bit ^= 1;
       }
       if (err && status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
     }
     if (warp < 2) TRACE(9 + warp);
   } else {
-    // ---------------- consumers: warp cw takes units cw, cw + NCW, ... of the CTA's stream ----------------
+    // ---------------- consumers: pair `pr` takes units pr, pr + NPAIR, ... of the CTA's stream ----------------
+    constexpr int NPAIR = Fm<FMT>::NPAIR;
     const int cw = warp - NPROD;
+    const int pr = cw >> 1, part = cw & 1;
+    const int pair_bar = 2 + pr;  // named barrier of the pair (0 = __syncthreads, 1 = all consumers)
 #pragma unroll
     for (int j = 0; j < XB; ++j) {
       const int b = tid + j * NCT;
@@ -533,25 +559,29 @@ fused_decode_kernel(BankView bank, Geo G, const __nv_bfloat16* __restrict__ x, c
     }
     named_bar_sync(1, NCT);
     if (cw == 0) TRACE(1);
+    int n_done = 0;  // units of this pair so far (selects the exchange buffer)
 
     // -------- phase 0 --------
     CYC_DECL;
     CYC_START;
-    for (int i = cw; i < n0; i += NCW) {
-      const int idx = i % G.nst;
-      const uint32_t par = (uint32_t)(i / G.nst) & 1u;
-      if (!err && !mbar_wait(&full[idx], par)) err = 1;
+    for (int i = pr; i < n0; i += NPAIR, ++n_done) {
+      const int idx = i % nst0;
+      if (!err && !mbar_wait(&full0[idx], (uint32_t)(i / nst0) & 1u)) err = 1;
       CYC_ADD(cyc_a);
       if (cw == 0 && i == 0) TRACE(2);
-      float2 r = unit_dot<FMT, 0, SDT>(ring + (size_t)idx * G.stage_bytes, G, act, pexs, zeros, g, t);
+      float2 r = unit_dot<FMT, 0, SDT>(ring + (size_t)idx * G.stage_bytes[0], G, act, pexs, zeros, g, t, part);
       __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[idx]);
+      if (lane == 0) mbar_arrive(&empty0[idx]);
       r.x += __shfl_xor_sync(0xffffffffu, r.x, 1), r.y += __shfl_xor_sync(0xffffffffu, r.y, 1);
       r.x += __shfl_xor_sync(0xffffffffu, r.x, 2), r.y += __shfl_xor_sync(0xffffffffu, r.y, 2);
-      if (t == 0) {
+      float2* xb2 = xch + (pr * 2 + (n_done & 1)) * 8;
+      if (part == 1 && t == 0) xb2[g] = r;
+      named_bar_sync(pair_bar, 64);
+      if (part == 0 && t == 0) {
+        const float2 o = xb2[g];
         const int u = u_begin + i;
         const int p = u / G.tiles0, tile = u - p * G.tiles0;
-        float gv = r.x, uv = r.y;
+        float gv = r.x + o.x, uv = r.y + o.y;
         if (numerics != CACHALOT_NUMERICS_F32) gv = bf16_round(gv), uv = bf16_round(uv);
         float h = swiglu(gv, uv, limit) * s_gw[p];
         if (numerics == CACHALOT_NUMERICS_BF16) h = bf16_round(h);
@@ -577,14 +607,14 @@ fused_decode_kernel(BankView bank, Geo G, const __nv_bfloat16* __restrict__ x, c
     const int row_stride1 = G.act_stride[1];
     const int nsub1 = I / SUB;
     {
+      constexpr int SB = 4;  // blocks per thread and round; all their loads are issued before any is used
       const int nblk = I / 16, total = np * nblk;
-      for (int base = 0; base < total; base += 2 * NCT) {
-        // two blocks per thread, both loads issued before either is used
-        float4 q[2][4];
-        int rr[2], bbk[2];
-        bool ok[2];
+      for (int base = 0; base < total; base += SB * NCT) {
+        float4 q[SB][4];
+        int rr[SB], bbk[SB];
+        bool ok[SB];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < SB; ++h) {
           const int idx = base + h * NCT + tid;
           ok[h] = idx < total;
           rr[h] = ok[h] ? idx / nblk : 0;
@@ -599,11 +629,13 @@ fused_decode_kernel(BankView bank, Geo G, const __nv_bfloat16* __restrict__ x, c
           }
         }
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          float v[16];
+        for (int h = 0; h < SB; ++h) {
+          if (base + h * NCT < total) {  // warp-uniform
+            float v[16];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) v[4 * i] = q[h][i].x, v[4 * i + 1] = q[h][i].y, v[4 * i + 2] = q[h][i].z, v[4 * i + 3] = q[h][i].w;
-          convert_block<FMT>(act + (size_t)rr[h] * row_stride1, pexs + rr[h] * nsub1, bbk[h], ok[h], v);
+            for (int i = 0; i < 4; ++i) v[4 * i] = q[h][i].x, v[4 * i + 1] = q[h][i].y, v[4 * i + 2] = q[h][i].z, v[4 * i + 3] = q[h][i].w;
+            convert_block<FMT>(act + (size_t)rr[h] * row_stride1, pexs + rr[h] * nsub1, bbk[h], ok[h], v);
+          }
         }
       }
     }
@@ -612,20 +644,22 @@ fused_decode_kernel(BankView bank, Geo G, const __nv_bfloat16* __restrict__ x, c
 
     // -------- phase 1: unit q of the CTA = (tile t_begin + q / np, expert q % np) --------
     CYC_START;
-    for (int q = cw; q < n1; q += NCW) {
-      const int i = n0 + q;
-      const int idx = i % G.nst;
-      const uint32_t par = (uint32_t)(i / G.nst) & 1u;
+    for (int q = pr; q < n1; q += NPAIR, ++n_done) {
+      const int idx = q % nst1;
       const int tl = q / np, p = q - tl * np;
-      if (!err && !mbar_wait(&full[idx], par)) err = 1;
+      if (!err && !mbar_wait(&full1[idx], (uint32_t)(q / nst1) & 1u)) err = 1;
       CYC_ADD(cyc_c);
-      float2 r = unit_dot<FMT, 1, SDT>(ring + (size_t)idx * G.stage_bytes, G, act + (size_t)p * row_stride1, pexs + p * nsub1, zeros, g, t);
+      float2 r = unit_dot<FMT, 1, SDT>(ring + (size_t)idx * G.stage_bytes[1], G, act + (size_t)p * row_stride1, pexs + p * nsub1, zeros, g, t, part);
       __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[idx]);
+      if (lane == 0) mbar_arrive(&empty1[idx]);
       r.x += __shfl_xor_sync(0xffffffffu, r.x, 1), r.y += __shfl_xor_sync(0xffffffffu, r.y, 1);
       r.x += __shfl_xor_sync(0xffffffffu, r.x, 2), r.y += __shfl_xor_sync(0xffffffffu, r.y, 2);
-      if (t == 0) {
-        float y0 = r.x, y1 = r.y;
+      float2* xb2 = xch + (pr * 2 + (n_done & 1)) * 8;
+      if (part == 1 && t == 0) xb2[g] = r;
+      named_bar_sync(pair_bar, 64);
+      if (part == 0 && t == 0) {
+        const float2 o = xb2[g];
+        float y0 = r.x + o.x, y1 = r.y + o.y;
         if (numerics != CACHALOT_NUMERICS_F32) y0 = bf16_round(y0), y1 = bf16_round(y1);
         const int wr = (g >> 1) + 4 * (g & 1);  // the weight row of MMA row g
         ybuf[(tl * KMAX + p) * 16 + wr] = y0;
@@ -664,7 +698,7 @@ bool make_geo_fmt(const BankView& v, int k, Geo* out) {
   }
   if (!fp4 && v.hidden % 128) return false;  // phase 0 indexes scale groups per row
   if (v.inter % 8 || v.hidden % 16) return false;
-  if (v.hidden > 16 * 4 * Fm<FMT>::NCW * 32) return false;  // x is staged in at most four 16-element blocks per thread
+  if (v.hidden > 16 * 3 * Fm<FMT>::NCW * 32) return false;  // x is staged in at most three 16-element blocks per thread
   G.tiles0 = v.inter / 8, G.tiles1 = v.hidden / 16;
   int n_sc[2];
   if (fp4) {
@@ -688,24 +722,28 @@ bool make_geo_fmt(const BankView& v, int k, Geo* out) {
   for (int p = 0; p < 2; ++p) {
     G.sc_off[p] = 16 * G.row_bytes[p] + 4 * G.skew[p];
     st[p] = G.sc_off[p] + n_sc[p] * G.sc_bytes[p] + 64;  // a partial last step reads up to 48 bytes past a row's end
+    G.stage_bytes[p] = (int)align_up((size_t)st[p], 128);
   }
-  G.stage_bytes = (int)align_up((size_t)(st[0] > st[1] ? st[0] : st[1]), 128);
   // operand area: phase 0 one row of hidden, phase 1 k rows of inter
   const int act0 = G.act_stride[0], act1 = k * G.act_stride[1];
   const int act = (int)align_up((size_t)(act0 > act1 ? act0 : act1), 128);
   const int pe0 = (v.hidden / SUB) * 8, pe1 = k * (v.inter / SUB) * 8;
   const int pe = (int)align_up((size_t)(pe0 > pe1 ? pe0 : pe1), 128);
   int p = 0;
-  G.off_bar = p, p += 1024;  // mbarriers (256 B) + 512 zero bytes
+  G.off_bar = p, p += 2048;  // mbarriers (512 B), 512 zero bytes, pair exchange buffers
   G.off_act = p, p += act;
   G.off_pe = p, p += pe;
   G.off_part = p, p += MAX_TILES * KMAX * 16 * 4;  // per-expert results of the CTA's output tiles
   G.off_ring = p;
   const int room = SMEM_LIMIT - 256 /* static shared */ - p;
-  G.nst = room / G.stage_bytes;
-  if (G.nst > 16) G.nst = 16;
-  if (G.nst < 2) return false;
-  G.total = p + G.nst * G.stage_bytes;
+  for (int ph = 0; ph < 2; ++ph) {
+    G.nst[ph] = room / G.stage_bytes[ph];
+    if (G.nst[ph] > 16) G.nst[ph] = 16;
+  }
+  // a pair holds a stage while it works on it; at least one more must be in flight
+  if (G.nst[0] < Fm<FMT>::NPAIR + 1 || G.nst[1] < Fm<FMT>::NPAIR + 1) return false;
+  const int r0 = G.nst[0] * G.stage_bytes[0], r1 = G.nst[1] * G.stage_bytes[1];
+  G.total = p + (r0 > r1 ? r0 : r1);
   *out = G;
   return true;
 }
@@ -745,7 +783,10 @@ static int launch_fused_fmt(const BankView& v, const Geo& G, const void* x, cons
     const long long U0 = (long long)k * G.tiles0, b0 = G.unit_bytes[0], b1 = (long long)k * G.unit_bytes[1];
     const long long T = U0 * b0 + (long long)G.tiles1 * b1;
     const long long max_tiles = (G.tiles1 + sms - 1) / sms;
-    Gl.balance = (T / sms >= max_tiles * b1 + 2 * b0) ? 1 : 0;
+    // the grid barrier makes every CTA wait for the slowest one in each phase, so the units of a phase are
+    // split evenly (a split by total bytes would only pay if the kernel were bandwidth-bound throughout)
+    Gl.balance = 0;
+    (void)T;
     if (max_tiles > MAX_TILES) return CACHALOT_EUNSUPPORTED;
   }
   cudaLaunchConfig_t cfg = {};

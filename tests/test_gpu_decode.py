@@ -243,10 +243,10 @@ def test_single_launch_kernel_matches_oracle(kind, dims):
         return total
 
     # With the affine op's rounding points (g, u, h and every expert's output go through bf16) two correct
-    # accumulation orders can land on different sides of a rounding boundary; one bf16 ulp of one expert's
-    # output (2**-8 relative) is then the honest bound.  The arithmetic itself is held to TOL with the
-    # rounding points switched off.
-    tol_op = TOL if kind == "fp4" else 2 ** -8
+    # accumulation orders can land on different sides of a rounding boundary: an output element then
+    # moves by one bf16 ulp (2**-8 relative) of one expert's contribution, and two experts can do so at
+    # the same element.  The arithmetic itself is held to TOL with the rounding points switched off.
+    tol_op = TOL if kind == "fp4" else 2 ** -7
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     xs, ws = bf16_tensor(x), torch.from_numpy(w[None]).cuda()
     got = cb.moe_forward(xs, torch.from_numpy(ids[None]).cuda(), ws, bank, status=status).cpu().numpy()[0]
