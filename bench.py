@@ -35,7 +35,7 @@ SWIGLU_LIMIT = 10.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # capture summarised under profiles/ (None until a capture exists for the workload)
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {("affine2", 1, "fused"): 59817472 + 1118208}
 
 
 def parse_args():
@@ -193,25 +193,7 @@ def workload_config(args, extra):
 # ---- GPU arm --------------------------------------------------------------------------------
 
 def fill_bank(bank, gen):
-    import torch
-
-    kind = bank.fmt.kind
-    step = 64
-    for s0 in range(0, bank.n_slots, step):
-        s1 = min(s0 + step, bank.n_slots)
-        for name in bank.fmt.tensor_names:
-            o, n = bank.offsets[name], bank.tensor_sizes[name]
-            region = bank.slab[s0:s1, o:o + n]
-            if name.endswith("weight"):
-                region.copy_(torch.randint(0, 256, (s1 - s0, n), dtype=torch.uint8, device=bank.slab.device, generator=gen))
-            elif kind == "fp4":
-                region.copy_(torch.randint(118, 124, (s1 - s0, n), dtype=torch.uint8, device=bank.slab.device, generator=gen))
-            elif name.endswith("scales"):
-                v = torch.rand((s1 - s0, n // 2), device=bank.slab.device, generator=gen) * 0.018 + 0.002
-                region.view(torch.float16).copy_(v.to(torch.float16))
-            else:
-                v = torch.randn((s1 - s0, n // 2), device=bank.slab.device, generator=gen) * 0.01
-                region.view(torch.float16).copy_(v.to(torch.float16))
+    bank.fill_random(gen)
 
 
 def run_ours(args):

@@ -167,6 +167,26 @@ class SlabBank:
                 raise ValueError(f"{name}: {src.numel()} bytes, slot expects {self.tensor_sizes[name]}")
             self.view(slot, name).copy_(src)
 
+    def fill_random(self, gen: torch.Generator | None = None, step: int = 64) -> None:
+        """Fills every slot with synthetic weights of the benchmark's distributions: uniform codes; FP4
+        block scales uniform in 2**-9 .. 2**-4; affine scales ~U(0.002, 0.02) and biases ~N(0, 0.01)."""
+        dev = self.slab.device
+        for s0 in range(0, self.n_slots, step):
+            s1 = min(s0 + step, self.n_slots)
+            for name in self.fmt.tensor_names:
+                o, n = self.offsets[name], self.tensor_sizes[name]
+                region = self.slab[s0:s1, o:o + n]
+                if name.endswith("weight"):
+                    region.copy_(torch.randint(0, 256, (s1 - s0, n), dtype=torch.uint8, device=dev, generator=gen))
+                elif self.fmt.kind == "fp4":
+                    region.copy_(torch.randint(118, 124, (s1 - s0, n), dtype=torch.uint8, device=dev, generator=gen))
+                elif name.endswith("scales"):
+                    v = torch.rand((s1 - s0, n // 2), device=dev, generator=gen) * 0.018 + 0.002
+                    region.view(torch.float16).copy_(v.to(torch.float16))
+                else:
+                    v = torch.randn((s1 - s0, n // 2), device=dev, generator=gen) * 0.01
+                    region.view(torch.float16).copy_(v.to(torch.float16))
+
     def expert(self, layer: int, expert: int) -> "ResidentExpert":
         in_range = 0 <= layer < self.layers and 0 <= expert < self.n_experts
         slot = int(self.slot_table_host[layer, expert]) if in_range else -1

@@ -33,9 +33,18 @@
 //                scaled per sub-block by 2**e;  acc += 2**(scale-127) * 2**-e * T.
 #include "kernels.cuh"
 
+#ifndef CB_UNROLL
+#define CB_UNROLL 4
+#endif
+
 namespace cachalot {
 namespace {
 
+constexpr int kUnroll = CB_UNROLL;  // steps of the reduction loop unrolled together
+
+#ifndef CB_UNROLL
+#define CB_UNROLL 4
+#endif
 constexpr int NPROD = 4;                          // producer warps (one issuing lane each; a lane's copies do not overlap)
 constexpr int KMAX = 8;                           // routed experts per token
 constexpr int MAX_TILES = 8;                      // phase-1 output tiles one CTA may own
@@ -385,7 +394,7 @@ __device__ __forceinline__ float2 unit_dot(const uint8_t* stage, const Geo& G, c
     }
     const uint16_t* psA = S + ia + 2 * c_begin;
     const uint16_t* psB = S + ib + 2 * c_begin;
-#pragma unroll 4
+#pragma unroll kUnroll
     for (int c = c_begin; c < c_end; ++c) {
       step_affine<SDT, false>(accA, accB, pa, pbrow, pb, ppx, psA, psB, arr, true);
       pa += 64, pbrow += 64, pb += bstep, ppx += 4, psA += 2, psB += 2;
@@ -395,7 +404,7 @@ __device__ __forceinline__ float2 unit_dot(const uint8_t* stage, const Geo& G, c
     const int nblk = K >> 5;  // E8M0 bytes per row: [rows 0..15][K/32]
     const uint8_t* psA = sc + wr * nblk + t + 4 * c_begin;
     const uint8_t* psB = psA + 8 * nblk;
-#pragma unroll 4
+#pragma unroll kUnroll
     for (int c = c_begin; c < c_end; ++c) {
       step_fp4<false>(accA, accB, pa, pbrow, pb, ppx, psA, psB, true);
       pa += 64, pbrow += 64, pb += bstep, ppx += 4, psA += 4, psB += 4;

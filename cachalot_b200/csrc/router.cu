@@ -78,25 +78,24 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, const float*
     if (rank < k) top[mode == CACHALOT_ROUTER_SQRT_SOFTPLUS ? k - 1 - rank : rank] = t;
   }
   __syncthreads();
-  if (t == 0) {
-    // sum in output order, as both reference kernels do
+  if (t < k) {
+    // one thread per selected expert (the slot lookups are independent loads); every thread adds the
+    // scores up in output order, as both reference kernels do, so all of them hold the same total
     float total = 0.f;
     for (int r = 0; r < k; ++r) total += score[top[r]];
-    float den = total + 1e-20f;
-    for (int r = 0; r < k; ++r) {
-      int e = top[r];
-      float w = score[e];
-      if (mode == CACHALOT_ROUTER_SIGMOID) {
-        w = (w / den) * route_scale;
-      } else {
-        if (norm && k > 1) w = w / den;
-        w = w * route_scale;
-      }
-      if (weights_bf16) w = bf16_round(w);
-      indices[(size_t)row * k + r] = e;
-      weights[(size_t)row * k + r] = w;
-      if (slots) slots[(size_t)row * k + r] = slot_table ? slot_table[(size_t)layer * n_experts + e] : e;
+    const float den = total + 1e-20f;
+    const int e = top[t];
+    float w = score[e];
+    if (mode == CACHALOT_ROUTER_SIGMOID) {
+      w = (w / den) * route_scale;
+    } else {
+      if (norm && k > 1) w = w / den;
+      w = w * route_scale;
     }
+    if (weights_bf16) w = bf16_round(w);
+    indices[(size_t)row * k + t] = e;
+    weights[(size_t)row * k + t] = w;
+    if (slots) slots[(size_t)row * k + t] = slot_table ? slot_table[(size_t)layer * n_experts + e] : e;
   }
 }
 
