@@ -52,6 +52,9 @@ SIGNATURES = {
     "cachalot_route_topk": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "cachalot_moe_decode_workspace_bytes": (_sz, [_desc, _i, _i]),
     "cachalot_moe_decode": (_i, [_vp, _desc, _vp, _vp, _vp, _i, _i, _f, _i, _vp, _sz, _vp, _i, _vp, _vp]),
+    "cachalot_moe_layer_decode_workspace_bytes": (_sz, [_desc, _i]),
+    "cachalot_moe_layer_decode": (_i, [_vp, _desc, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _i, _i, _f, _i, _vp, _sz, _vp, _i,
+                                       _vp, _vp, _vp, _vp]),
     "cachalot_moe_decode_static_scratch_bytes": (_sz, []),
     "cachalot_moe_decode_static": (_i, [_vp, _desc, _vp, _vp, _vp, _i, _i, _f, _i, _vp, _i, _vp, _vp]),
     "cachalot_fp8_act_quant": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp]),

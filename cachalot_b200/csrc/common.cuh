@@ -93,4 +93,27 @@ __device__ __forceinline__ float swiglu(float g, float u, float limit) {
   return g / (1.0f + expf(-g)) * u;
 }
 
+
+// Router score and selection key of one expert (both routers, one arithmetic):
+//   SQRT_SOFTPLUS: score = sqrt(softplus(raw / temp)), key = score + bias (higher first, ties to the larger index)
+//   SIGMOID:       score = sigmoid(raw) as y = 1/(1+exp(|x|)), x < 0 ? y : 1-y;  key = -(score + bias) (lower
+//                  first, ties to the lower index)
+__device__ __forceinline__ void router_score_key(int mode, float raw, float b, float gate_temp, float& score, float& key) {
+  if (mode == CACHALOT_ROUTER_SQRT_SOFTPLUS) {
+    const float s = raw / gate_temp;
+    const float sp = fmaxf(s, 0.f) + logf(1.0f + expf(-fabsf(s)));
+    score = sqrtf(sp);
+    key = score + b;
+  } else {
+    const float y = 1.0f / (1.0f + expf(fabsf(raw)));
+    score = raw < 0.f ? y : 1.0f - y;
+    key = -(score + b);
+  }
+}
+// true when expert (ka, ia) is selected before expert (kb, ib)
+__device__ __forceinline__ bool router_before(int mode, float ka, int ia, float kb, int ib) {
+  if (mode == CACHALOT_ROUTER_SQRT_SOFTPLUS) return ka > kb || (ka == kb && ia > ib);
+  return ka < kb || (ka == kb && ia < ib);
+}
+
 }  // namespace cachalot

@@ -55,5 +55,11 @@ int launch_decode_fused(const BankView& v, const void* x, const int32_t* slots, 
                         cudaStream_t stream);
 size_t decode_fused_workspace_bytes(int hidden, int inter, int rows, int k);
 bool decode_fused_supported(const BankView& v, int rows, int k);
+// ... with the routing tail (scores, top-k, weights, slot lookup) done inside the same launch
+int launch_layer_fused(const BankView& v, const void* x, const float* logits, const float* bias, const int32_t* slot_table,
+                       int layer, int n_experts, int k, int mode, float gate_temp, float route_scale, int norm,
+                       int weights_bf16, float limit, int numerics_flags, void* workspace, void* out, int out_dtype,
+                       int32_t* indices_out, float* weights_out, int* status, cudaStream_t stream);
+bool layer_fused_supported(const BankView& v, int n_experts, int k);
 
 }  // namespace cachalot

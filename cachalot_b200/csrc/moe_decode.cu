@@ -296,6 +296,49 @@ extern "C" int cachalot_moe_decode(const void* bank, const cachalot_bank_desc* d
   return launch_decode<CACHALOT_BANK_AFFINE>(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, numerics, (float*)workspace, out, out_dtype, status, (cudaStream_t)stream);
 }
 
+// ---- decode layer: routing tail + routed experts in one call --------------------------------------
+
+extern "C" size_t cachalot_moe_layer_decode_workspace_bytes(const cachalot_bank_desc* desc, int k) {
+  if (!desc || k <= 0) return 0;
+  return cachalot_moe_decode_workspace_bytes(desc, 1, k) + 1024;  // + indices, weights, slots of the two-call path
+}
+
+extern "C" int cachalot_moe_layer_decode(const void* bank, const cachalot_bank_desc* desc, const void* x_bf16,
+                                         const float* logits, const float* bias, const int32_t* slot_table, int layer,
+                                         int n_experts, int k, int mode, float gate_temp, float route_scale,
+                                         int norm_topk_prob, int weights_bf16, float swiglu_limit, int numerics,
+                                         void* workspace, size_t workspace_bytes, void* out, int out_dtype,
+                                         int32_t* indices_out, float* weights_out, int* status, cachalot_stream_t stream) {
+  BankView v;
+  int rc = make_view(bank, desc, &v, "moe_layer_decode");
+  if (rc) return rc;
+  if (!x_bf16 || !logits || !out) return fail(CACHALOT_EINVAL, "moe_layer_decode: null pointer");
+  if (n_experts <= 0 || n_experts > 1024) return fail(CACHALOT_EINVAL, "moe_layer_decode: E=%d must be in 1..1024", n_experts);
+  if (k < 1 || k > n_experts || k > 32) return fail(CACHALOT_EINVAL, "Invalid topk=%d for %d experts", k, n_experts);
+  if (mode != CACHALOT_ROUTER_SQRT_SOFTPLUS && mode != CACHALOT_ROUTER_SIGMOID)
+    return fail(CACHALOT_EINVAL, "moe_layer_decode: unknown router mode %d", mode);
+  if (layer < 0) return fail(CACHALOT_EINVAL, "moe_layer_decode: bad layer");
+  if ((numerics & 0xff) > CACHALOT_NUMERICS_BF16_H32 || (numerics & ~0xfff)) return fail(CACHALOT_EINVAL, "moe_layer_decode: unknown numerics %d", numerics);
+  if (out_dtype != CACHALOT_F32 && out_dtype != CACHALOT_BF16) return fail(CACHALOT_EINVAL, "moe_layer_decode: out dtype must be f32 or bf16");
+  const size_t need = cachalot_moe_layer_decode_workspace_bytes(desc, k);
+  if (!workspace || workspace_bytes < need) return fail(CACHALOT_ESCRATCH, "moe_layer_decode: workspace %zu < %zu bytes", workspace_bytes, need);
+  if (!aligned(workspace, 256) || !aligned(x_bf16, 16) || !aligned(out, 4)) return fail(CACHALOT_EALIGN, "moe_layer_decode: workspace needs 256-byte, x 16-byte alignment");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (!(numerics & (CACHALOT_DECODE_SIMPLE | CACHALOT_DECODE_UNFUSED)) && layer_fused_supported(v, n_experts, k))
+    return launch_layer_fused(v, x_bf16, logits, bias, slot_table, layer, n_experts, k, mode, gate_temp, route_scale, norm_topk_prob,
+                              weights_bf16, swiglu_limit, numerics, workspace, out, out_dtype, indices_out, weights_out, status, s);
+  // two calls: the routing kernel, then the experts
+  uint8_t* tail = static_cast<uint8_t*>(workspace) + (need - 1024);
+  int32_t* idx = indices_out ? indices_out : reinterpret_cast<int32_t*>(tail);
+  float* w = weights_out ? weights_out : reinterpret_cast<float*>(tail + 256);
+  int32_t* slots = reinterpret_cast<int32_t*>(tail + 512);
+  rc = cachalot_route_topk(logits, bias, slot_table, layer, 1, n_experts, k, mode, gate_temp, route_scale, norm_topk_prob,
+                           weights_bf16, idx, w, slots, nullptr, stream);
+  if (rc) return rc;
+  return cachalot_moe_decode(bank, desc, x_bf16, slots, w, 1, k, swiglu_limit, numerics, workspace, need - 1024, out, out_dtype,
+                             status, stream);
+}
+
 // ---- prefill -------------------------------------------------------------------------------
 
 namespace cachalot {

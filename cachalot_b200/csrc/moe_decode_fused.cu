@@ -87,6 +87,17 @@ __device__ __forceinline__ unsigned long long gtimer() {
 // their barrier at the same time because a launch holds every SM until it has passed its own.
 __device__ unsigned grid_bar_word;
 
+// Routing done inside the kernel (logits == nullptr: the caller passes slots and weights instead).
+struct RouteArgs {
+  const float* logits;        // f32 [E]
+  const float* bias;          // f32 [E] or null
+  const int32_t* slot_table;  // i32 [layers, E] or null (slot = expert id)
+  int32_t* indices_out;       // i32 [k] or null
+  float* weights_out;         // f32 [k] or null
+  int layer, n_experts, mode, norm, weights_bf16;
+  float gate_temp, route_scale;
+};
+
 struct Geo {
   int K[2];           // reduction length: hidden, inter
   int nsteps[2];      // steps along K (the last may be partial)
@@ -416,7 +427,7 @@ __device__ __forceinline__ float2 unit_dot(const uint8_t* stage, const Geo& G, c
 
 template <int FMT, int SDT, typename OutT>
 __global__ void __launch_bounds__(Fm<FMT>::NTHREADS, 1)
-fused_decode_kernel(BankView bank, Geo G, const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ slots,
+fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ slots,
                     const float* __restrict__ gate_w, int k, float limit, int numerics, float* __restrict__ hidden,
                     OutT* __restrict__ out, int* __restrict__ status) {
   constexpr int SUB = Fm<FMT>::SUB, NCW = Fm<FMT>::NCW, NCT = NCW * 32;
@@ -454,15 +465,90 @@ fused_decode_kernel(BankView bank, Geo G, const __nv_bfloat16* __restrict__ x, c
       }
     }
   }
+  // routing inside the kernel: every CTA selects the top-k itself (same arithmetic and tie rules as
+  // route_topk_kernel), so no launch and no round trip through global memory sits before the first copy
+  uint32_t* r_ord = reinterpret_cast<uint32_t*>(smem + G.off_act + G.act_stride[0]);  // scratch behind x in the operand area
+  float* r_score = reinterpret_cast<float*>(r_ord + 1024);
+  int32_t* r_slot = reinterpret_cast<int32_t*>(r_ord + 2048);
+  if (R.logits) {
+    for (int e = threadIdx.x; e < R.n_experts; e += blockDim.x) {
+      // the three loads are independent: one round trip to L2 for the whole routing tail
+      const float raw = R.logits[e];
+      const float b = R.bias ? R.bias[e] : 0.f;
+      const int32_t sl = R.slot_table ? R.slot_table[(size_t)R.layer * R.n_experts + e] : e;
+      float sc, ky;
+      router_score_key(R.mode, raw, b, R.gate_temp, sc, ky);
+      // "better" as an unsigned order: the sigmoid router prefers the lower key, the other the higher
+      const uint32_t u = __float_as_uint(R.mode == CACHALOT_ROUTER_SIGMOID ? -ky : ky);
+      r_ord[e] = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+      r_score[e] = sc, r_slot[e] = sl;
+    }
+    __syncthreads();
+  }
   // warp 0: the present experts in routing order; its lane 0: the barriers
   if (warp == 0) {
     int my_slot = -1;
-    if (lane < k) my_slot = slots[lane];
+    float my_w = 0.f;
+    if (R.logits) {
+      // k rounds of a warp-wide arg-best.  Lane l keeps experts l, l + 32, ... in registers; a taken expert's
+      // order drops to 0 (below every real one).  Ties: the sigmoid router prefers the lower index, the other
+      // the larger one, as route_topk_kernel does.
+      const bool low_wins = R.mode == CACHALOT_ROUTER_SIGMOID;
+      const bool ascending = !low_wins;  // the sqrt-softplus router writes the weakest first
+      uint32_t ord[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) ord[i] = (i * 32 + lane < R.n_experts) ? r_ord[i * 32 + lane] : 0u;
+      int my_e = -1;
+      for (int r = 0; r < k; ++r) {
+        uint32_t bo = 0u;
+        int bi = -1;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const bool better = low_wins ? ord[i] > bo : (ord[i] >= bo && ord[i] != 0u);
+          if (better) bo = ord[i], bi = i * 32 + lane;
+        }
+        const uint32_t wo = __reduce_max_sync(0xffffffffu, bo);
+        const bool cand = bo == wo && bi >= 0;
+        const int win = low_wins ? (int)__reduce_min_sync(0xffffffffu, cand ? (unsigned)bi : 0x7fffffffu)
+                                 : (int)__reduce_max_sync(0xffffffffu, cand ? (unsigned)(bi + 1) : 0u) - 1;
+        if (wo == 0u) break;  // fewer than k experts
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i * 32 + lane == win) ord[i] = 0u;
+        if (lane == (ascending ? k - 1 - r : r)) my_e = win;
+      }
+      // lane r holds output position r; the total is added up in output order as route_topk_kernel does
+      float total = 0.f;
+      for (int r = 0; r < k; ++r) {
+        const int e = __shfl_sync(0xffffffffu, my_e, r);
+        total += e >= 0 ? r_score[e] : 0.f;
+      }
+      if (lane < k && my_e >= 0) {
+        const float den = total + 1e-20f;
+        float w = r_score[my_e];
+        if (R.mode == CACHALOT_ROUTER_SIGMOID) {
+          w = (w / den) * R.route_scale;
+        } else {
+          if (R.norm && k > 1) w = w / den;
+          w = w * R.route_scale;
+        }
+        if (R.weights_bf16) w = bf16_round(w);
+        my_w = w;
+        my_slot = r_slot[my_e];
+        if (blockIdx.x == 0) {
+          if (R.indices_out) R.indices_out[lane] = my_e;
+          if (R.weights_out) R.weights_out[lane] = w;
+        }
+      }
+    } else if (lane < k) {
+      my_slot = slots[lane];
+      my_w = gate_w[lane];
+    }
     const bool present = my_slot >= 0 && my_slot < bank.n_slots;
     const unsigned pmask = __ballot_sync(0xffffffffu, present);
     if (present) {
       const int p = __popc(pmask & ((1u << lane) - 1u));
-      s_route[p] = lane, s_slot[p] = my_slot, s_gw[p] = gate_w[lane];
+      s_route[p] = lane, s_slot[p] = my_slot, s_gw[p] = my_w;
     }
     const bool oob = lane < k && my_slot >= bank.n_slots;
     if (__any_sync(0xffffffffu, oob) && lane == 0 && blockIdx.x == 0 && status) atomicOr(status, CACHALOT_STATUS_SLOT_RANGE);
@@ -777,9 +863,9 @@ size_t decode_fused_workspace_bytes(int hidden, int inter, int rows, int k) {
 }
 
 template <int FMT>
-static int launch_fused_fmt(const BankView& v, const Geo& G, const void* x, const int32_t* slots, const float* gate_w, int k,
-                            float limit, int numerics, void* workspace, void* out, int out_dtype, int* status,
-                            cudaStream_t stream) {
+static int launch_fused_fmt(const BankView& v, const Geo& G, const RouteArgs& R, const void* x, const int32_t* slots,
+                            const float* gate_w, int k, float limit, int numerics, void* workspace, void* out, int out_dtype,
+                            int* status, cudaStream_t stream) {
   float* hidden = static_cast<float*>(workspace);
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
@@ -811,7 +897,7 @@ static int launch_fused_fmt(const BankView& v, const Geo& G, const void* x, cons
   cudaError_t e = cudaSuccess;
   auto go = [&](auto kern, auto* outp) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT - 256);
-    if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, v, Gl, xb, slots, gate_w, k, limit, numerics, hidden, outp, status);
+    if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, v, Gl, R, xb, slots, gate_w, k, limit, numerics, hidden, outp, status);
   };
   const bool bf16_scales = FMT == CACHALOT_BANK_AFFINE && v.scale_dtype == CACHALOT_BF16;
   if (out_dtype == CACHALOT_BF16) {
@@ -831,9 +917,35 @@ int launch_decode_fused(const BankView& v, const void* x, const int32_t* slots, 
   Geo G;
   if (rows != 1 || !make_geo(v, k, &G)) return CACHALOT_EUNSUPPORTED;
   const int numerics = numerics_flags & 0xff;
+  const RouteArgs R = {};
   if (v.format == CACHALOT_BANK_FP4)
-    return launch_fused_fmt<CACHALOT_BANK_FP4>(v, G, x, slots, gate_w, k, limit, numerics, workspace, out, out_dtype, status, stream);
-  return launch_fused_fmt<CACHALOT_BANK_AFFINE>(v, G, x, slots, gate_w, k, limit, numerics, workspace, out, out_dtype, status, stream);
+    return launch_fused_fmt<CACHALOT_BANK_FP4>(v, G, R, x, slots, gate_w, k, limit, numerics, workspace, out, out_dtype, status, stream);
+  return launch_fused_fmt<CACHALOT_BANK_AFFINE>(v, G, R, x, slots, gate_w, k, limit, numerics, workspace, out, out_dtype, status, stream);
+}
+
+// The same launch with the routing tail inside: logits -> top-k -> slots, then the experts.
+int launch_layer_fused(const BankView& v, const void* x, const float* logits, const float* bias, const int32_t* slot_table,
+                       int layer, int n_experts, int k, int mode, float gate_temp, float route_scale, int norm,
+                       int weights_bf16, float limit, int numerics_flags, void* workspace, void* out, int out_dtype,
+                       int32_t* indices_out, float* weights_out, int* status, cudaStream_t stream) {
+  Geo G;
+  if (!make_geo(v, k, &G) || n_experts > 1024) return CACHALOT_EUNSUPPORTED;
+  if (G.act_stride[1] * k < G.act_stride[0] + 12288) return CACHALOT_EUNSUPPORTED;  // the routing scratch sits behind x in the operand area
+  const int numerics = numerics_flags & 0xff;
+  RouteArgs R = {};
+  R.logits = logits, R.bias = bias, R.slot_table = slot_table, R.indices_out = indices_out, R.weights_out = weights_out;
+  R.layer = layer, R.n_experts = n_experts, R.mode = mode, R.norm = norm, R.weights_bf16 = weights_bf16;
+  R.gate_temp = gate_temp, R.route_scale = route_scale;
+  if (v.format == CACHALOT_BANK_FP4)
+    return launch_fused_fmt<CACHALOT_BANK_FP4>(v, G, R, x, nullptr, nullptr, k, limit, numerics, workspace, out, out_dtype, status, stream);
+  return launch_fused_fmt<CACHALOT_BANK_AFFINE>(v, G, R, x, nullptr, nullptr, k, limit, numerics, workspace, out, out_dtype, status, stream);
+}
+
+bool layer_fused_supported(const BankView& v, int n_experts, int k) {
+  Geo G;
+  if (k < 1 || k > KMAX || n_experts < k || n_experts > 1024) return false;
+  if (v.format == CACHALOT_BANK_AFFINE && (v.group != 128 || v.bits != 2)) return false;
+  return make_geo(v, k, &G) && G.act_stride[1] * k >= G.act_stride[0] + 12288;
 }
 
 }  // namespace cachalot

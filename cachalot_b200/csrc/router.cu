@@ -47,16 +47,7 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, const float*
   if (t < n_experts) {
     float raw = logits[(size_t)row * n_experts + t];
     float b = bias ? bias[t] : 0.f;
-    if (mode == CACHALOT_ROUTER_SQRT_SOFTPLUS) {
-      float s = raw / gate_temp;
-      float sp = fmaxf(s, 0.f) + logf(1.0f + expf(-fabsf(s)));
-      my_score = sqrtf(sp);
-      my_key = my_score + b;
-    } else {
-      float y = 1.0f / (1.0f + expf(fabsf(raw)));
-      my_score = raw < 0.f ? y : 1.0f - y;
-      my_key = -(my_score + b);
-    }
+    router_score_key(mode, raw, b, gate_temp, my_score, my_key);
     key[t] = my_key;
     score[t] = my_score;
     if (scores_out) scores_out[(size_t)row * n_experts + t] = my_score;

@@ -210,6 +210,51 @@ def moe_forward(x: torch.Tensor, slot_ids: torch.Tensor, gate_weights: torch.Ten
     return out
 
 
+def moe_layer_decode(x: torch.Tensor, logits: torch.Tensor, bank: SlabBank, *, layer: int = 0, topk: int = 6,
+                     bias: torch.Tensor | None = None, table: torch.Tensor | None = None, router: str = "sigmoid",
+                     gate_temp: float = 1.0, route_scale: float = 1.0, norm_topk_prob: bool = True, weights_bf16: bool = False,
+                     swiglu_limit: float = 10.0, numerics: str | None = None, out_dtype=torch.float32,
+                     out: torch.Tensor | None = None, status: torch.Tensor | None = None,
+                     workspace: torch.Tensor | None = None, want_routing: bool = False):
+    """Routing tail + routed experts of one decode token as ONE launch: the GPU-side form of the routed half
+    of `moe_layer_forward` (model/moe_layer_metal.py:133-405) with slot selection on the device as in
+    minimax/gpu_select.py:330-551.  x bf16 [H]; logits float32 [E] (gate output); `table` int32 [layers,E]
+    (default: the bank's slot table); router "sigmoid" (route_tail rules) or "sqrt_softplus" (route_topk rules).
+    Returns out [H], or (out, indices int32 [k], weights float32 [k]) with want_routing."""
+    _need_cuda(x, logits)
+    if x.dim() != 1 or x.numel() != bank.hidden:
+        raise ValueError(f"x must be 1-D with {bank.hidden} elements, got {tuple(x.shape)}")
+    if logits.dim() != 1:
+        raise ValueError(f"logits must be 1-D [E], got {tuple(logits.shape)}")
+    e = logits.numel()
+    if not 1 <= topk <= e:
+        raise ValueError(f"Invalid topk={topk} for {e} experts")
+    if bias is not None and tuple(bias.shape) != (e,):
+        raise ValueError(f"bias shape {tuple(bias.shape)} != ({e},)")
+    mode = {"sigmoid": _lib.ROUTER_SIGMOID, "sqrt_softplus": _lib.ROUTER_SQRT_SOFTPLUS}[router]
+    if numerics is None:
+        numerics = "f32" if bank.fmt.kind == "fp4" else "bf16"
+    num = {"f32": _lib.NUMERICS_F32, "bf16": _lib.NUMERICS_BF16, "bf16_h32": _lib.NUMERICS_BF16_H32}[numerics]
+    if table is None:
+        table = bank.slot_table
+    xb = x.to(torch.bfloat16).contiguous()
+    lg = logits.to(torch.float32).contiguous()
+    b = None if bias is None else bias.to(torch.float32).contiguous()
+    odt = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}[out_dtype]
+    if out is None:
+        out = torch.empty(bank.hidden, dtype=out_dtype, device=x.device)
+    idx = torch.empty(topk, dtype=torch.int32, device=x.device) if want_routing else None
+    w = torch.empty(topk, dtype=torch.float32, device=x.device) if want_routing else None
+    need = lib.cachalot_moe_layer_decode_workspace_bytes(bank.desc_ptr, topk)
+    ws = workspace if workspace is not None else _workspace(x.device, need + 256)
+    base = (ws.data_ptr() + 255) // 256 * 256
+    check(lib.cachalot_moe_layer_decode(_ptr(bank.slab), bank.desc_ptr, _ptr(xb), _ptr(lg), _ptr(b), _ptr(table.contiguous()), int(layer),
+                                        e, int(topk), mode, float(gate_temp), float(route_scale), int(norm_topk_prob),
+                                        int(weights_bf16), float(swiglu_limit), num, base, ws.numel() - (base - ws.data_ptr()),
+                                        _ptr(out), odt, _ptr(idx), _ptr(w), _ptr(status), _stream()))
+    return (out, idx, w) if want_routing else out
+
+
 def _slots_of(experts) -> tuple[SlabBank, torch.Tensor]:
     if len(experts) == 0:
         raise ValueError("no experts given")

@@ -148,6 +148,23 @@ CACHALOT_API int cachalot_moe_decode(const void* bank, const cachalot_bank_desc*
                         int numerics, void* workspace, size_t workspace_bytes, void* out, int out_dtype,
                         int* status, cachalot_stream_t stream);
 
+/* Replaces the routed half of model/moe_layer_metal.py:133-405 moe_layer_forward for one decode token
+ * without its host round trip (router -> mx.eval -> store.get_many -> experts, :279-355), in the way
+ * minimax/gpu_select.py:330-551 keeps slot selection on the GPU: the routing tail of
+ * cachalot_route_topk (same modes, tie rules and weight formulas) runs inside the expert kernel's
+ * prologue, so a layer is one launch.  logits f32 [E]; bias f32 [E] or NULL; slot_table i32
+ * [layers,E] or NULL; x bf16 [H]; out [H].  indices_out i32 [k] / weights_out f32 [k] (either may
+ * be NULL) receive the routing result.  k <= 8 runs as one launch; otherwise (and for bank shapes
+ * the single-launch kernel does not cover) the call issues the routing kernel and
+ * cachalot_moe_decode. */
+CACHALOT_API size_t cachalot_moe_layer_decode_workspace_bytes(const cachalot_bank_desc* desc /* host */, int k);
+CACHALOT_API int cachalot_moe_layer_decode(const void* bank, const cachalot_bank_desc* desc /* host */, const void* x_bf16,
+                              const float* logits, const float* bias, const int32_t* slot_table, int layer,
+                              int n_experts, int k, int mode, float gate_temp, float route_scale, int norm_topk_prob,
+                              int weights_bf16, float swiglu_limit, int numerics, void* workspace,
+                              size_t workspace_bytes, void* out, int out_dtype, int32_t* indices_out,
+                              float* weights_out, int* status, cachalot_stream_t stream);
+
 /* No counterpart in the reference.  The same computation as cachalot_moe_decode for callers that
  * must not allocate device memory and have no workspace to hand over: an embedding whose memory
  * pool already owns all of HBM (a cudaMalloc there fails, or forces a device-wide

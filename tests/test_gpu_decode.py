@@ -266,6 +266,45 @@ def test_single_launch_kernel_matches_oracle(kind, dims):
     assert max_rel(got_b, got) < 2 ** -8
 
 
+@pytest.mark.parametrize("kind", ["fp4", "affine"])
+@pytest.mark.parametrize("router_mode", ["sigmoid", "sqrt_softplus"])
+def test_layer_decode_one_launch_equals_route_then_experts(kind, router_mode):
+    """Routing inside the expert kernel: indices equal the oracle's (bit-exact), weights and the layer output equal
+    the two-step path (routing kernel, then the experts) bit for bit, including an expert that is not resident."""
+    import cachalot_b200 as cb
+    hidden, inter, n_exp, k = 1024, 704, 40, 6
+    rng = np.random.default_rng(99)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    fmt = cb.FP4_FORMAT if kind == "fp4" else cb.affine_format(hidden, inter)
+    bank = cb.SlabBank(fmt, hidden, inter, n_exp, layers=1, n_experts=n_exp)
+    bank.fill_random(g)
+    logits = rng.standard_normal(n_exp).astype(np.float32)
+    logits[7] = logits[3]                                   # a tie inside the candidate set
+    bias = (rng.standard_normal(n_exp) * 0.1).astype(np.float32)
+    x = bf16_tensor(rng.standard_normal(hidden).astype(np.float32))
+    table = bank.slot_table.clone()
+    scale = 1.5
+    if router_mode == "sigmoid":
+        want_idx, want_w, _ = router.route_tail(logits, bias, np.arange(n_exp, dtype=np.int32)[None], 0, k, scale, weights_bf16=False)
+    else:
+        want_idx, want_w = router.topk_from_scores_r1(router.sqrt_softplus_scores(logits, 1.0), bias, topk=k, route_scale=scale,
+                                                      norm_topk_prob=True)
+    table[0, int(want_idx[2])] = -1                          # the third selected expert is not resident
+    lg, bs = torch.from_numpy(logits).cuda(), torch.from_numpy(bias).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out, idx, w = cb.moe_layer_decode(x, lg, bank, layer=0, topk=k, bias=bs, table=table, router=router_mode, route_scale=scale,
+                                      status=status, want_routing=True)
+    assert int(status.item()) == 0
+    assert idx.cpu().numpy().tolist() == [int(i) for i in want_idx]
+    assert np.allclose(w.cpu().numpy(), want_w, rtol=2e-6, atol=0)
+    # two-step path through the C ABI's routing kernel
+    mode = cb.ops._lib.ROUTER_SIGMOID if router_mode == "sigmoid" else cb.ops._lib.ROUTER_SQRT_SOFTPLUS
+    idx2, w2, slots2, _ = cb.ops._route(lg[None], bs, table, 0, k, mode, 1.0, scale, True, False, False)
+    assert torch.equal(idx2[0], idx) and torch.equal(w2[0], w)
+    two = cb.moe_forward(x[None], slots2, w2, bank)[0]
+    assert torch.equal(two, out)
+
+
 def test_fp4_scale_window_and_calibration():
     """Block scales far from the default centre: the grouped (two-launch) kernels hold scales relative to
     a centre in f16 and need the bank calibrated; the single-launch kernel applies every E8M0 scale in
