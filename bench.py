@@ -49,6 +49,7 @@ def parse_args():
     p.add_argument("--distinct-layers", type=int, default=8)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-graph", action="store_true")
+    p.add_argument("--watchdog", type=int, default=0, help="dump all Python stacks and exit after this many seconds (0 = off)")
     return p.parse_args()
 
 
@@ -196,6 +197,18 @@ def fill_bank(bank, gen):
     bank.fill_random(gen)
 
 
+def _leave(world: int) -> None:
+    """End of a multi-rank run.  The captured CUDA graphs still hold NCCL work; tearing the process group
+    down with them alive blocks, so a rank that has printed (or has nothing to print) leaves at once."""
+    if world > 1:
+        import torch
+
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -339,8 +352,7 @@ def run_ours(args):
     st = int(status.item())
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        _leave(world)
         return
 
     sizes = bank.tensor_sizes
@@ -396,12 +408,15 @@ def run_ours(args):
                                 "sample": f"3 timed passes of one MoE layer (6 routed experts from packed bytes, numpy), {dt:.2f} s each; "
                                           f"a token = {LAYERS} passes"}
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    _leave(world)
 
 
 def main():
     args = parse_args()
+    if args.watchdog > 0:
+        import faulthandler
+
+        faulthandler.dump_traceback_later(args.watchdog, exit=True)
     if args.impl == "reference":
         run_reference(args)
     else:
