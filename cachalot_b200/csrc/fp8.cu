@@ -40,78 +40,140 @@ __global__ void act_quant_kernel(const __nv_bfloat16* __restrict__ x, int rows, 
   if (lane == 0) scales[warp] = scale;
 }
 
-// four E4M3 codes -> four floats; the two NaN encodings (0x7F, 0xFF) read as zero like the
-// reference's decode table
-__device__ __forceinline__ void e4m3x4_to_f32(uint32_t w, float* o) {
-  uint32_t nan_mask = __vcmpeq4(w & 0x7F7F7F7Fu, 0x7F7F7F7Fu);
-  w &= ~nan_mask;
-  __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w & 0xffffu), __NV_E4M3);
-  __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w >> 16), __NV_E4M3);
-  float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo));
-  float2 b = __half22float2(*reinterpret_cast<__half2*>(&hi));
-  o[0] = a.x;
-  o[1] = a.y;
-  o[2] = b.x;
-  o[3] = b.y;
+// ---- GEMV on the tensor cores -------------------------------------------------------------------
+// Both operands are E4M3 codes, so the products can be formed by mma.sync.m16n8k32.e4m3 (exact in
+// fp32) without decoding anything: weight bytes go from global memory straight into the A operand.
+//   CTA  = 16 output rows (the MMA's M), KS warps (4, 8 or 16: enough to put ~12 warps on every SM) that each
+//          take a slice of K, partial sums added through shared memory at the end
+//   lane = (g, t): loads 8 bytes of rows g and g+8 per step; the quad covers 32 consecutive K = one
+//          MMA, and never straddles a scale block (32 or 128)
+//   N    = eight tokens per MMA (token g of the group in operand column g); more tokens loop over
+//          groups of eight with the weight registers reused
+// Per scale block the fp32 partial sum of the block is multiplied by act_scale * weight_scale and
+// added to the row's accumulator: the reference's scale placement (model/fp8_ref.py:208-229).
+constexpr int GEMV_MAX_TG = 8;   // token groups of eight handled by one launch (64 tokens)
+
+__device__ __forceinline__ uint32_t e4m3x4_nan_to_zero(uint32_t w) {  // the codes 0x7F / 0xFF read as zero
+  return w & ~__vcmpeq4(w & 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+}
+__device__ __forceinline__ void qmma_e4m3(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-constexpr int GEMV_WARPS = 8;
+template <int NTG, int BLOCK, int KS, typename OutT>
+__global__ void __launch_bounds__(KS * 32)
+fp8_gemv_mma_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ act_scales,
+                    const uint8_t* __restrict__ weight, const void* __restrict__ w_scales, int scale_rule, int rows,
+                    int n_out, int k, OutT* __restrict__ out) {
+  constexpr int MPB = BLOCK / 32;  // MMAs per scale block
+  constexpr int UNR = BLOCK == 32 ? 8 : 2;  // scale blocks in flight: sixteen 8-byte weight loads per lane either way
+  __shared__ float red[KS][NTG][4][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * 16;
+  const int nkb = k / BLOCK;
+  // this warp's scale blocks
+  const int kb_lo = nkb * warp / KS, kb_hi = nkb * (warp + 1) / KS;
+  // rows past the end read the last row; their results are not stored
+  const int ra = min(n0 + g, n_out - 1), rb = min(n0 + g + 8, n_out - 1);
+  const uint8_t* wa = weight + (size_t)ra * k + t * 8;
+  const uint8_t* wb = weight + (size_t)rb * k + t * 8;
+  // weight scales: rows n0 .. n0+15 share a scale row when BLOCK is a multiple of 16 (it is: 32 or 128)
+  const size_t srow = (size_t)(n0 / BLOCK) * nkb;
+  // tokens of this lane: operand column g of group tg is token tg*8 + g; accumulator columns 2t, 2t+1
+  const uint8_t* cb[NTG];
+  bool tok_ok[NTG];
+#pragma unroll
+  for (int tg = 0; tg < NTG; ++tg) {
+    const int tok = tg * 8 + g;
+    tok_ok[tg] = tok < rows;
+    cb[tg] = codes + (size_t)(tok_ok[tg] ? tok : 0) * k + t * 8;
+  }
+  float acc[NTG][4];
+#pragma unroll
+  for (int tg = 0; tg < NTG; ++tg) acc[tg][0] = acc[tg][1] = acc[tg][2] = acc[tg][3] = 0.f;
 
-// grid = (ceil(N / 8), rows): one warp per (token, output row).  Activations are decoded once
-// per CTA into shared memory (16-element chunks, chunk-transposed); each lane multiplies its
-// 16-byte weight chunks and applies act_scale * weight_scale of the chunk's K-block to the
-// chunk's partial sum before accumulating, which is the reference's per-block scale placement.
-template <typename OutT>
-__global__ void __launch_bounds__(GEMV_WARPS * 32)
-fp8_gemv_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ act_scales,
-                const uint8_t* __restrict__ weight, const void* __restrict__ w_scales, int scale_rule, int block,
-                int n_out, int k, OutT* __restrict__ out) {
-  extern __shared__ float smem[];
-  const int nch = k / 16, nkb = k / block;
-  float* xs = smem;             // [16][nch]
-  float* as = smem + k;         // [nkb]
-  const int t = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t* crow = reinterpret_cast<const uint32_t*>(codes + (size_t)t * k);
-  for (int w = threadIdx.x; w < k / 4; w += blockDim.x) {
-    float f[4];
-    e4m3x4_to_f32(crow[w], f);
+#pragma unroll UNR
+  for (int kb = kb_lo; kb < kb_hi; ++kb) {
+    float d[NTG][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      int e = w * 4 + i;
-      xs[(e & 15) * nch + (e >> 4)] = f[i];
+    for (int tg = 0; tg < NTG; ++tg) d[tg][0] = d[tg][1] = d[tg][2] = d[tg][3] = 0.f;
+#pragma unroll
+    for (int m = 0; m < MPB; ++m) {
+      const int ko = kb * BLOCK + m * 32;
+      const uint2 va = ld_stream_u2(wa + ko), vb = ld_stream_u2(wb + ko);
+      const uint32_t a0 = e4m3x4_nan_to_zero(va.x), a2 = e4m3x4_nan_to_zero(va.y);
+      const uint32_t a1 = e4m3x4_nan_to_zero(vb.x), a3 = e4m3x4_nan_to_zero(vb.y);
+#pragma unroll
+      for (int tg = 0; tg < NTG; ++tg) {
+        uint2 b = make_uint2(0u, 0u);
+        if (tok_ok[tg]) b = __ldg(reinterpret_cast<const uint2*>(cb[tg] + ko));
+        qmma_e4m3(d[tg], a0, a1, a2, a3, b.x, b.y);
+      }
+    }
+    const float ws = scale_rule == CACHALOT_SCALE_E8M0 ? e8m0_to_f32(reinterpret_cast<const uint8_t*>(w_scales)[srow + kb])
+                                                        : reinterpret_cast<const float*>(w_scales)[srow + kb];
+#pragma unroll
+    for (int tg = 0; tg < NTG; ++tg) {
+      const int t0 = tg * 8 + 2 * t;
+      const float s0 = (t0 < rows ? act_scales[(size_t)t0 * nkb + kb] : 0.f) * ws;
+      const float s1 = (t0 + 1 < rows ? act_scales[(size_t)(t0 + 1) * nkb + kb] : 0.f) * ws;
+      acc[tg][0] = fmaf(d[tg][0], s0, acc[tg][0]);
+      acc[tg][1] = fmaf(d[tg][1], s1, acc[tg][1]);
+      acc[tg][2] = fmaf(d[tg][2], s0, acc[tg][2]);
+      acc[tg][3] = fmaf(d[tg][3], s1, acc[tg][3]);
     }
   }
-  for (int b = threadIdx.x; b < nkb; b += blockDim.x) as[b] = act_scales[(size_t)t * nkb + b];
+  // add the K quarters (fixed order) and store
+#pragma unroll
+  for (int tg = 0; tg < NTG; ++tg)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) red[warp][tg][i][lane] = acc[tg][i];
   __syncthreads();
-  const int n = blockIdx.x * GEMV_WARPS + warp;
-  if (n >= n_out) return;
-  const uint8_t* wrow = weight + (size_t)n * k;
-  const size_t srow = (size_t)(n / block) * nkb;
-  float acc = 0.f;
-  for (int c = lane; c < nch; c += 32) {
-    uint4 v = ld_stream_u4(wrow + (size_t)c * 16);
-    uint32_t words[4] = {v.x, v.y, v.z, v.w};
-    float part = 0.f;
+  if (warp == 0) {
 #pragma unroll
-    for (int wi = 0; wi < 4; ++wi) {
-      float f[4];
-      e4m3x4_to_f32(words[wi], f);
+    for (int tg = 0; tg < NTG; ++tg) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) part = fmaf(f[i], xs[(wi * 4 + i) * nch + c], part);
+      for (int i = 0; i < 4; ++i) {
+        float v = red[0][tg][i][lane];
+#pragma unroll
+        for (int w = 1; w < KS; ++w) v += red[w][tg][i][lane];
+        const int tok = tg * 8 + 2 * t + (i & 1), row = n0 + g + (i >> 1) * 8;
+        if (tok < rows && row < n_out) {
+          if constexpr (sizeof(OutT) == 2)
+            out[(size_t)tok * n_out + row] = __float2bfloat16_rn(v);
+          else
+            out[(size_t)tok * n_out + row] = v;
+        }
+      }
     }
-    const int kb = (c * 16) / block;
-    float ws = scale_rule == CACHALOT_SCALE_E8M0 ? e8m0_to_f32(reinterpret_cast<const uint8_t*>(w_scales)[srow + kb])
-                                                 : reinterpret_cast<const float*>(w_scales)[srow + kb];
-    acc = fmaf(part, as[kb] * ws, acc);
   }
-  acc = warp_sum(acc);
-  if (lane == 0) {
-    if constexpr (sizeof(OutT) == 2)
-      out[(size_t)t * n_out + n] = __float2bfloat16_rn(acc);
-    else
-      out[(size_t)t * n_out + n] = acc;
+}
+
+template <int BLOCK, typename OutT>
+static void launch_gemv_mma(int ntg, dim3 grid, cudaStream_t s, const uint8_t* codes, const float* act_scales, const uint8_t* weight,
+                            const void* w_scales, int scale_rule, int rows, int n, int k, OutT* out) {
+  // warps per CTA: about twelve warps per SM in total (the reduction buffer limits it for many tokens)
+  int sms = 148, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long tiles = grid.x;
+  int ks = 4;
+  if (tiles * 4 < 12LL * sms && ntg <= 4) ks = 8;
+  if (tiles * 8 < 12LL * sms && ntg <= 2) ks = 16;
+#define CACHALOT_GEMV(NTGV, KSV) \
+  fp8_gemv_mma_kernel<NTGV, BLOCK, KSV, OutT><<<grid, KSV * 32, 0, s>>>(codes, act_scales, weight, w_scales, scale_rule, rows, n, k, out)
+  if (ntg == 1) {
+    if (ks == 16) CACHALOT_GEMV(1, 16); else if (ks == 8) CACHALOT_GEMV(1, 8); else CACHALOT_GEMV(1, 4);
+  } else if (ntg == 2) {
+    if (ks == 16) CACHALOT_GEMV(2, 16); else if (ks == 8) CACHALOT_GEMV(2, 8); else CACHALOT_GEMV(2, 4);
+  } else if (ntg <= 4) {
+    if (ks == 8) CACHALOT_GEMV(4, 8); else CACHALOT_GEMV(4, 4);
+  } else {
+    CACHALOT_GEMV(8, 4);
   }
+#undef CACHALOT_GEMV
 }
 
 }  // namespace cachalot
@@ -141,23 +203,27 @@ extern "C" int cachalot_fp8_gemv(const uint8_t* codes, const float* act_scales, 
   if (!codes || !act_scales || !weight || !w_scales || !out) return fail(CACHALOT_EINVAL, "fp8_gemv: null pointer");
   if (block != 32 && block != 128) return fail(CACHALOT_EUNSUPPORTED, "fp8_gemv: block=%d (32 or 128)", block);
   if (rows < 0 || n <= 0 || k <= 0 || k % block) return fail(CACHALOT_EINVAL, "K=%d is not divisible by %d", k, block);
-  if (rows > 65535) return fail(CACHALOT_EINVAL, "fp8_gemv: rows=%d exceeds 65535", rows);
   if (scale_rule != CACHALOT_SCALE_E8M0 && scale_rule != CACHALOT_SCALE_F32) return fail(CACHALOT_EINVAL, "fp8_gemv: unknown scale rule");
   if (out_dtype != CACHALOT_BF16 && out_dtype != CACHALOT_F32) return fail(CACHALOT_EINVAL, "fp8_gemv: out dtype must be bf16 or f32");
-  if (!aligned(weight, 16) || !aligned(codes, 4)) return fail(CACHALOT_EALIGN, "fp8_gemv: weight needs 16-byte, codes 4-byte alignment");
+  if (!aligned(weight, 8) || !aligned(codes, 8) || k % 8) return fail(CACHALOT_EALIGN, "fp8_gemv: weight and codes need 8-byte alignment");
   if (rows == 0) return CACHALOT_OK;
-  size_t smem = (size_t)k * 4 + (size_t)(k / block) * 4;
-  if (smem > 200 * 1024) return fail(CACHALOT_EINVAL, "fp8_gemv: K=%d too large", k);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(fp8_gemv_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    cudaFuncSetAttribute(fp8_gemv_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    attr_done = true;
+  cudaStream_t s = (cudaStream_t)stream;
+  const dim3 grid((n + 15) / 16);
+  // 64 tokens per launch; more tokens take more launches over the same weights
+  for (int r0 = 0; r0 < rows; r0 += 8 * GEMV_MAX_TG) {
+    const int nr = rows - r0 < 8 * GEMV_MAX_TG ? rows - r0 : 8 * GEMV_MAX_TG;
+    const int ntg = (nr + 7) / 8;
+    const uint8_t* c = codes + (size_t)r0 * k;
+    const float* as = act_scales + (size_t)r0 * (k / block);
+    if (out_dtype == CACHALOT_BF16) {
+      __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)r0 * n;
+      if (block == 32) launch_gemv_mma<32>(ntg, grid, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
+      else launch_gemv_mma<128>(ntg, grid, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
+    } else {
+      float* o = (float*)out + (size_t)r0 * n;
+      if (block == 32) launch_gemv_mma<32>(ntg, grid, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
+      else launch_gemv_mma<128>(ntg, grid, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
+    }
   }
-  dim3 grid((n + GEMV_WARPS - 1) / GEMV_WARPS, rows);
-  if (out_dtype == CACHALOT_BF16)
-    fp8_gemv_kernel<__nv_bfloat16><<<grid, GEMV_WARPS * 32, smem, (cudaStream_t)stream>>>(codes, act_scales, weight, w_scales, scale_rule, block, n, k, (__nv_bfloat16*)out);
-  else
-    fp8_gemv_kernel<float><<<grid, GEMV_WARPS * 32, smem, (cudaStream_t)stream>>>(codes, act_scales, weight, w_scales, scale_rule, block, n, k, (float*)out);
   return check_launch("fp8_gemv");
 }
