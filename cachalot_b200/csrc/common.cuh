@@ -84,6 +84,27 @@ __device__ __forceinline__ float e2m1_to_f32(uint32_t code) {
   return __uint_as_float(bits);
 }
 
+// E2M1 nearest with ties to even, as a threshold chain (the reference's explicit table)
+__device__ __forceinline__ uint32_t e2m1_round_code(float v) {
+  float a = fabsf(v);
+  uint32_t mag = a <= 0.25f ? 0u : a < 0.75f ? 1u : a <= 1.25f ? 2u : a < 1.75f ? 3u : a <= 2.5f ? 4u : a < 3.5f ? 5u : a <= 5.0f ? 6u : 7u;
+  return mag | ((__float_as_uint(v) >> 28) & 8u);
+}
+
+// block scale of MXFP4: 2**ceil(log2(max(amax, 6*2**-126) / 6)); returns the exponent
+__device__ __forceinline__ int mxfp4_exponent(float amax) {
+  amax = fmaxf(amax, 6.0f * 1.1754943508222875e-38f);
+  float raw = __fdiv_rn(amax, 6.0f);
+  uint32_t b = __float_as_uint(raw);
+  int e = (int)((b >> 23) & 0xffu);
+  if (e == 0) return -126;  // denormal quotient can only be just below 2**-126
+  return e - 127 + ((b & 0x7fffffu) ? 1 : 0);
+}
+
+__device__ __forceinline__ float pow2f(int e) {  // e in [-127, 127]
+  return e >= -126 ? __uint_as_float((uint32_t)(e + 127) << 23) : __uint_as_float(0x00400000u);
+}
+
 // SwiGLU with the reference's clamp: up both sides, gate from above only, when limit > 0.
 __device__ __forceinline__ float swiglu(float g, float u, float limit) {
   if (limit > 0.f) {

@@ -62,4 +62,12 @@ int launch_layer_fused(const BankView& v, const void* x, const float* logits, co
                        int32_t* indices_out, float* weights_out, int* status, cudaStream_t stream);
 bool layer_fused_supported(const BankView& v, int n_experts, int k);
 
+
+// Prefill on the block-scaled FP4 tensor cores (prefill_tc.cu): FP4 bank, MXFP4 activations.
+int launch_prefill_tc(const BankView& v, const void* x_bf16, const int32_t* perm, const int32_t* offsets,
+                      const int32_t* slot_of_expert, const float* gate_w, int tokens, int k, int n_experts, float limit,
+                      void* workspace, float* out, int* status, cudaStream_t stream);
+size_t prefill_tc_workspace_bytes(int hidden, int inter, int tokens, int k, int n_experts);
+bool prefill_tc_supported(const BankView& v);
+
 }  // namespace cachalot

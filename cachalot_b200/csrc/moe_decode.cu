@@ -369,6 +369,10 @@ extern "C" size_t cachalot_moe_prefill_workspace_bytes(const cachalot_bank_desc*
   size_t b = align_up(rows * desc->inter * sizeof(float), 256);   // hidden
   b += align_up(rows * sizeof(int32_t), 256);                     // slot per routed row
   if (mxfp4_act) b += align_up((size_t)tokens * desc->hidden * 2, 256);  // MXFP4-rounded x as bf16
+  if (mxfp4_act == 1 && desc->format == CACHALOT_BANK_FP4) {
+    const size_t tc = prefill_tc_workspace_bytes(desc->hidden, desc->inter, tokens, k, /*n_experts<=*/tokens * k);
+    if (tc > b) b = tc;
+  }
   return b;
 }
 
@@ -389,6 +393,9 @@ extern "C" int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc* 
   if (!aligned(workspace, 256)) return fail(CACHALOT_EALIGN, "moe_prefill: workspace must be 256-byte aligned");
   cudaStream_t s = (cudaStream_t)stream;
   const size_t rows = (size_t)tokens * k;
+  if (mxfp4_act == 1 && prefill_tc_supported(v) && (size_t)n_experts <= rows)
+    return launch_prefill_tc(v, x_bf16, perm, offsets, slot_of_expert, gate_w, tokens, k, n_experts, swiglu_limit, workspace, out,
+                             status, s);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   float* hidden = reinterpret_cast<float*>(ws);
   ws += align_up(rows * desc->inter * sizeof(float), 256);

@@ -1,0 +1,605 @@
+// Prefill routed experts on the block-scaled FP4 tensor cores (tcgen05.mma kind::mxf4, E8M0 scale per 32).
+//
+// Rows are already grouped by expert (perm, offsets).  Two grouped GEMMs run per call, both with the
+// weights as the M side of the MMA so that an expert with few rows wastes no tensor-core work:
+//
+//   gate/up : D_g, D_u [128 weight rows, <=96 routed rows] = W1/W3 tile . X^T      K = hidden
+//             epilogue  h = silu(min(g,L)) * clip(u) * gate_w  -> MXFP4 per 32 along the weight-row axis
+//   down    : D   [128 weight rows, <=96 routed rows]        = W2 tile . H^T        K = inter
+//             epilogue  y -> bf16, stored per routed row; a last kernel adds a token's k rows in slot order
+//
+// Work item = (unit, weight-row tile); a unit is up to 96 consecutive routed rows of one expert.  CTAs are
+// persistent and take items round-robin, unit-major, so the CTAs that run together read different tiles of
+// the same expert and share its activation rows in L2.
+//
+// Warp roles (320 threads): warp 0 issues the TMA tile loads (weights straight out of the bank through a
+// 3-D tensor map {K bytes, rows, slot}; activations through a 2-D map), warp 1 owns TMEM and issues
+// tcgen05.cp (scales, shared -> TMEM) and tcgen05.mma, warps 2-5 bring the E8M0 scale bytes of the stage
+// from the bank's row-major arrays into the 32x16-byte pattern tcgen05.cp wants, warps 6-9 drain the
+// accumulators (tcgen05.ld) while the next item's MMAs fill the other accumulator buffer.
+//
+// Every wait is bounded: when one gives up the CTA raises CACHALOT_STATUS_WAIT_EXPIRED, all roles leave
+// their loops, TMEM is released and the kernel returns.
+#include <cuda.h>
+
+#include "kernels.cuh"
+
+namespace cachalot {
+namespace {
+
+constexpr int BM = 128;          // weight rows per tile (MMA M)
+constexpr int NTMAX = 96;        // routed rows per unit (MMA N <= 96, multiple of 16)
+constexpr int BKB = 128;         // bytes of K per stage and row = 256 codes = 8 scale blocks = 4 MMAs of K=64
+constexpr int A_TILE = BM * BKB;
+constexpr int B_TILE = NTMAX * BKB;
+constexpr int SF_TILE = 1024;    // 128 rows x 8 scale bytes, as two 512-byte groups of four blocks
+constexpr int NTHREADS = 320;
+constexpr int TMEM_COLS = 512;
+constexpr int SF_COL = 2 * 2 * NTMAX;  // scale columns start behind the (up to) four accumulators
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
+
+struct Unit {
+  int32_t slot, row_start, ntok, pad;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* b, int n) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(n));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(smem_u32(b)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// false when the wait gave up (it sets *abort) or another role already had
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile int* abort) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try(b, parity)) return true;
+    if ((i & 63u) == 63u && *abort) return false;
+  }
+  *abort = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
+          "r"(smem_u32(dst)),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// shared-memory matrix descriptors (address and offsets in 16-byte units, descriptor version 1)
+// operand tile: rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// scale group: 32 rows of 16 bytes, no swizzle, 8-row groups 128 bytes apart
+__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (8ull << 32) | (1ull << 46);
+}
+// instruction descriptor of kind::mxf4: E2M1 x E2M1, both K-major, E8M0 scales, M = 128, N = n
+__device__ __forceinline__ uint32_t idesc_mxf4(int n) {
+  return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tacc, uint64_t da, uint64_t db, uint32_t idesc, uint32_t tsfa, uint32_t tsfb,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n}" ::"r"(tacc),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+struct GemmArgs {
+  const uint8_t* bank;        // slot records
+  long long record_bytes;
+  long long off_sc[2];        // offsets of the weight matrices' scale arrays inside a record
+  const uint8_t* act_scales;  // u8 [rows, K/32]
+  const Unit* units;
+  const int32_t* n_units;
+  int n_rows;                 // weight rows N
+  int k_codes;                // K
+  int total_rows;             // routed rows R
+  // gate/up epilogue
+  const int32_t* perm;
+  const float* gate_w;
+  float limit;
+  uint8_t* h_codes;           // u8 [R, N/2]
+  uint8_t* h_scales;          // u8 [R, N/32]
+  // down epilogue
+  __nv_bfloat16* y;           // bf16 [R, N]
+  int* status;
+};
+
+// eight scale bytes of one row for the stage that starts at block kb0; blocks past the row's end read as 2**0
+__device__ __forceinline__ uint2 load_sf8(const uint8_t* row, int kb0, int nkb, bool valid) {
+  uint2 v = make_uint2(0x7F7F7F7Fu, 0x7F7F7F7Fu);
+  if (!valid) return v;
+  const uint8_t* p = row + kb0;
+  if (kb0 + 8 <= nkb) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    if ((a & 3) == 0) {
+      v.x = __ldg(reinterpret_cast<const uint32_t*>(p));
+      v.y = __ldg(reinterpret_cast<const uint32_t*>(p) + 1);
+    } else if ((a & 1) == 0) {
+      const uint16_t* q = reinterpret_cast<const uint16_t*>(p);
+      v.x = (uint32_t)__ldg(q) | ((uint32_t)__ldg(q + 1) << 16);
+      v.y = (uint32_t)__ldg(q + 2) | ((uint32_t)__ldg(q + 3) << 16);
+    } else {
+      v.x = (uint32_t)__ldg(p) | ((uint32_t)__ldg(p + 1) << 8) | ((uint32_t)__ldg(p + 2) << 16) | ((uint32_t)__ldg(p + 3) << 24);
+      v.y = (uint32_t)__ldg(p + 4) | ((uint32_t)__ldg(p + 5) << 8) | ((uint32_t)__ldg(p + 6) << 16) | ((uint32_t)__ldg(p + 7) << 24);
+    }
+    return v;
+  }
+  uint32_t b[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) b[i] = kb0 + i < nkb ? (uint32_t)__ldg(p + i) : 0x7Fu;
+  v.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+  v.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+  return v;
+}
+
+// NA = 2: gate and up tiles with the SwiGLU + MXFP4 epilogue; NA = 1: down tile with the bf16 store epilogue
+template <int NA, int NSTAGE>
+__global__ void __launch_bounds__(NTHREADS, 1)
+grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
+                    const __grid_constant__ CUtensorMap map_b, GemmArgs A) {
+  constexpr int STAGE_BYTES = NA * A_TILE + B_TILE + (NA + 1) * SF_TILE;
+  constexpr int ACC_COLS = NA * NTMAX;  // per accumulator buffer
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)NSTAGE * STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + NSTAGE;
+  uint64_t* acc_full = bars + 2 * NSTAGE;
+  uint64_t* acc_empty = bars + 2 * NSTAGE + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGE + 4);
+  volatile int* abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSTAGE; ++s) mbar_init(&full[s], 5), mbar_init(&empty[s], 1);
+    for (int b = 0; b < 2; ++b) mbar_init(&acc_full[b], 1), mbar_init(&acc_empty[b], 4);
+    *abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_holder;
+
+  const int n_units = *A.n_units;
+  const int n_mt = (A.n_rows + BM - 1) / BM;
+  const long long total = (long long)n_units * n_mt;
+  const int k_bytes = A.k_codes / 2, nkb = A.k_codes / 32;
+  const int nks = (k_bytes + BKB - 1) / BKB;
+
+  if (warp == 0) {
+    // ---- tile loads ------------------------------------------------------------------------
+    if (lane == 0) {
+      long long it = 0;
+      bool ok = true;
+      for (long long w = blockIdx.x; w < total && ok; w += gridDim.x) {
+        const Unit u = A.units[w / n_mt];
+        const int mt = (int)(w % n_mt);
+        for (int ks = 0; ks < nks; ++ks, ++it) {
+          const int s = (int)(it % NSTAGE);
+          if (it >= NSTAGE && !mbar_wait(&empty[s], (uint32_t)((it / NSTAGE) - 1) & 1u, abort)) { ok = false; break; }
+          uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+          mbar_expect_tx(&full[s], NA * A_TILE + B_TILE);
+          tma_load_3d(st, &map_a0, ks * BKB, mt * BM, u.slot, &full[s]);
+          if (NA == 2) tma_load_3d(st + A_TILE, &map_a1, ks * BKB, mt * BM, u.slot, &full[s]);
+          tma_load_2d(st + NA * A_TILE, &map_b, ks * BKB, u.row_start, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- scale copies into TMEM and the MMAs -------------------------------------------------
+    if (lane == 0) {
+      long long it = 0, item = 0;
+      bool ok = true;
+      for (long long w = blockIdx.x; w < total && ok; w += gridDim.x, ++item) {
+        const Unit u = A.units[w / n_mt];
+        const int buf = (int)(item & 1);
+        const uint32_t idesc = idesc_mxf4((u.ntok + 15) & ~15);
+        if (item >= 2 && !mbar_wait(&acc_empty[buf], (uint32_t)((item >> 1) - 1) & 1u, abort)) { ok = false; break; }
+        tc_fence_after();
+        for (int ks = 0; ks < nks; ++ks, ++it) {
+          const int s = (int)(it % NSTAGE);
+          if (!mbar_wait(&full[s], (uint32_t)(it / NSTAGE) & 1u, abort)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
+          const uint32_t sf = st + NA * A_TILE + B_TILE;
+#pragma unroll
+          for (int m = 0; m < NA + 1; ++m)
+#pragma unroll
+            for (int q = 0; q < 2; ++q) tc_cp_sf(tmem + SF_COL + m * 8 + q * 4, desc_sf(sf + m * SF_TILE + q * 512));
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t sfid = (uint32_t)(kk & 1) * 2u, q = (uint32_t)kk >> 1;
+            const uint64_t db = desc_sw128(st + NA * A_TILE + kk * 32);
+            const uint32_t tsfb = (tmem + SF_COL + NA * 8 + q * 4) | (sfid << 30);
+#pragma unroll
+            for (int m = 0; m < NA; ++m) {
+              const uint64_t da = desc_sw128(st + m * A_TILE + kk * 32);
+              const uint32_t tsfa = (tmem + SF_COL + m * 8 + q * 4) | (sfid << 30);
+              tc_mma(tmem + buf * ACC_COLS + m * NTMAX, da, db, idesc | (sfid << 29) | (sfid << 4), tsfa, tsfb,
+                     (ks > 0 || kk > 0) ? 1u : 0u);
+            }
+          }
+          tc_commit(&empty[s]);
+        }
+        if (ok) tc_commit(&acc_full[buf]);
+      }
+    }
+  } else if (warp < 6) {
+    // ---- scale bytes: bank rows -> the stage's 32x16-byte groups --------------------------------
+    const int m = (warp - 2) * 32 + lane;                                   // row of the tile
+    const uint32_t sf_off = (uint32_t)((m & 31) * 16 + (m >> 5) * 4);
+    long long it = 0;
+    bool ok = true;
+    for (long long w = blockIdx.x; w < total && ok; w += gridDim.x) {
+      const Unit u = A.units[w / n_mt];
+      const int mt = (int)(w % n_mt);
+      const int row_a = mt * BM + m;
+      const bool va = row_a < A.n_rows;
+      const uint8_t* rec = A.bank + (size_t)u.slot * A.record_bytes;
+      const uint8_t* ra0 = rec + A.off_sc[0] + (size_t)row_a * nkb;
+      const uint8_t* ra1 = rec + A.off_sc[NA - 1] + (size_t)row_a * nkb;
+      const bool vb = m < u.ntok;
+      const uint8_t* rb = A.act_scales + (size_t)(u.row_start + m) * nkb;
+      uint2 c0 = load_sf8(ra0, 0, nkb, va), c1 = make_uint2(0, 0), cb = load_sf8(rb, 0, nkb, vb);
+      if (NA == 2) c1 = load_sf8(ra1, 0, nkb, va);
+      for (int ks = 0; ks < nks; ++ks, ++it) {
+        uint2 n0 = c0, n1 = c1, nb = cb;
+        if (ks + 1 < nks) {
+          n0 = load_sf8(ra0, (ks + 1) * 8, nkb, va);
+          if (NA == 2) n1 = load_sf8(ra1, (ks + 1) * 8, nkb, va);
+          nb = load_sf8(rb, (ks + 1) * 8, nkb, vb);
+        }
+        const int s = (int)(it % NSTAGE);
+        if (it >= NSTAGE && !__all_sync(0xffffffffu, mbar_wait(&empty[s], (uint32_t)((it / NSTAGE) - 1) & 1u, abort))) {
+          ok = false;
+          break;
+        }
+        uint8_t* sf = smem + (size_t)s * STAGE_BYTES + NA * A_TILE + B_TILE;
+        *reinterpret_cast<uint32_t*>(sf + sf_off) = c0.x;
+        *reinterpret_cast<uint32_t*>(sf + 512 + sf_off) = c0.y;
+        if (NA == 2) {
+          *reinterpret_cast<uint32_t*>(sf + SF_TILE + sf_off) = c1.x;
+          *reinterpret_cast<uint32_t*>(sf + SF_TILE + 512 + sf_off) = c1.y;
+        }
+        *reinterpret_cast<uint32_t*>(sf + NA * SF_TILE + sf_off) = cb.x;
+        *reinterpret_cast<uint32_t*>(sf + NA * SF_TILE + 512 + sf_off) = cb.y;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[s]);
+        c0 = n0, c1 = n1, cb = nb;
+      }
+    }
+  } else {
+    // ---- accumulators -> results ----------------------------------------------------------------
+    const int q = warp & 3;  // TMEM lanes 32q .. 32q+31 belong to this warp
+    const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
+    long long item = 0;
+    bool ok = true;
+    for (long long w = blockIdx.x; w < total && ok; w += gridDim.x, ++item) {
+      const Unit u = A.units[w / n_mt];
+      const int mt = (int)(w % n_mt);
+      const int buf = (int)(item & 1);
+      const int n = mt * BM + q * 32 + lane;           // weight row = output index
+      const bool rows_ok = mt * BM + q * 32 < A.n_rows;  // whole warps: n_rows is a multiple of 32
+      if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (uint32_t)(item >> 1) & 1u, abort))) { ok = false; break; }
+      tc_fence_after();
+      for (int j0 = 0; j0 < u.ntok; j0 += 16) {
+        uint32_t g[16], up[16];
+        tc_ld16(lane_base + buf * ACC_COLS + j0, g);
+        if (NA == 2) tc_ld16(lane_base + buf * ACC_COLS + NTMAX + j0, up);
+        float wv = 0.f;
+        if (NA == 2 && lane < 16 && j0 + lane < u.ntok) wv = A.gate_w[A.perm[u.row_start + j0 + lane]];
+        tc_ld_wait();
+        if (!rows_ok) continue;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (j0 + j >= u.ntok) break;
+          const size_t row = (size_t)(u.row_start + j0 + j);
+          if (NA == 2) {
+            const float wj = __shfl_sync(0xffffffffu, wv, j);
+            const float h = swiglu(bf16_round(__uint_as_float(g[j])), bf16_round(__uint_as_float(up[j])), A.limit) * wj;
+            const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(h))));
+            const int e = mxfp4_exponent(amax);
+            const float qv = fminf(fmaxf(__fdiv_rn(h, pow2f(e)), -6.0f), 6.0f);
+            const uint32_t code = e2m1_round_code(qv);
+            const uint32_t hi = __shfl_down_sync(0xffffffffu, code, 1);
+            if ((lane & 1) == 0) A.h_codes[row * (size_t)(A.n_rows / 2) + (n >> 1)] = (uint8_t)(code | (hi << 4));
+            if (lane == 0) A.h_scales[row * (size_t)(A.n_rows / 32) + (n >> 5)] = (uint8_t)(e + 127);
+          } else {
+            A.y[row * (size_t)A.n_rows + n] = __float2bfloat16_rn(__uint_as_float(g[j]));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort) {
+    if (threadIdx.x == 0 && A.status) atomicOr(A.status, CACHALOT_STATUS_WAIT_EXPIRED);
+    // give tile loads still in flight time to land before the shared memory goes away
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- planning ---------------------------------------------------------------------------------
+
+// one CTA per expert: inverse permutation and source token of every grouped row of a present expert
+__global__ void plan_rows_kernel(const int32_t* __restrict__ perm, const int32_t* __restrict__ offsets,
+                                 const int32_t* __restrict__ slot_of_expert, int n_slots, int k, int32_t* __restrict__ inv,
+                                 int32_t* __restrict__ src_token, int* __restrict__ status) {
+  const int e = blockIdx.x;
+  const int s = slot_of_expert ? slot_of_expert[e] : e;
+  const bool present = s >= 0 && s < n_slots;
+  if (s >= n_slots && status && threadIdx.x == 0 && offsets[e + 1] > offsets[e]) atomicOr(status, CACHALOT_STATUS_SLOT_RANGE);
+  for (int p = offsets[e] + threadIdx.x; p < offsets[e + 1]; p += blockDim.x) {
+    const int r = perm[p];
+    src_token[p] = r / k;
+    if (present) inv[r] = p;
+  }
+}
+
+// single CTA: units of up to NTMAX rows per present expert, experts ascending
+__global__ void plan_units_kernel(const int32_t* __restrict__ offsets, const int32_t* __restrict__ slot_of_expert, int n_experts,
+                                  int n_slots, Unit* __restrict__ units, int32_t* __restrict__ n_units) {
+  extern __shared__ int32_t sh[];  // [blockDim.x] unit counts of each thread's span
+  const int t = threadIdx.x, nt = blockDim.x;
+  const int per = (n_experts + nt - 1) / nt;
+  const int lo = min(t * per, n_experts), hi = min(lo + per, n_experts);
+  auto units_of = [&](int e) {
+    const int s = slot_of_expert ? slot_of_expert[e] : e;
+    if (s < 0 || s >= n_slots) return 0;
+    return (offsets[e + 1] - offsets[e] + NTMAX - 1) / NTMAX;
+  };
+  int sum = 0;
+  for (int e = lo; e < hi; ++e) sum += units_of(e);
+  sh[t] = sum;
+  __syncthreads();
+  if (t == 0) {
+    int run = 0;
+    for (int i = 0; i < nt; ++i) {
+      const int v = sh[i];
+      sh[i] = run;
+      run += v;
+    }
+    *n_units = run;
+  }
+  __syncthreads();
+  int at = sh[t];
+  for (int e = lo; e < hi; ++e) {
+    const int nu = units_of(e);
+    const int s = slot_of_expert ? slot_of_expert[e] : e;
+    const int begin = offsets[e], end = offsets[e + 1];
+    for (int i = 0; i < nu; ++i) {
+      Unit u;
+      u.slot = s;
+      u.row_start = begin + i * NTMAX;
+      u.ntok = min(NTMAX, end - u.row_start);
+      u.pad = 0;
+      units[at++] = u;
+    }
+  }
+}
+
+// out[t, :] = sum over the token's route slots j = 0..k-1 (in that order) of its row of y
+__global__ void combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ inv, int k, int hidden,
+                               float* __restrict__ out) {
+  const int t = blockIdx.x;
+  for (int n = threadIdx.x * 2; n < hidden; n += blockDim.x * 2) {
+    float a = 0.f, b = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const int p = inv[t * k + j];
+      if (p < 0) continue;
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(y + (size_t)p * hidden + n);
+      a += __bfloat162float(v.x);
+      b += __bfloat162float(v.y);
+    }
+    out[(size_t)t * hidden + n] = a;
+    out[(size_t)t * hidden + n + 1] = b;
+  }
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// byte matrix [planes][rows][row_bytes] with the given pitches; box = {128 bytes, box_rows, 1}, 128-byte swizzle
+int make_map(CUtensorMap* m, const void* base, int row_bytes, long long row_pitch, int rows, long long plane_pitch, int planes,
+             int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(CACHALOT_ECUDA, "moe_prefill: cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {(cuuint64_t)row_bytes, (cuuint64_t)rows, (cuuint64_t)planes};
+  cuuint64_t strides[2] = {(cuuint64_t)row_pitch, (cuuint64_t)plane_pitch};
+  cuuint32_t box[3] = {(cuuint32_t)BKB, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const int rank = planes > 0 ? 3 : 2;
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(CACHALOT_ECUDA, "moe_prefill: cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return CACHALOT_OK;
+}
+
+constexpr int STAGES_GU = 4, STAGES_DN = 6;
+constexpr size_t smem_bytes(int na, int nstage) {
+  return (size_t)nstage * (na * A_TILE + B_TILE + (na + 1) * SF_TILE) + (2 * nstage + 4) * 8 + 16 + 1024;
+}
+
+struct Scratch {
+  uint8_t *x_codes, *x_scales, *h_codes, *h_scales;
+  __nv_bfloat16* y;
+  int32_t *inv, *src_token, *n_units;
+  Unit* units;
+  size_t total;
+};
+
+Scratch carve(uint8_t* base, int hidden, int inter, size_t rows, int n_experts) {
+  Scratch s;
+  size_t at = 0;
+  auto take = [&](size_t bytes) {
+    uint8_t* p = base ? base + at : nullptr;
+    at += align_up(bytes, 256);
+    return p;
+  };
+  // NTMAX rows of slack behind the code arrays: a unit's tile load always covers NTMAX rows
+  s.x_codes = take(rows * (hidden / 2));
+  s.x_scales = take(rows * (hidden / 32));
+  s.h_codes = take(rows * (inter / 2));
+  s.h_scales = take(rows * (inter / 32));
+  s.y = reinterpret_cast<__nv_bfloat16*>(take(rows * hidden * 2));
+  s.inv = reinterpret_cast<int32_t*>(take(rows * 4));
+  s.src_token = reinterpret_cast<int32_t*>(take(rows * 4));
+  s.units = reinterpret_cast<Unit*>(take((rows / NTMAX + n_experts + 1) * sizeof(Unit)));
+  s.n_units = reinterpret_cast<int32_t*>(take(256));
+  s.total = at;
+  return s;
+}
+
+}  // namespace
+
+bool prefill_tc_supported(const BankView& v) {
+  return v.format == CACHALOT_BANK_FP4 && v.hidden % 128 == 0 && v.inter % 32 == 0 && (v.hidden / 2) % 16 == 0 &&
+         (v.inter / 2) % 16 == 0 && v.record_bytes % 16 == 0;
+}
+
+size_t prefill_tc_workspace_bytes(int hidden, int inter, int tokens, int k, int n_experts) {
+  return carve(nullptr, hidden, inter, (size_t)tokens * k, n_experts).total;
+}
+
+int launch_prefill_tc(const BankView& v, const void* x_bf16, const int32_t* perm, const int32_t* offsets,
+                      const int32_t* slot_of_expert, const float* gate_w, int tokens, int k, int n_experts, float limit,
+                      void* workspace, float* out, int* status, cudaStream_t stream) {
+  if (!prefill_tc_supported(v)) return CACHALOT_EUNSUPPORTED;
+  const int H = v.hidden, I = v.inter;
+  const size_t rows = (size_t)tokens * k;
+  const Scratch s = carve(static_cast<uint8_t*>(workspace), H, I, rows, n_experts);
+
+  CUtensorMap m_w1, m_w3, m_w2, m_x, m_h;
+  int rc;
+  if ((rc = make_map(&m_w1, v.base + v.off[0], H / 2, H / 2, I, v.record_bytes, v.n_slots, BM))) return rc;
+  if ((rc = make_map(&m_w3, v.base + v.off[4], H / 2, H / 2, I, v.record_bytes, v.n_slots, BM))) return rc;
+  if ((rc = make_map(&m_w2, v.base + v.off[2], I / 2, I / 2, H, v.record_bytes, v.n_slots, BM))) return rc;
+  if ((rc = make_map(&m_x, s.x_codes, H / 2, H / 2, (int)rows, 0, 0, NTMAX))) return rc;
+  if ((rc = make_map(&m_h, s.h_codes, I / 2, I / 2, (int)rows, 0, 0, NTMAX))) return rc;
+
+  cudaError_t e = cudaMemsetAsync(s.inv, 0xFF, rows * 4, stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(s.src_token, 0, rows * 4, stream);
+  if (e != cudaSuccess) return fail(CACHALOT_ECUDA, "moe_prefill: memset: %s", cudaGetErrorString(e));
+  plan_rows_kernel<<<n_experts, 128, 0, stream>>>(perm, offsets, slot_of_expert, v.n_slots, k, s.inv, s.src_token, status);
+  plan_units_kernel<<<1, 256, 256 * sizeof(int32_t), stream>>>(offsets, slot_of_expert, n_experts, v.n_slots, s.units, s.n_units);
+  if ((rc = check_launch("moe_prefill plan"))) return rc;
+  if ((rc = cachalot_mxfp4_act_quant(x_bf16, s.src_token, (int)rows, H, s.x_codes, s.x_scales, stream))) return rc;
+
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(grouped_mxf4_kernel<2, STAGES_GU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(2, STAGES_GU));
+    cudaFuncSetAttribute(grouped_mxf4_kernel<1, STAGES_DN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(1, STAGES_DN));
+    attr_done = true;
+  }
+  GemmArgs a;
+  a.bank = v.base;
+  a.record_bytes = v.record_bytes;
+  a.units = s.units;
+  a.n_units = s.n_units;
+  a.total_rows = (int)rows;
+  a.perm = perm;
+  a.gate_w = gate_w;
+  a.limit = limit;
+  a.h_codes = s.h_codes;
+  a.h_scales = s.h_scales;
+  a.y = s.y;
+  a.status = status;
+  // gate/up: K = hidden, N = inter
+  a.off_sc[0] = v.off[1];
+  a.off_sc[1] = v.off[5];
+  a.act_scales = s.x_scales;
+  a.n_rows = I;
+  a.k_codes = H;
+  grouped_mxf4_kernel<2, STAGES_GU><<<sms, NTHREADS, smem_bytes(2, STAGES_GU), stream>>>(m_w1, m_w3, m_x, a);
+  if ((rc = check_launch("moe_prefill gate/up (tcgen05)"))) return rc;
+  // down: K = inter, N = hidden
+  a.off_sc[0] = v.off[3];
+  a.off_sc[1] = v.off[3];
+  a.act_scales = s.h_scales;
+  a.n_rows = H;
+  a.k_codes = I;
+  grouped_mxf4_kernel<1, STAGES_DN><<<sms, NTHREADS, smem_bytes(1, STAGES_DN), stream>>>(m_w2, m_w2, m_h, a);
+  if ((rc = check_launch("moe_prefill down (tcgen05)"))) return rc;
+  combine_kernel<<<tokens, 256, 0, stream>>>(s.y, s.inv, k, H, out);
+  return check_launch("moe_prefill combine");
+}
+
+}  // namespace cachalot

@@ -228,7 +228,9 @@ CACHALOT_API size_t cachalot_moe_prefill_workspace_bytes(const cachalot_bank_des
  * their expert once, results are kept per route slot and summed in slot order 0..k-1.
  * x bf16 [tokens,H]; slot_of_expert i32 [E] maps expert id -> bank slot (-1 = absent -> zeros);
  * gate_w f32 [tokens,k]; mxfp4_act != 0 quantises x and the hidden activation to MXFP4 per 32
- * first.  out f32 [tokens,H]. */
+ * first: 1 = on the block-scaled FP4 tensor cores when the bank is FP4 (grouped GEMM, weights as
+ * the M side), 2 = always on the plain per-row kernels (the same arithmetic in a fixed summation
+ * order, kept as the check for 1).  out f32 [tokens,H]. */
 CACHALOT_API int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc* desc /* host */, const void* x_bf16,
                          const int32_t* perm, const int32_t* offsets, const int32_t* slot_of_expert,
                          const float* gate_w, int tokens, int k, int n_experts, float swiglu_limit, int mxfp4_act,

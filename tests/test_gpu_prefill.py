@@ -96,3 +96,22 @@ def test_prefill_equals_decode_row_by_row():
     fast = cb.moe_forward(xt, it, wt, bank, numerics="bf16")
     # the tensor-core kernels round the same values to bf16; a value on a rounding boundary may move one step
     assert float((fast - dec).abs().max()) <= 2e-3 * float(dec.abs().max())
+
+
+@pytest.mark.parametrize("tokens,hidden,inter,n_exp", [(48, 256, 192, 16), (300, 512, 320, 12), (64, 1024, 2880 // 5, 40)])
+def test_prefill_tensor_core_path_matches_plain_kernels(tokens, hidden, inter, n_exp):
+    """mxfp4_act=1 (block-scaled FP4 MMAs, weights as the M side) against mxfp4_act=2 (per-row kernels):
+    same codes in, same rounding points, different summation order."""
+    import cachalot_b200 as cb
+    k = 6
+    x, ids, w, experts = configs.config3(seed=5, tokens=tokens, hidden=hidden, inter=inter, n_experts=n_exp, k=k,
+                                         materialise=range(n_exp))
+    bank = make_bank([experts[e] for e in range(n_exp)], cb.FP4_FORMAT, hidden, inter)
+    bank.slot_table[0, 3] = -1  # an absent expert contributes zeros on both paths
+    xt, it, wt = bf16_tensor(x), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tc = cb.moe_prefill_grouped(xt, it, wt, bank, mxfp4_act=1, status=status)
+    plain = cb.moe_prefill_grouped(xt, it, wt, bank, mxfp4_act=2)
+    assert int(status.item()) == 0
+    err = (tc - plain).abs().amax(dim=1) / plain.abs().max()
+    assert float((err < TOL).float().mean()) >= 0.9 and float(err.max()) < 5e-2
