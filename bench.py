@@ -46,6 +46,9 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--bank", default="affine2", choices=["affine2", "fp4"])
     p.add_argument("--batch", type=int, default=1)
+    p.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                   help="prefill: one 4096-token chunk through one FP4 layer, Zipf(1.1) expert popularity (1 GPU)")
+    p.add_argument("--tokens", type=int, default=4096, help="prefill chunk length")
     p.add_argument("--distinct-layers", type=int, default=8)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-graph", action="store_true")
@@ -411,6 +414,107 @@ def run_ours(args):
     _leave(world)
 
 
+# ---- prefill workload --------------------------------------------------------------------------
+
+def zipf_routing(rng, tokens, n_experts, k, s=1.1):
+    """k distinct experts per token with popularity ~ 1/rank**s under a seeded rank permutation
+    (Gumbel top-k), weights = sigmoid of N(0,1) logits renormalised to sum 1."""
+    import numpy as np
+
+    p = 1.0 / np.arange(1, n_experts + 1) ** s
+    p = p[rng.permutation(n_experts)]
+    p /= p.sum()
+    keys = np.log(p)[None, :] + rng.gumbel(size=(tokens, n_experts))
+    ids = np.argsort(-keys, axis=1)[:, :k].astype(np.int32)
+    w = 1.0 / (1.0 + np.exp(-rng.standard_normal((tokens, k))))
+    return ids, (w / w.sum(1, keepdims=True)).astype(np.float32)
+
+
+def run_prefill(args):
+    """One step = one chunk of `--tokens` prompt tokens through one MoE layer: expert-major grouping,
+    MXFP4 activation quantisation, the two grouped block-scaled FP4 GEMMs and the slot-ordered combine."""
+    import numpy as np
+    import torch
+
+    import cachalot_b200 as cb
+
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"metric": "moe_prefill_tok_per_s", "unavailable": "the prefill workload is built for one GPU"}), flush=True)
+        return
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    T, K = args.tokens, TOPK
+    bank = cb.SlabBank(cb.FP4_FORMAT, HIDDEN, INTER, EXPERTS, layers=1, n_experts=EXPERTS, device=dev)
+    bank.fill_random(torch.Generator(device=dev).manual_seed(1234))
+    rng = np.random.default_rng(0)
+    P = 4
+    g_in = torch.Generator().manual_seed(7)
+    x_host = torch.randn((P, T, HIDDEN), generator=g_in).to(torch.bfloat16).pin_memory()
+    routes = [zipf_routing(rng, T, EXPERTS, K) for _ in range(P)]
+    ids_host = torch.stack([torch.from_numpy(r[0]) for r in routes]).pin_memory()
+    w_host = torch.stack([torch.from_numpy(r[1]) for r in routes]).pin_memory()
+    out_host = torch.empty((T, HIDDEN), dtype=torch.float32).pin_memory()
+    x_pool, ids_pool, w_pool = x_host.to(dev), ids_host.to(dev), w_host.to(dev)
+    x, ids, w = x_pool[0].clone(), ids_pool[0].clone(), w_pool[0].clone()
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+    result = [None]
+
+    def step():
+        result[0] = cb.moe_prefill_grouped(x, ids, w, bank, swiglu_limit=SWIGLU_LIMIT, mxfp4_act=1, status=status)
+
+    def timed(steps, host):
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for i in range(steps):
+                src = (x_host, ids_host, w_host) if host else (x_pool, ids_pool, w_pool)
+                x.copy_(src[0][i % P], non_blocking=True)
+                ids.copy_(src[1][i % P], non_blocking=True)
+                w.copy_(src[2][i % P], non_blocking=True)
+                step()
+                if host:
+                    out_host.copy_(result[0], non_blocking=True)
+                    stream.synchronize()
+            e1.record(stream)
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1)
+
+    timed(max(args.warmup, 3), False)
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = timed(args.steps, False)
+    ms_e2e = timed(args.steps, True)
+    clocks = sampler.stop()
+    if int(status.item()):
+        raise RuntimeError(f"device status {int(status.item())}")
+    touched = float(np.mean([len(set(r[0].reshape(-1).tolist())) for r in routes]))
+    rows = T * K
+    per_expert = 3 * (HIDDEN * INTER // 2 + HIDDEN * INTER // 32)
+    act_bytes = T * HIDDEN * 2 + rows * (HIDDEN // 2 + HIDDEN // 32) * 2 + rows * (INTER // 2 + INTER // 32) * 2 + rows * HIDDEN * 2 * 2 + T * HIDDEN * 4
+    alg = touched * per_expert + act_bytes
+    us = ms * 1e3 / args.steps
+    peak, which = measured_peak()
+    flops = 6.0 * rows * INTER * HIDDEN
+    line = {
+        "metric": "moe_prefill_tok_per_s", "value": T / (us * 1e-6), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp4 (E2M1 x E2M1, E8M0 block scales, f32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"prefill expert-major MoE layer: FP4 E2M1/E8M0 bank, {EXPERTS} experts, {T} tokens, top-{K}, Zipf(1.1) expert "
+                               f"popularity, hidden {HIDDEN}, inter {INTER}, activations MXFP4 per 32",
+                   "l2": "inputs larger than L2: 7.2 GB of expert weights are streamed per step"},
+        "roofline": {"bound": "hbm", "achieved": alg / us / 1e3, "peak": peak, "unit": "GB/s", "frac": alg / us / 1e3 / peak,
+                     "traffic": None, "peak_source": which, "kernel": "whole call: grouping, quantiser, gate/up GEMM, down GEMM, combine",
+                     "tensor_tflops": flops / us / 1e6},
+        "e2e": {"value": T / (ms_e2e * 1e-3 / args.steps), "unit": "tok/s", "h2d_bytes_per_step": T * HIDDEN * 2 + rows * 8,
+                "d2h_bytes_per_step": T * HIDDEN * 4},
+        "gpu_launches": 10 * args.steps, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
     if args.watchdog > 0:
@@ -419,6 +523,8 @@ def main():
         faulthandler.dump_traceback_later(args.watchdog, exit=True)
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
     else:
         run_ours(args)
 

@@ -74,23 +74,36 @@ __global__ void group_place_kernel(const int32_t* __restrict__ ids, int total, c
   }
 }
 
-// one warp per (row, 32-block), one lane per element
+// one thread per 8 consecutive elements (one 16-byte load), four threads per 32-block
 __global__ void mxfp4_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ src_rows,
                                    long long rows, int k, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales) {
-  const int nblk = k / 32;
-  long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (warp >= rows * nblk) return;
-  long long r = warp / nblk;
-  int b = (int)(warp - r * nblk);
-  long long src = src_rows ? src_rows[r] : r;
-  float v = __bfloat162float(x[src * k + b * 32 + lane]);
-  int e = mxfp4_exponent(warp_max(fabsf(v)));
-  float q = fminf(fmaxf(__fdiv_rn(v, pow2f(e)), -6.0f), 6.0f);
-  uint32_t code = e2m1_round_code(q);
-  uint32_t hi = __shfl_down_sync(0xffffffffu, code, 1);
-  if ((lane & 1) == 0) codes[r * (k / 2) + b * 16 + (lane >> 1)] = (uint8_t)(code | (hi << 4));
-  if (lane == 0) scales[r * nblk + b] = (uint8_t)(e + 127);
+  const int per_row = k / 8;
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const bool live = i < rows * per_row;
+  const long long r = live ? i / per_row : 0;
+  const int c = live ? (int)(i - r * per_row) : 0;
+  const long long src = src_rows ? src_rows[r] : r;
+  uint4 raw = make_uint4(0, 0, 0, 0);
+  if (live) raw = *reinterpret_cast<const uint4*>(x + src * k + c * 8);
+  const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+  float v[8];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[2 * j] = __uint_as_float(wds[j] << 16);
+    v[2 * j + 1] = __uint_as_float(wds[j] & 0xffff0000u);
+    amax = fmaxf(amax, fmaxf(fabsf(v[2 * j]), fabsf(v[2 * j + 1])));
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  const int e = mxfp4_exponent(amax);
+  const float s = pow2f(e);
+  uint32_t packed = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) packed |= e2m1_round_code(fminf(fmaxf(__fdiv_rn(v[j], s), -6.0f), 6.0f)) << (4 * j);
+  if (!live) return;
+  *reinterpret_cast<uint32_t*>(codes + r * (k / 2) + c * 4) = packed;
+  if ((c & 3) == 0) scales[r * (k / 32) + (c >> 2)] = (uint8_t)(e + 127);
 }
 
 template <typename T>
@@ -150,8 +163,9 @@ extern "C" int cachalot_mxfp4_act_quant(const void* x_bf16, const int32_t* src_r
   if (!x_bf16 || !codes || !scales) return fail(CACHALOT_EINVAL, "mxfp4_act_quant: null pointer");
   if (rows < 0 || k <= 0 || k % 32) return fail(CACHALOT_EINVAL, "last dimension %d must be divisible by block_size=32", k);
   if (rows == 0) return CACHALOT_OK;
-  long long warps = (long long)rows * (k / 32);
-  unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+  if (!aligned(x_bf16, 16) || !aligned(codes, 4)) return fail(CACHALOT_EALIGN, "mxfp4_act_quant: x must be 16-byte and codes 4-byte aligned");
+  long long threads = (long long)rows * (k / 8);
+  unsigned blocks = (unsigned)((threads + 255) / 256);
   mxfp4_quant_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x_bf16, src_rows, rows, k, codes, scales);
   return check_launch("mxfp4_act_quant");
 }

@@ -71,18 +71,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile
   return false;
 }
 
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar, uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-          smem_u32(dst)),
-      "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::
+          "r"(smem_u32(dst)),
+      "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
 }
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar,
+                                            uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
-          "r"(smem_u32(dst)),
-      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], "
+      "%6;" ::"r"(smem_u32(dst)),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
 }
 
@@ -175,13 +176,17 @@ __device__ __forceinline__ uint2 load_sf8(const uint8_t* row, int kb0, int nkb, 
   return v;
 }
 
-// NA = 2: gate and up tiles with the SwiGLU + MXFP4 epilogue; NA = 1: down tile with the bf16 store epilogue
-template <int NA, int NSTAGE>
+// NA = 2: gate and up tiles with the SwiGLU + MXFP4 epilogue; NA = 1: down tile with the bf16 store epilogue.
+// A stage holds KSUB consecutive 128-byte pieces of every row (one swizzled tile each), so that a row's bytes
+// of a stage are asked from DRAM back to back.
+template <int NA, int NSTAGE, int KSUB>
 __global__ void __launch_bounds__(NTHREADS, 1)
 grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
                     const __grid_constant__ CUtensorMap map_b, GemmArgs A) {
-  constexpr int STAGE_BYTES = NA * A_TILE + B_TILE + (NA + 1) * SF_TILE;
+  constexpr int STAGE_BYTES = KSUB * (NA * A_TILE + B_TILE + (NA + 1) * SF_TILE);
+  constexpr int OFF_B = KSUB * NA * A_TILE, OFF_SF = OFF_B + KSUB * B_TILE;
   constexpr int ACC_COLS = NA * NTMAX;  // per accumulator buffer
+  static_assert(SF_COL + (NA + 1) * KSUB * 8 <= TMEM_COLS, "scale columns do not fit");
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)NSTAGE * STAGE_BYTES);
@@ -213,11 +218,15 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
   const int n_mt = (A.n_rows + BM - 1) / BM;
   const long long total = (long long)n_units * n_mt;
   const int k_bytes = A.k_codes / 2, nkb = A.k_codes / 32;
-  const int nks = (k_bytes + BKB - 1) / BKB;
+  const int nks = (k_bytes + KSUB * BKB - 1) / (KSUB * BKB);
 
   if (warp == 0) {
     // ---- tile loads ------------------------------------------------------------------------
     if (lane == 0) {
+      // weights are read once: first out of L2; activation rows are re-read by every tile of the expert
+      uint64_t pol_w, pol_x;
+      asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol_w));
+      asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol_x));
       long long it = 0;
       bool ok = true;
       for (long long w = blockIdx.x; w < total && ok; w += gridDim.x) {
@@ -227,10 +236,15 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
           const int s = (int)(it % NSTAGE);
           if (it >= NSTAGE && !mbar_wait(&empty[s], (uint32_t)((it / NSTAGE) - 1) & 1u, abort)) { ok = false; break; }
           uint8_t* st = smem + (size_t)s * STAGE_BYTES;
-          mbar_expect_tx(&full[s], NA * A_TILE + B_TILE);
-          tma_load_3d(st, &map_a0, ks * BKB, mt * BM, u.slot, &full[s]);
-          if (NA == 2) tma_load_3d(st + A_TILE, &map_a1, ks * BKB, mt * BM, u.slot, &full[s]);
-          tma_load_2d(st + NA * A_TILE, &map_b, ks * BKB, u.row_start, &full[s]);
+          mbar_expect_tx(&full[s], KSUB * (NA * A_TILE + B_TILE));
+#pragma unroll
+          for (int j = 0; j < KSUB; ++j) {
+            const int kx = (ks * KSUB + j) * BKB;
+            tma_load_3d(st + j * A_TILE, &map_a0, kx, mt * BM, u.slot, &full[s], pol_w);
+            if (NA == 2) tma_load_3d(st + (KSUB + j) * A_TILE, &map_a1, kx, mt * BM, u.slot, &full[s], pol_w);
+          }
+#pragma unroll
+          for (int j = 0; j < KSUB; ++j) tma_load_2d(st + OFF_B + j * B_TILE, &map_b, (ks * KSUB + j) * BKB, u.row_start, &full[s], pol_x);
         }
       }
     }
@@ -250,22 +264,29 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
           if (!mbar_wait(&full[s], (uint32_t)(it / NSTAGE) & 1u, abort)) { ok = false; break; }
           tc_fence_after();
           const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
-          const uint32_t sf = st + NA * A_TILE + B_TILE;
 #pragma unroll
-          for (int m = 0; m < NA + 1; ++m)
+          for (int j = 0; j < KSUB; ++j) {
+            if ((ks * KSUB + j) * BKB >= k_bytes) break;  // piece wholly behind the end of K: zeros, nothing to add
+#ifdef CB_PF_NOMMA
+            if (A.total_rows >= 0) break;
+#endif
 #pragma unroll
-            for (int q = 0; q < 2; ++q) tc_cp_sf(tmem + SF_COL + m * 8 + q * 4, desc_sf(sf + m * SF_TILE + q * 512));
+            for (int m = 0; m < NA + 1; ++m)
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint32_t sfid = (uint32_t)(kk & 1) * 2u, q = (uint32_t)kk >> 1;
-            const uint64_t db = desc_sw128(st + NA * A_TILE + kk * 32);
-            const uint32_t tsfb = (tmem + SF_COL + NA * 8 + q * 4) | (sfid << 30);
+              for (int q = 0; q < 2; ++q)
+                tc_cp_sf(tmem + SF_COL + (m * KSUB + j) * 8 + q * 4, desc_sf(st + OFF_SF + (m * KSUB + j) * SF_TILE + q * 512));
 #pragma unroll
-            for (int m = 0; m < NA; ++m) {
-              const uint64_t da = desc_sw128(st + m * A_TILE + kk * 32);
-              const uint32_t tsfa = (tmem + SF_COL + m * 8 + q * 4) | (sfid << 30);
-              tc_mma(tmem + buf * ACC_COLS + m * NTMAX, da, db, idesc | (sfid << 29) | (sfid << 4), tsfa, tsfb,
-                     (ks > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint32_t sfid = (uint32_t)(kk & 1) * 2u, q = (uint32_t)kk >> 1;
+              const uint64_t db = desc_sw128(st + OFF_B + j * B_TILE + kk * 32);
+              const uint32_t tsfb = (tmem + SF_COL + (NA * KSUB + j) * 8 + q * 4) | (sfid << 30);
+#pragma unroll
+              for (int m = 0; m < NA; ++m) {
+                const uint64_t da = desc_sw128(st + (m * KSUB + j) * A_TILE + kk * 32);
+                const uint32_t tsfa = (tmem + SF_COL + (m * KSUB + j) * 8 + q * 4) | (sfid << 30);
+                tc_mma(tmem + buf * ACC_COLS + m * NTMAX, da, db, idesc | (sfid << 29) | (sfid << 4), tsfa, tsfb,
+                       (ks > 0 || j > 0 || kk > 0) ? 1u : 0u);
+              }
             }
           }
           tc_commit(&empty[s]);
@@ -275,48 +296,65 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
     }
   } else if (warp < 6) {
     // ---- scale bytes: bank rows -> the stage's 32x16-byte groups --------------------------------
-    const int m = (warp - 2) * 32 + lane;                                   // row of the tile
+    // One flat walk over (item, stage) with the next stage's bytes already on their way, also across items.
+    const int m = (warp - 2) * 32 + lane;  // row of the tile
     const uint32_t sf_off = (uint32_t)((m & 31) * 16 + (m >> 5) * 4);
-    long long it = 0;
-    bool ok = true;
-    for (long long w = blockIdx.x; w < total && ok; w += gridDim.x) {
+    const uint8_t *ra0 = nullptr, *ra1 = nullptr, *rb = nullptr;
+    bool va = false, vb = false;
+    auto point_at = [&](long long w) {
       const Unit u = A.units[w / n_mt];
-      const int mt = (int)(w % n_mt);
-      const int row_a = mt * BM + m;
-      const bool va = row_a < A.n_rows;
+      const int row_a = (int)(w % n_mt) * BM + m;
+      va = row_a < A.n_rows;
       const uint8_t* rec = A.bank + (size_t)u.slot * A.record_bytes;
-      const uint8_t* ra0 = rec + A.off_sc[0] + (size_t)row_a * nkb;
-      const uint8_t* ra1 = rec + A.off_sc[NA - 1] + (size_t)row_a * nkb;
-      const bool vb = m < u.ntok;
-      const uint8_t* rb = A.act_scales + (size_t)(u.row_start + m) * nkb;
-      uint2 c0 = load_sf8(ra0, 0, nkb, va), c1 = make_uint2(0, 0), cb = load_sf8(rb, 0, nkb, vb);
-      if (NA == 2) c1 = load_sf8(ra1, 0, nkb, va);
-      for (int ks = 0; ks < nks; ++ks, ++it) {
-        uint2 n0 = c0, n1 = c1, nb = cb;
-        if (ks + 1 < nks) {
-          n0 = load_sf8(ra0, (ks + 1) * 8, nkb, va);
-          if (NA == 2) n1 = load_sf8(ra1, (ks + 1) * 8, nkb, va);
-          nb = load_sf8(rb, (ks + 1) * 8, nkb, vb);
-        }
-        const int s = (int)(it % NSTAGE);
-        if (it >= NSTAGE && !__all_sync(0xffffffffu, mbar_wait(&empty[s], (uint32_t)((it / NSTAGE) - 1) & 1u, abort))) {
-          ok = false;
-          break;
-        }
-        uint8_t* sf = smem + (size_t)s * STAGE_BYTES + NA * A_TILE + B_TILE;
-        *reinterpret_cast<uint32_t*>(sf + sf_off) = c0.x;
-        *reinterpret_cast<uint32_t*>(sf + 512 + sf_off) = c0.y;
-        if (NA == 2) {
-          *reinterpret_cast<uint32_t*>(sf + SF_TILE + sf_off) = c1.x;
-          *reinterpret_cast<uint32_t*>(sf + SF_TILE + 512 + sf_off) = c1.y;
-        }
-        *reinterpret_cast<uint32_t*>(sf + NA * SF_TILE + sf_off) = cb.x;
-        *reinterpret_cast<uint32_t*>(sf + NA * SF_TILE + 512 + sf_off) = cb.y;
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full[s]);
-        c0 = n0, c1 = n1, cb = nb;
+      ra0 = rec + A.off_sc[0] + (size_t)row_a * nkb;
+      ra1 = rec + A.off_sc[NA - 1] + (size_t)row_a * nkb;
+      vb = m < u.ntok;
+      rb = A.act_scales + (size_t)(u.row_start + m) * nkb;
+    };
+    uint2 cur[NA + 1][KSUB], nxt[NA + 1][KSUB];
+    auto fetch = [&](uint2 (&d)[NA + 1][KSUB], int ks) {
+#pragma unroll
+      for (int j = 0; j < KSUB; ++j) {
+        d[0][j] = load_sf8(ra0, (ks * KSUB + j) * 8, nkb, va);
+        if (NA == 2) d[1][j] = load_sf8(ra1, (ks * KSUB + j) * 8, nkb, va);
+        d[NA][j] = load_sf8(rb, (ks * KSUB + j) * 8, nkb, vb);
       }
+    };
+    long long it = 0;
+    long long w = blockIdx.x;
+    if (w < total) {
+      point_at(w);
+      fetch(cur, 0);
+    }
+    int ks = 0;
+    while (w < total) {
+      // the stage after this one
+      long long w2 = w;
+      int ks2 = ks + 1;
+      if (ks2 == nks) ks2 = 0, w2 = w + gridDim.x;
+      if (w2 < total) {
+        if (ks2 == 0) point_at(w2);
+        fetch(nxt, ks2);
+      }
+      const int s = (int)(it % NSTAGE);
+      if (it >= NSTAGE && !__all_sync(0xffffffffu, mbar_wait(&empty[s], (uint32_t)((it / NSTAGE) - 1) & 1u, abort))) break;
+      uint8_t* sf = smem + (size_t)s * STAGE_BYTES + OFF_SF;
+#pragma unroll
+      for (int mm = 0; mm < NA + 1; ++mm)
+#pragma unroll
+        for (int j = 0; j < KSUB; ++j) {
+          *reinterpret_cast<uint32_t*>(sf + (mm * KSUB + j) * SF_TILE + sf_off) = cur[mm][j].x;
+          *reinterpret_cast<uint32_t*>(sf + (mm * KSUB + j) * SF_TILE + 512 + sf_off) = cur[mm][j].y;
+        }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full[s]);
+#pragma unroll
+      for (int mm = 0; mm < NA + 1; ++mm)
+#pragma unroll
+        for (int j = 0; j < KSUB; ++j) cur[mm][j] = nxt[mm][j];
+      ++it;
+      w = w2, ks = ks2;
     }
   } else {
     // ---- accumulators -> results ----------------------------------------------------------------
@@ -339,6 +377,9 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
         float wv = 0.f;
         if (NA == 2 && lane < 16 && j0 + lane < u.ntok) wv = A.gate_w[A.perm[u.row_start + j0 + lane]];
         tc_ld_wait();
+#ifdef CB_PF_NOEPI
+        if (A.total_rows >= 0) continue;
+#endif
         if (!rows_ok) continue;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -490,9 +531,13 @@ int make_map(CUtensorMap* m, const void* base, int row_bytes, long long row_pitc
   return CACHALOT_OK;
 }
 
-constexpr int STAGES_GU = 4, STAGES_DN = 6;
+#ifndef CB_PF_KSUB
+#define CB_PF_KSUB 2
+#endif
+constexpr int KSUB = CB_PF_KSUB;
+constexpr int STAGES_GU = 4 / KSUB, STAGES_DN = 6 / KSUB;
 constexpr size_t smem_bytes(int na, int nstage) {
-  return (size_t)nstage * (na * A_TILE + B_TILE + (na + 1) * SF_TILE) + (2 * nstage + 4) * 8 + 16 + 1024;
+  return (size_t)nstage * KSUB * (na * A_TILE + B_TILE + (na + 1) * SF_TILE) + (2 * nstage + 4) * 8 + 16 + 1024;
 }
 
 struct Scratch {
@@ -565,8 +610,8 @@ int launch_prefill_tc(const BankView& v, const void* x_bf16, const int32_t* perm
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   static bool attr_done = false;
   if (!attr_done) {
-    cudaFuncSetAttribute(grouped_mxf4_kernel<2, STAGES_GU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(2, STAGES_GU));
-    cudaFuncSetAttribute(grouped_mxf4_kernel<1, STAGES_DN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(1, STAGES_DN));
+    cudaFuncSetAttribute(grouped_mxf4_kernel<2, STAGES_GU, KSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(2, STAGES_GU));
+    cudaFuncSetAttribute(grouped_mxf4_kernel<1, STAGES_DN, KSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(1, STAGES_DN));
     attr_done = true;
   }
   GemmArgs a;
@@ -588,7 +633,7 @@ int launch_prefill_tc(const BankView& v, const void* x_bf16, const int32_t* perm
   a.act_scales = s.x_scales;
   a.n_rows = I;
   a.k_codes = H;
-  grouped_mxf4_kernel<2, STAGES_GU><<<sms, NTHREADS, smem_bytes(2, STAGES_GU), stream>>>(m_w1, m_w3, m_x, a);
+  grouped_mxf4_kernel<2, STAGES_GU, KSUB><<<sms, NTHREADS, smem_bytes(2, STAGES_GU), stream>>>(m_w1, m_w3, m_x, a);
   if ((rc = check_launch("moe_prefill gate/up (tcgen05)"))) return rc;
   // down: K = inter, N = hidden
   a.off_sc[0] = v.off[3];
@@ -596,7 +641,7 @@ int launch_prefill_tc(const BankView& v, const void* x_bf16, const int32_t* perm
   a.act_scales = s.h_scales;
   a.n_rows = H;
   a.k_codes = I;
-  grouped_mxf4_kernel<1, STAGES_DN><<<sms, NTHREADS, smem_bytes(1, STAGES_DN), stream>>>(m_w2, m_w2, m_h, a);
+  grouped_mxf4_kernel<1, STAGES_DN, KSUB><<<sms, NTHREADS, smem_bytes(1, STAGES_DN), stream>>>(m_w2, m_w2, m_h, a);
   if ((rc = check_launch("moe_prefill down (tcgen05)"))) return rc;
   combine_kernel<<<tokens, 256, 0, stream>>>(s.y, s.inv, k, H, out);
   return check_launch("moe_prefill combine");
