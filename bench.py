@@ -49,6 +49,7 @@ def parse_args():
     p.add_argument("--workload", default="decode", choices=["decode", "prefill"],
                    help="prefill: one 4096-token chunk through one FP4 layer, Zipf(1.1) expert popularity (1 GPU)")
     p.add_argument("--tokens", type=int, default=4096, help="prefill chunk length")
+    p.add_argument("--experts", type=int, default=EXPERTS, help="prefill: experts in the layer (smaller = a case sized for profiling)")
     p.add_argument("--distinct-layers", type=int, default=8)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-graph", action="store_true")
@@ -444,14 +445,14 @@ def run_prefill(args):
         return
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
-    T, K = args.tokens, TOPK
-    bank = cb.SlabBank(cb.FP4_FORMAT, HIDDEN, INTER, EXPERTS, layers=1, n_experts=EXPERTS, device=dev)
+    T, K, E = args.tokens, TOPK, args.experts
+    bank = cb.SlabBank(cb.FP4_FORMAT, HIDDEN, INTER, E, layers=1, n_experts=E, device=dev)
     bank.fill_random(torch.Generator(device=dev).manual_seed(1234))
     rng = np.random.default_rng(0)
     P = 4
     g_in = torch.Generator().manual_seed(7)
     x_host = torch.randn((P, T, HIDDEN), generator=g_in).to(torch.bfloat16).pin_memory()
-    routes = [zipf_routing(rng, T, EXPERTS, K) for _ in range(P)]
+    routes = [zipf_routing(rng, T, E, K) for _ in range(P)]
     ids_host = torch.stack([torch.from_numpy(r[0]) for r in routes]).pin_memory()
     w_host = torch.stack([torch.from_numpy(r[1]) for r in routes]).pin_memory()
     out_host = torch.empty((T, HIDDEN), dtype=torch.float32).pin_memory()
@@ -502,9 +503,9 @@ def run_prefill(args):
         "metric": "moe_prefill_tok_per_s", "value": T / (us * 1e-6), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp4 (E2M1 x E2M1, E8M0 block scales, f32 accumulate)", "data": "synthetic",
-        "config": {"workload": f"prefill expert-major MoE layer: FP4 E2M1/E8M0 bank, {EXPERTS} experts, {T} tokens, top-{K}, Zipf(1.1) expert "
+        "config": {"workload": f"prefill expert-major MoE layer: FP4 E2M1/E8M0 bank, {E} experts, {T} tokens, top-{K}, Zipf(1.1) expert "
                                f"popularity, hidden {HIDDEN}, inter {INTER}, activations MXFP4 per 32",
-                   "l2": "inputs larger than L2: 7.2 GB of expert weights are streamed per step"},
+                   "l2": f"inputs larger than L2: {E * 18.8e6 / 1e9:.1f} GB of expert weights are streamed per step"},
         "roofline": {"bound": "hbm", "achieved": alg / us / 1e3, "peak": peak, "unit": "GB/s", "frac": alg / us / 1e3 / peak,
                      "traffic": None, "peak_source": which, "kernel": "whole call: grouping, quantiser, gate/up GEMM, down GEMM, combine",
                      "tensor_tflops": flops / us / 1e6},

@@ -91,14 +91,20 @@ __device__ __forceinline__ uint32_t e2m1_round_code(float v) {
   return mag | ((__float_as_uint(v) >> 28) & 8u);
 }
 
-// block scale of MXFP4: 2**ceil(log2(max(amax, 6*2**-126) / 6)); returns the exponent
+// block scale of MXFP4: 2**ceil(log2(max(amax, 6*2**-126) / 6)); returns the exponent.  With
+// amax = m * 2**E (1 <= m < 2) the fp32 quotient amax/6 is at most 2**(E-2) exactly when m <= 1.5, so the
+// answer is E-2, plus one when the mantissa is above 1.5 (checked against the division form over all
+// exponents and 2e8 random values).
 __device__ __forceinline__ int mxfp4_exponent(float amax) {
-  amax = fmaxf(amax, 6.0f * 1.1754943508222875e-38f);
-  float raw = __fdiv_rn(amax, 6.0f);
-  uint32_t b = __float_as_uint(raw);
-  int e = (int)((b >> 23) & 0xffu);
-  if (e == 0) return -126;  // denormal quotient can only be just below 2**-126
-  return e - 127 + ((b & 0x7fffffu) ? 1 : 0);
+  const uint32_t b = __float_as_uint(fmaxf(amax, 6.0f * 1.1754943508222875e-38f));
+  return (int)(b >> 23) - 129 + ((b & 0x7fffffu) > 0x400000u ? 1 : 0);
+}
+
+// two floats -> one byte of E2M1 codes (lo in bits 0-3), round to nearest even, saturating at +-6
+__device__ __forceinline__ uint32_t e2m1x2_byte(float lo, float hi) {
+  uint32_t r;
+  asm("{\n.reg .b8 t;\ncvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\nmov.b32 %0, {t, t, t, t};\n}" : "=r"(r) : "f"(hi), "f"(lo));
+  return r & 0xffu;
 }
 
 __device__ __forceinline__ float pow2f(int e) {  // e in [-127, 127]

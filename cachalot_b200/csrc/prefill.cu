@@ -97,10 +97,10 @@ __global__ void mxfp4_quant_kernel(const __nv_bfloat16* __restrict__ x, const in
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   const int e = mxfp4_exponent(amax);
-  const float s = pow2f(e);
+  const float inv = pow2f(-e);  // times 2**-e is the same rounding as over 2**e
   uint32_t packed = 0;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) packed |= e2m1_round_code(fminf(fmaxf(__fdiv_rn(v[j], s), -6.0f), 6.0f)) << (4 * j);
+  for (int j = 0; j < 4; ++j) packed |= e2m1x2_byte(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
   if (!live) return;
   *reinterpret_cast<uint32_t*>(codes + r * (k / 2) + c * 4) = packed;
   if ((c & 3) == 0) scales[r * (k / 32) + (c >> 2)] = (uint8_t)(e + 127);

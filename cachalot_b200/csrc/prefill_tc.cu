@@ -12,10 +12,10 @@
 // persistent and take items round-robin, unit-major, so the CTAs that run together read different tiles of
 // the same expert and share its activation rows in L2.
 //
-// Warp roles (320 threads): warp 0 issues the TMA tile loads (weights straight out of the bank through a
+// Warp roles (448 threads): warp 0 issues the TMA tile loads (weights straight out of the bank through a
 // 3-D tensor map {K bytes, rows, slot}; activations through a 2-D map), warp 1 owns TMEM and issues
 // tcgen05.cp (scales, shared -> TMEM) and tcgen05.mma, warps 2-5 bring the E8M0 scale bytes of the stage
-// from the bank's row-major arrays into the 32x16-byte pattern tcgen05.cp wants, warps 6-9 drain the
+// from the bank's row-major arrays into the 32x16-byte pattern tcgen05.cp wants, warps 6-13 drain the
 // accumulators (tcgen05.ld) while the next item's MMAs fill the other accumulator buffer.
 //
 // Every wait is bounded: when one gives up the CTA raises CACHALOT_STATUS_WAIT_EXPIRED, all roles leave
@@ -33,7 +33,7 @@ constexpr int BKB = 128;         // bytes of K per stage and row = 256 codes = 8
 constexpr int A_TILE = BM * BKB;
 constexpr int B_TILE = NTMAX * BKB;
 constexpr int SF_TILE = 1024;    // 128 rows x 8 scale bytes, as two 512-byte groups of four blocks
-constexpr int NTHREADS = 320;
+constexpr int NTHREADS = 448;
 constexpr int TMEM_COLS = 512;
 constexpr int SF_COL = 2 * 2 * NTMAX;  // scale columns start behind the (up to) four accumulators
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
@@ -200,7 +200,7 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGE; ++s) mbar_init(&full[s], 5), mbar_init(&empty[s], 1);
-    for (int b = 0; b < 2; ++b) mbar_init(&acc_full[b], 1), mbar_init(&acc_empty[b], 4);
+    for (int b = 0; b < 2; ++b) mbar_init(&acc_full[b], 1), mbar_init(&acc_empty[b], 8);
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -358,7 +358,9 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
     }
   } else {
     // ---- accumulators -> results ----------------------------------------------------------------
+    // eight warps: two per TMEM lane quarter, taking alternate 16-column chunks
     const int q = warp & 3;  // TMEM lanes 32q .. 32q+31 belong to this warp
+    const int half = (warp - 6) >> 2;
     const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
     long long item = 0;
     bool ok = true;
@@ -370,7 +372,7 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
       const bool rows_ok = mt * BM + q * 32 < A.n_rows;  // whole warps: n_rows is a multiple of 32
       if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (uint32_t)(item >> 1) & 1u, abort))) { ok = false; break; }
       tc_fence_after();
-      for (int j0 = 0; j0 < u.ntok; j0 += 16) {
+      for (int j0 = 16 * half; j0 < u.ntok; j0 += 32) {
         uint32_t g[16], up[16];
         tc_ld16(lane_base + buf * ACC_COLS + j0, g);
         if (NA == 2) tc_ld16(lane_base + buf * ACC_COLS + NTMAX + j0, up);
@@ -387,13 +389,17 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
           const size_t row = (size_t)(u.row_start + j0 + j);
           if (NA == 2) {
             const float wj = __shfl_sync(0xffffffffu, wv, j);
-            const float h = swiglu(bf16_round(__uint_as_float(g[j])), bf16_round(__uint_as_float(up[j])), A.limit) * wj;
+            float gg = bf16_round(__uint_as_float(g[j])), uu = bf16_round(__uint_as_float(up[j]));
+            if (A.limit > 0.f) {
+              uu = fminf(fmaxf(uu, -A.limit), A.limit);
+              gg = fminf(gg, A.limit);
+            }
+            const float h = __fdividef(gg, 1.0f + __expf(-gg)) * uu * wj;
             const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(h))));
             const int e = mxfp4_exponent(amax);
-            const float qv = fminf(fmaxf(__fdiv_rn(h, pow2f(e)), -6.0f), 6.0f);
-            const uint32_t code = e2m1_round_code(qv);
-            const uint32_t hi = __shfl_down_sync(0xffffffffu, code, 1);
-            if ((lane & 1) == 0) A.h_codes[row * (size_t)(A.n_rows / 2) + (n >> 1)] = (uint8_t)(code | (hi << 4));
+            const float qv = h * pow2f(-e);
+            const float qn = __shfl_down_sync(0xffffffffu, qv, 1);
+            if ((lane & 1) == 0) A.h_codes[row * (size_t)(A.n_rows / 2) + (n >> 1)] = (uint8_t)e2m1x2_byte(qv, qn);
             if (lane == 0) A.h_scales[row * (size_t)(A.n_rows / 32) + (n >> 5)] = (uint8_t)(e + 127);
           } else {
             A.y[row * (size_t)A.n_rows + n] = __float2bfloat16_rn(__uint_as_float(g[j]));
