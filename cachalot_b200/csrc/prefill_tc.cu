@@ -38,6 +38,18 @@ constexpr int TMEM_COLS = 512;
 constexpr int SF_COL = 2 * 2 * NTMAX;  // scale columns start behind the (up to) four accumulators
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
 
+#ifdef CB_PF_TRACE
+// development build: per-CTA cycle counts of where each role waits
+__device__ unsigned long long pf_trace[2][256][16];
+#define PF_T0 long long t0_ = clock64()
+#define PF_ADD(acc) do { long long n_ = clock64(); acc += n_ - t0_; t0_ = n_; } while (0)
+#define PF_STORE(slot, v) pf_trace[NA - 1][blockIdx.x][slot] = (unsigned long long)(v)
+#else
+#define PF_T0 do { } while (0)
+#define PF_ADD(acc) do { } while (0)
+#define PF_STORE(slot, v) do { } while (0)
+#endif
+
 struct Unit {
   int32_t slot, row_start, ntok, pad;
 };
@@ -85,6 +97,18 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
       "%6;" ::"r"(smem_u32(dst)),
       "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
+}
+
+// contiguous bytes -> shared memory (both 16-byte aligned, size a multiple of 16), completion on an mbarrier
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)), "l"(src),
+               "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// pulls one weight tile into L2 ahead of its load
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
 // shared-memory matrix descriptors (address and offsets in 16-byte units, descriptor version 1)
@@ -148,38 +172,52 @@ struct GemmArgs {
   int* status;
 };
 
-// eight scale bytes of one row for the stage that starts at block kb0; blocks past the row's end read as 2**0
-__device__ __forceinline__ uint2 load_sf8(const uint8_t* row, int kb0, int nkb, bool valid) {
-  uint2 v = make_uint2(0x7F7F7F7Fu, 0x7F7F7F7Fu);
-  if (!valid) return v;
-  const uint8_t* p = row + kb0;
-  if (kb0 + 8 <= nkb) {
-    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-    if ((a & 3) == 0) {
-      v.x = __ldg(reinterpret_cast<const uint32_t*>(p));
-      v.y = __ldg(reinterpret_cast<const uint32_t*>(p) + 1);
-    } else if ((a & 1) == 0) {
-      const uint16_t* q = reinterpret_cast<const uint16_t*>(p);
-      v.x = (uint32_t)__ldg(q) | ((uint32_t)__ldg(q + 1) << 16);
-      v.y = (uint32_t)__ldg(q + 2) | ((uint32_t)__ldg(q + 3) << 16);
-    } else {
-      v.x = (uint32_t)__ldg(p) | ((uint32_t)__ldg(p + 1) << 8) | ((uint32_t)__ldg(p + 2) << 16) | ((uint32_t)__ldg(p + 3) << 24);
-      v.y = (uint32_t)__ldg(p + 4) | ((uint32_t)__ldg(p + 5) << 8) | ((uint32_t)__ldg(p + 6) << 16) | ((uint32_t)__ldg(p + 7) << 24);
-    }
-    return v;
-  }
-  uint32_t b[8];
+// Sixteen scale bytes of one row (one stage: two pieces of eight 32-blocks) starting at block kb0, for any
+// even row pitch: one or two aligned 16-byte loads and a byte shift.  Blocks past the row's end read as 2**0
+// (their codes are zero-filled), and no byte past the row's end is touched.
+__device__ __forceinline__ uint4 load_sf16(const uint8_t* row, int kb0, int nkb, bool valid) {
+  uint4 r = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+  const int have = min(16, nkb - kb0);  // bytes of this stage that exist
+  if (!valid || have <= 0) return r;
+  const uintptr_t a = reinterpret_cast<uintptr_t>(row + kb0);
+  const uint4* q = reinterpret_cast<const uint4*>(a & ~(uintptr_t)15);
+  const int off = (int)(a & 15);
+  const uint4 lo = __ldg(q);
+  if (off == 0) {
+    r = lo;
+  } else {
+    uint4 hi = make_uint4(0, 0, 0, 0);
+    if (off + have > 16) hi = __ldg(q + 1);
+    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    const int ws = off >> 2, bs = (off & 3) * 8;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) b[i] = kb0 + i < nkb ? (uint32_t)__ldg(p + i) : 0x7Fu;
-  v.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
-  v.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
-  return v;
+    for (int t = 0; t < 4; ++t)
+      if (ws == t) {
+        r.x = __funnelshift_r(w[t], w[t + 1], bs);
+        r.y = __funnelshift_r(w[t + 1], w[t + 2], bs);
+        r.z = __funnelshift_r(w[t + 2], w[t + 3], bs);
+        r.w = __funnelshift_r(w[t + 3], w[t + 4], bs);
+      }
+  }
+  if (have < 16) {
+    uint32_t* v = &r.x;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int n = have - 4 * i;  // valid bytes of word i
+      const uint32_t keep = n >= 4 ? 0xFFFFFFFFu : n <= 0 ? 0u : (1u << (8 * n)) - 1u;
+      v[i] = (v[i] & keep) | (0x7F7F7F7Fu & ~keep);
+    }
+  }
+  return r;
 }
 
 // NA = 2: gate and up tiles with the SwiGLU + MXFP4 epilogue; NA = 1: down tile with the bf16 store epilogue.
 // A stage holds KSUB consecutive 128-byte pieces of every row (one swizzled tile each), so that a row's bytes
 // of a stage are asked from DRAM back to back.
-template <int NA, int NSTAGE, int KSUB>
+// RAW: the scale bytes of an item (contiguous in the bank: 128 rows of K/32 bytes per matrix, and the unit's
+// rows of the activation scales) are bulk-copied into shared memory one item ahead and the loader warps read
+// them from there; otherwise the loader warps read their rows from global memory (one row per lane).
+template <int NA, int NSTAGE, int KSUB, bool RAW>
 __global__ void __launch_bounds__(NTHREADS, 1)
 grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
                     const __grid_constant__ CUtensorMap map_b, GemmArgs A) {
@@ -194,13 +232,17 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
   uint64_t* empty = bars + NSTAGE;
   uint64_t* acc_full = bars + 2 * NSTAGE;
   uint64_t* acc_empty = bars + 2 * NSTAGE + 2;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGE + 4);
+  uint64_t* raw_full = bars + 2 * NSTAGE + 4;
+  uint64_t* raw_empty = bars + 2 * NSTAGE + 6;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGE + 8);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  uint8_t* raw_base = smem + (size_t)NSTAGE * STAGE_BYTES + 256;  // two slots of raw scale bytes behind the barriers
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGE; ++s) mbar_init(&full[s], 5), mbar_init(&empty[s], 1);
     for (int b = 0; b < 2; ++b) mbar_init(&acc_full[b], 1), mbar_init(&acc_empty[b], 8);
+    for (int b = 0; b < 2; ++b) mbar_init(&raw_full[b], 1), mbar_init(&raw_empty[b], 4);
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -219,6 +261,9 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
   const long long total = (long long)n_units * n_mt;
   const int k_bytes = A.k_codes / 2, nkb = A.k_codes / 32;
   const int nks = (k_bytes + KSUB * BKB - 1) / (KSUB * BKB);
+  // raw scale slot: NA blocks of 128 rows, then the unit's activation rows (with up to 15 bytes of lead-in)
+  const int raw_a = (BM * nkb + 15) & ~15, raw_b = (NTMAX * nkb + 15 + 15) & ~15;
+  const int raw_slot = NA * raw_a + raw_b;
 
   if (warp == 0) {
     // ---- tile loads ------------------------------------------------------------------------
@@ -227,14 +272,59 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
       uint64_t pol_w, pol_x;
       asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol_w));
       asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol_x));
-      long long it = 0;
-      bool ok = true;
-      for (long long w = blockIdx.x; w < total && ok; w += gridDim.x) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool wrapped = false, ok = true;
+      long long c_wait = 0, c_issue = 0;
+      // The shared-memory ring is only two or three stages deep, less than the HBM latency under load, so the
+      // weight tiles of the next PFD stages are asked into L2 ahead of their loads.
+      constexpr int PFD = NA == 2 ? 4 : 6;
+      long long pw = blockIdx.x;  // prefetch cursor (item, stage)
+      int pks = 0;
+      auto prefetch_next = [&]() {
+        if (pw >= total) return;
+        const Unit u = A.units[pw / n_mt];
+        const int mt = (int)(pw % n_mt);
+#pragma unroll
+        for (int j = 0; j < KSUB; ++j) {
+          const int kx = (pks * KSUB + j) * BKB;
+          if (kx >= k_bytes) break;
+          tma_prefetch_3d(&map_a0, kx, mt * BM, u.slot);
+          if (NA == 2) tma_prefetch_3d(&map_a1, kx, mt * BM, u.slot);
+        }
+        if (++pks == nks) pks = 0, pw += gridDim.x;
+      };
+      for (int i = 0; i < PFD; ++i) prefetch_next();
+      // raw scale bytes of item number `no` (work item wi) into slot no & 1
+      auto raw_copy = [&](long long wi, long long no) -> bool {
+        const int slot = (int)(no & 1);
+        if (no >= 2 && !mbar_wait(&raw_empty[slot], (uint32_t)((no >> 1) - 1) & 1u, abort)) return false;
+        const Unit u = A.units[wi / n_mt];
+        const int mt = (int)(wi % n_mt);
+        const int rows_a = min(BM, A.n_rows - mt * BM);
+        const uint32_t bytes_a = (uint32_t)(rows_a * nkb + 15) & ~15u;
+        const uint8_t* sb = A.act_scales + (size_t)u.row_start * nkb;
+        const uint32_t lead = (uint32_t)(reinterpret_cast<uintptr_t>(sb) & 15);
+        const uint32_t bytes_b = (lead + (uint32_t)(u.ntok * nkb) + 15) & ~15u;
+        uint8_t* dst = raw_base + (size_t)slot * raw_slot;
+        const uint8_t* rec = A.bank + (size_t)u.slot * A.record_bytes;
+        mbar_expect_tx(&raw_full[slot], NA * bytes_a + bytes_b);
+        bulk_load(dst, rec + A.off_sc[0] + (size_t)mt * BM * nkb, bytes_a, &raw_full[slot]);
+        if (NA == 2) bulk_load(dst + raw_a, rec + A.off_sc[1] + (size_t)mt * BM * nkb, bytes_a, &raw_full[slot]);
+        bulk_load(dst + NA * raw_a, sb - lead, bytes_b, &raw_full[slot]);
+        return true;
+      };
+      long long item_no = 0;
+      if (RAW && total > blockIdx.x) ok = raw_copy(blockIdx.x, 0);
+      PF_T0;
+      for (long long w = blockIdx.x; w < total && ok; w += gridDim.x, ++item_no) {
         const Unit u = A.units[w / n_mt];
         const int mt = (int)(w % n_mt);
-        for (int ks = 0; ks < nks; ++ks, ++it) {
-          const int s = (int)(it % NSTAGE);
-          if (it >= NSTAGE && !mbar_wait(&empty[s], (uint32_t)((it / NSTAGE) - 1) & 1u, abort)) { ok = false; break; }
+        if (RAW && w + gridDim.x < total && !raw_copy(w + gridDim.x, item_no + 1)) { ok = false; break; }
+        for (int ks = 0; ks < nks; ++ks) {
+          PF_ADD(c_issue);
+          if (wrapped && !mbar_wait(&empty[s], ph ^ 1u, abort)) { ok = false; break; }
+          PF_ADD(c_wait);
           uint8_t* st = smem + (size_t)s * STAGE_BYTES;
           mbar_expect_tx(&full[s], KSUB * (NA * A_TILE + B_TILE));
 #pragma unroll
@@ -245,25 +335,48 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
           }
 #pragma unroll
           for (int j = 0; j < KSUB; ++j) tma_load_2d(st + OFF_B + j * B_TILE, &map_b, (ks * KSUB + j) * BKB, u.row_start, &full[s], pol_x);
+          if (++s == NSTAGE) s = 0, ph ^= 1u, wrapped = true;
+          prefetch_next();
         }
       }
+      PF_STORE(0, c_wait);
+      PF_STORE(1, c_issue);
     }
   } else if (warp == 1) {
     // ---- scale copies into TMEM and the MMAs -------------------------------------------------
+    // One thread issues everything, so its own instruction count is on the critical path: all descriptors are
+    // the stage's base descriptor plus a compile-time constant (addresses are in 16-byte units in the low bits).
     if (lane == 0) {
-      long long it = 0, item = 0;
+      int s = 0;
+      uint32_t ph = 0;
+      long long item = 0;
       bool ok = true;
+      const uint64_t d_op0 = desc_sw128(smem_u32(smem));
+      const uint64_t d_sf0 = desc_sf(smem_u32(smem) + OFF_SF);
+      const uint32_t t_sf = tmem + SF_COL;
+      long long c_acc = 0, c_full = 0, c_issue = 0;
+#ifdef CB_PF_TRACE
+      const long long t_begin = clock64();
+#endif
+      PF_T0;
       for (long long w = blockIdx.x; w < total && ok; w += gridDim.x, ++item) {
         const Unit u = A.units[w / n_mt];
         const int buf = (int)(item & 1);
-        const uint32_t idesc = idesc_mxf4((u.ntok + 15) & ~15);
+        const uint32_t id0 = idesc_mxf4((u.ntok + 15) & ~15);
+        const uint32_t id2 = id0 | (2u << 29) | (2u << 4);  // scale bytes 2,3 of the column for the second K=64 of a pair
+        const uint32_t t_acc = tmem + buf * ACC_COLS;
+        uint32_t accumulate = 0;
+        PF_ADD(c_issue);
         if (item >= 2 && !mbar_wait(&acc_empty[buf], (uint32_t)((item >> 1) - 1) & 1u, abort)) { ok = false; break; }
+        PF_ADD(c_acc);
         tc_fence_after();
-        for (int ks = 0; ks < nks; ++ks, ++it) {
-          const int s = (int)(it % NSTAGE);
-          if (!mbar_wait(&full[s], (uint32_t)(it / NSTAGE) & 1u, abort)) { ok = false; break; }
+        for (int ks = 0; ks < nks; ++ks) {
+          PF_ADD(c_issue);
+          if (!mbar_wait(&full[s], ph, abort)) { ok = false; break; }
+          PF_ADD(c_full);
           tc_fence_after();
-          const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
+          const uint64_t so = (uint64_t)((uint32_t)(s * STAGE_BYTES) >> 4);
+          const uint64_t dop = d_op0 + so, dsf = d_sf0 + so;
 #pragma unroll
           for (int j = 0; j < KSUB; ++j) {
             if ((ks * KSUB + j) * BKB >= k_bytes) break;  // piece wholly behind the end of K: zeros, nothing to add
@@ -274,29 +387,39 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
             for (int m = 0; m < NA + 1; ++m)
 #pragma unroll
               for (int q = 0; q < 2; ++q)
-                tc_cp_sf(tmem + SF_COL + (m * KSUB + j) * 8 + q * 4, desc_sf(st + OFF_SF + (m * KSUB + j) * SF_TILE + q * 512));
+                tc_cp_sf(t_sf + (m * KSUB + j) * 8 + q * 4, dsf + (uint64_t)(((m * KSUB + j) * SF_TILE + q * 512) >> 4));
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
-              const uint32_t sfid = (uint32_t)(kk & 1) * 2u, q = (uint32_t)kk >> 1;
-              const uint64_t db = desc_sw128(st + OFF_B + j * B_TILE + kk * 32);
-              const uint32_t tsfb = (tmem + SF_COL + (NA * KSUB + j) * 8 + q * 4) | (sfid << 30);
+              // the allocation's lane field is zero, so adding the byte selector into bits 30-31 equals OR-ing it
+              const uint32_t sel = (uint32_t)(kk & 1) << 31, q = (uint32_t)kk >> 1;
+              const uint64_t db = dop + (uint64_t)((OFF_B + j * B_TILE + kk * 32) >> 4);
+              const uint32_t tsfb = t_sf + (((NA * KSUB + j) * 8 + q * 4) | sel);
 #pragma unroll
               for (int m = 0; m < NA; ++m) {
-                const uint64_t da = desc_sw128(st + (m * KSUB + j) * A_TILE + kk * 32);
-                const uint32_t tsfa = (tmem + SF_COL + (m * KSUB + j) * 8 + q * 4) | (sfid << 30);
-                tc_mma(tmem + buf * ACC_COLS + m * NTMAX, da, db, idesc | (sfid << 29) | (sfid << 4), tsfa, tsfb,
-                       (ks > 0 || j > 0 || kk > 0) ? 1u : 0u);
+                const uint64_t da = dop + (uint64_t)(((m * KSUB + j) * A_TILE + kk * 32) >> 4);
+                const uint32_t tsfa = t_sf + (((m * KSUB + j) * 8 + q * 4) | sel);
+                tc_mma(t_acc + m * NTMAX, da, db, (kk & 1) ? id2 : id0, tsfa, tsfb, accumulate);
               }
+              accumulate = 1;
             }
           }
           tc_commit(&empty[s]);
+          if (++s == NSTAGE) s = 0, ph ^= 1u;
         }
         if (ok) tc_commit(&acc_full[buf]);
       }
+      PF_STORE(2, c_acc);
+      PF_STORE(3, c_full);
+      PF_STORE(4, c_issue);
+#ifdef CB_PF_TRACE
+      PF_STORE(5, clock64() - t_begin);
+#endif
+      PF_STORE(6, item);
     }
   } else if (warp < 6) {
     // ---- scale bytes: bank rows -> the stage's 32x16-byte groups --------------------------------
-    // One flat walk over (item, stage) with the next stage's bytes already on their way, also across items.
+    // One flat walk over (item, stage) with the next stage's bytes already on their way, also across items;
+    // the rows of the item after this one are pulled into L2 at the start of every item.
     const int m = (warp - 2) * 32 + lane;  // row of the tile
     const uint32_t sf_off = (uint32_t)((m & 31) * 16 + (m >> 5) * 4);
     const uint8_t *ra0 = nullptr, *ra1 = nullptr, *rb = nullptr;
@@ -311,50 +434,129 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
       vb = m < u.ntok;
       rb = A.act_scales + (size_t)(u.row_start + m) * nkb;
     };
-    uint2 cur[NA + 1][KSUB], nxt[NA + 1][KSUB];
-    auto fetch = [&](uint2 (&d)[NA + 1][KSUB], int ks) {
-#pragma unroll
-      for (int j = 0; j < KSUB; ++j) {
-        d[0][j] = load_sf8(ra0, (ks * KSUB + j) * 8, nkb, va);
-        if (NA == 2) d[1][j] = load_sf8(ra1, (ks * KSUB + j) * 8, nkb, va);
-        d[NA][j] = load_sf8(rb, (ks * KSUB + j) * 8, nkb, vb);
-      }
+    auto pull = [&](const uint8_t* p) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(p + nkb - 1));
     };
-    long long it = 0;
-    long long w = blockIdx.x;
-    if (w < total) {
-      point_at(w);
-      fetch(cur, 0);
-    }
-    int ks = 0;
-    while (w < total) {
-      // the stage after this one
-      long long w2 = w;
-      int ks2 = ks + 1;
-      if (ks2 == nks) ks2 = 0, w2 = w + gridDim.x;
-      if (w2 < total) {
-        if (ks2 == 0) point_at(w2);
-        fetch(nxt, ks2);
+    auto pull_item = [&](long long w) {
+      const Unit u = A.units[w / n_mt];
+      const int row_a = (int)(w % n_mt) * BM + m;
+      const uint8_t* rec = A.bank + (size_t)u.slot * A.record_bytes;
+      if (row_a < A.n_rows) {
+        pull(rec + A.off_sc[0] + (size_t)row_a * nkb);
+        if (NA == 2) pull(rec + A.off_sc[1] + (size_t)row_a * nkb);
       }
-      const int s = (int)(it % NSTAGE);
-      if (it >= NSTAGE && !__all_sync(0xffffffffu, mbar_wait(&empty[s], (uint32_t)((it / NSTAGE) - 1) & 1u, abort))) break;
+      if (m < u.ntok) pull(A.act_scales + (size_t)(u.row_start + m) * nkb);
+    };
+    static_assert(KSUB == 2, "the scale loaders fetch sixteen bytes = two pieces per stage");
+    // Three register sets in rotation: the bytes of stage i+2 are asked for before stage i is written, so a
+    // load has two stage times to arrive.
+    uint4 set_a[NA + 1], set_b[NA + 1], set_c[NA + 1];
+    const long long n_mine = total > blockIdx.x ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const long long n_stage = n_mine * nks;
+    long long wf = blockIdx.x, fetched = 0;  // fetch cursor: item and stage count
+    int ksf = 0;
+    // RAW: sixteen bytes of the row at byte offset `at` of the slot (2-byte aligned), blocks past nkb as 2**0
+    auto raw16 = [&](const uint8_t* base, int kb0, bool valid) -> uint4 {
+      uint4 r = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+      if (!valid) return r;
+      const uint16_t* p = reinterpret_cast<const uint16_t*>(base + kb0);
+      uint32_t* v = &r.x;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int n = nkb - kb0 - 4 * i;  // blocks left for word i
+        if (n >= 4) v[i] = (uint32_t)p[2 * i] | ((uint32_t)p[2 * i + 1] << 16);
+        else if (n > 0) {
+          const uint32_t lo = p[2 * i], hi = n > 2 ? p[2 * i + 1] : 0u;
+          const uint32_t keep = (1u << (8 * n)) - 1u;
+          v[i] = ((lo | (hi << 16)) & keep) | (0x7F7F7F7Fu & ~keep);
+        }
+      }
+      return r;
+    };
+    long long items_seen = 0;        // items whose raw bytes this warp has started to read
+    const uint8_t* raw_slot_ptr = nullptr;
+    uint32_t raw_lead = 0;
+    bool raw_ok = true;
+    auto fetch = [&](uint4 (&d)[NA + 1]) {
+      if (fetched >= n_stage) return;
+      if (RAW) {
+        if (ksf == 0) {
+          const Unit u = A.units[wf / n_mt];
+          va = (int)(wf % n_mt) * BM + m < A.n_rows;
+          vb = m < u.ntok;
+          raw_lead = (uint32_t)(reinterpret_cast<uintptr_t>(A.act_scales + (size_t)u.row_start * nkb) & 15);
+          const int slot = (int)(items_seen & 1);
+          raw_slot_ptr = raw_base + (size_t)slot * raw_slot;
+          if (!__all_sync(0xffffffffu, mbar_wait(&raw_full[slot], (uint32_t)(items_seen >> 1) & 1u, abort))) raw_ok = false;
+          ++items_seen;
+        }
+        if (raw_ok) {
+          d[0] = raw16(raw_slot_ptr + (size_t)m * nkb, ksf * 16, va);
+          if (NA == 2) d[1] = raw16(raw_slot_ptr + raw_a + (size_t)m * nkb, ksf * 16, va);
+          d[NA] = raw16(raw_slot_ptr + NA * raw_a + raw_lead + (size_t)m * nkb, ksf * 16, vb);
+        }
+        ++fetched;
+        if (++ksf == nks) {
+          ksf = 0, wf += gridDim.x;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&raw_empty[(items_seen - 1) & 1]);  // this warp is done with the slot
+        }
+        return;
+      }
+      if (ksf == 0) {
+        point_at(wf);
+        if (wf + gridDim.x < total) pull_item(wf + gridDim.x);
+      }
+#ifdef CB_PF_NOSFLOAD
+      d[0] = d[NA] = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+      if (NA == 2) d[1] = d[0];
+#else
+      d[0] = load_sf16(ra0, ksf * 16, nkb, va);
+      if (NA == 2) d[1] = load_sf16(ra1, ksf * 16, nkb, va);
+      d[NA] = load_sf16(rb, ksf * 16, nkb, vb);
+#endif
+      ++fetched;
+      if (++ksf == nks) ksf = 0, wf += gridDim.x;
+    };
+    int s = 0;
+    uint32_t ph = 0;
+    bool wrapped = false;
+    long long c_ld = 0, c_lw = 0;
+    PF_T0;
+    // writes one stage from `cur` after asking for the stage two ahead into `far`; false when a wait gave up
+    auto step = [&](uint4 (&cur)[NA + 1], uint4 (&far)[NA + 1]) -> bool {
+      fetch(far);
+      if (RAW && !raw_ok) return false;
+      PF_ADD(c_ld);
+      if (wrapped && !__all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u, abort))) return false;
+      PF_ADD(c_lw);
       uint8_t* sf = smem + (size_t)s * STAGE_BYTES + OFF_SF;
 #pragma unroll
-      for (int mm = 0; mm < NA + 1; ++mm)
-#pragma unroll
-        for (int j = 0; j < KSUB; ++j) {
-          *reinterpret_cast<uint32_t*>(sf + (mm * KSUB + j) * SF_TILE + sf_off) = cur[mm][j].x;
-          *reinterpret_cast<uint32_t*>(sf + (mm * KSUB + j) * SF_TILE + 512 + sf_off) = cur[mm][j].y;
-        }
+      for (int mm = 0; mm < NA + 1; ++mm) {
+        *reinterpret_cast<uint32_t*>(sf + (mm * 2) * SF_TILE + sf_off) = cur[mm].x;
+        *reinterpret_cast<uint32_t*>(sf + (mm * 2) * SF_TILE + 512 + sf_off) = cur[mm].y;
+        *reinterpret_cast<uint32_t*>(sf + (mm * 2 + 1) * SF_TILE + sf_off) = cur[mm].z;
+        *reinterpret_cast<uint32_t*>(sf + (mm * 2 + 1) * SF_TILE + 512 + sf_off) = cur[mm].w;
+      }
+#ifndef CB_PF_NOFENCE
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#endif
       __syncwarp();
       if (lane == 0) mbar_arrive(&full[s]);
-#pragma unroll
-      for (int mm = 0; mm < NA + 1; ++mm)
-#pragma unroll
-        for (int j = 0; j < KSUB; ++j) cur[mm][j] = nxt[mm][j];
-      ++it;
-      w = w2, ks = ks2;
+      if (++s == NSTAGE) s = 0, ph ^= 1u, wrapped = true;
+      return true;
+    };
+    fetch(set_a);
+    fetch(set_b);
+    for (long long i = 0; i < n_stage; i += 3) {
+      if (!step(set_a, set_c)) break;
+      if (i + 1 < n_stage && !step(set_b, set_a)) break;
+      if (i + 2 < n_stage && !step(set_c, set_b)) break;
+    }
+    if (warp == 2 && lane == 0) {
+      PF_STORE(9, c_ld);
+      PF_STORE(10, c_lw);
     }
   } else {
     // ---- accumulators -> results ----------------------------------------------------------------
@@ -364,13 +566,17 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
     const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
     long long item = 0;
     bool ok = true;
+    long long c_wait = 0, c_work = 0;
+    PF_T0;
     for (long long w = blockIdx.x; w < total && ok; w += gridDim.x, ++item) {
       const Unit u = A.units[w / n_mt];
       const int mt = (int)(w % n_mt);
       const int buf = (int)(item & 1);
       const int n = mt * BM + q * 32 + lane;           // weight row = output index
       const bool rows_ok = mt * BM + q * 32 < A.n_rows;  // whole warps: n_rows is a multiple of 32
+      PF_ADD(c_work);
       if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (uint32_t)(item >> 1) & 1u, abort))) { ok = false; break; }
+      PF_ADD(c_wait);
       tc_fence_after();
       for (int j0 = 16 * half; j0 < u.ntok; j0 += 32) {
         uint32_t g[16], up[16];
@@ -409,6 +615,10 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+    if (warp == 6 && lane == 0) {
+      PF_STORE(7, c_wait);
+      PF_STORE(8, c_work);
     }
   }
 
@@ -537,13 +747,14 @@ int make_map(CUtensorMap* m, const void* base, int row_bytes, long long row_pitc
   return CACHALOT_OK;
 }
 
-#ifndef CB_PF_KSUB
-#define CB_PF_KSUB 2
-#endif
-constexpr int KSUB = CB_PF_KSUB;
+constexpr int KSUB = 2;
 constexpr int STAGES_GU = 4 / KSUB, STAGES_DN = 6 / KSUB;
-constexpr size_t smem_bytes(int na, int nstage) {
-  return (size_t)nstage * KSUB * (na * A_TILE + B_TILE + (na + 1) * SF_TILE) + (2 * nstage + 4) * 8 + 16 + 1024;
+constexpr size_t SMEM_LIMIT = 227 * 1024;
+// stages, 256 bytes of barriers, optionally two raw scale slots, 1 KB of alignment slack
+size_t smem_bytes(int na, int nstage, int nkb, bool raw) {
+  size_t b = (size_t)nstage * KSUB * (na * A_TILE + B_TILE + (na + 1) * SF_TILE) + 256 + 1024;
+  if (raw) b += 2 * ((size_t)na * ((BM * nkb + 15) & ~15) + ((NTMAX * nkb + 30) & ~15));
+  return b;
 }
 
 struct Scratch {
@@ -579,7 +790,8 @@ Scratch carve(uint8_t* base, int hidden, int inter, size_t rows, int n_experts) 
 }  // namespace
 
 bool prefill_tc_supported(const BankView& v) {
-  return v.format == CACHALOT_BANK_FP4 && v.hidden % 128 == 0 && v.inter % 32 == 0 && (v.hidden / 2) % 16 == 0 &&
+  // inter a multiple of 64: rows of scale bytes start on even addresses (the loaders read them in 2-byte units)
+  return v.format == CACHALOT_BANK_FP4 && v.hidden % 128 == 0 && v.inter % 64 == 0 && (v.hidden / 2) % 16 == 0 &&
          (v.inter / 2) % 16 == 0 && v.record_bytes % 16 == 0;
 }
 
@@ -614,12 +826,12 @@ int launch_prefill_tc(const BankView& v, const void* x_bf16, const int32_t* perm
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(grouped_mxf4_kernel<2, STAGES_GU, KSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(2, STAGES_GU));
-    cudaFuncSetAttribute(grouped_mxf4_kernel<1, STAGES_DN, KSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(1, STAGES_DN));
-    attr_done = true;
-  }
+  auto launch = [&](auto kern, int na, int nstage, bool raw, const CUtensorMap& ma0, const CUtensorMap& ma1, const CUtensorMap& mb,
+                    const GemmArgs& ga) {
+    const size_t sm = smem_bytes(na, nstage, ga.k_codes / 32, raw);
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    kern<<<sms, NTHREADS, sm, stream>>>(ma0, ma1, mb, ga);
+  };
   GemmArgs a;
   a.bank = v.base;
   a.record_bytes = v.record_bytes;
@@ -639,7 +851,10 @@ int launch_prefill_tc(const BankView& v, const void* x_bf16, const int32_t* perm
   a.act_scales = s.x_scales;
   a.n_rows = I;
   a.k_codes = H;
-  grouped_mxf4_kernel<2, STAGES_GU, KSUB><<<sms, NTHREADS, smem_bytes(2, STAGES_GU), stream>>>(m_w1, m_w3, m_x, a);
+  if (smem_bytes(2, STAGES_GU, H / 32, true) <= SMEM_LIMIT)
+    launch(grouped_mxf4_kernel<2, STAGES_GU, KSUB, true>, 2, STAGES_GU, true, m_w1, m_w3, m_x, a);
+  else
+    launch(grouped_mxf4_kernel<2, STAGES_GU, KSUB, false>, 2, STAGES_GU, false, m_w1, m_w3, m_x, a);
   if ((rc = check_launch("moe_prefill gate/up (tcgen05)"))) return rc;
   // down: K = inter, N = hidden
   a.off_sc[0] = v.off[3];
@@ -647,10 +862,19 @@ int launch_prefill_tc(const BankView& v, const void* x_bf16, const int32_t* perm
   a.act_scales = s.h_scales;
   a.n_rows = H;
   a.k_codes = I;
-  grouped_mxf4_kernel<1, STAGES_DN, KSUB><<<sms, NTHREADS, smem_bytes(1, STAGES_DN), stream>>>(m_w2, m_w2, m_h, a);
+  if (smem_bytes(1, STAGES_DN, I / 32, true) <= SMEM_LIMIT)
+    launch(grouped_mxf4_kernel<1, STAGES_DN, KSUB, true>, 1, STAGES_DN, true, m_w2, m_w2, m_h, a);
+  else
+    launch(grouped_mxf4_kernel<1, STAGES_DN, KSUB, false>, 1, STAGES_DN, false, m_w2, m_w2, m_h, a);
   if ((rc = check_launch("moe_prefill down (tcgen05)"))) return rc;
   combine_kernel<<<tokens, 256, 0, stream>>>(s.y, s.inv, k, H, out);
   return check_launch("moe_prefill combine");
 }
 
 }  // namespace cachalot
+
+#ifdef CB_PF_TRACE
+extern "C" __attribute__((visibility("default"))) int cachalot_debug_prefill_trace(unsigned long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, cachalot::pf_trace, sizeof(unsigned long long) * 2 * 256 * 16);
+}
+#endif
