@@ -380,9 +380,6 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
 #pragma unroll
           for (int j = 0; j < KSUB; ++j) {
             if ((ks * KSUB + j) * BKB >= k_bytes) break;  // piece wholly behind the end of K: zeros, nothing to add
-#ifdef CB_PF_NOMMA
-            if (A.total_rows >= 0) break;
-#endif
 #pragma unroll
             for (int m = 0; m < NA + 1; ++m)
 #pragma unroll
@@ -508,14 +505,9 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
         point_at(wf);
         if (wf + gridDim.x < total) pull_item(wf + gridDim.x);
       }
-#ifdef CB_PF_NOSFLOAD
-      d[0] = d[NA] = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
-      if (NA == 2) d[1] = d[0];
-#else
       d[0] = load_sf16(ra0, ksf * 16, nkb, va);
       if (NA == 2) d[1] = load_sf16(ra1, ksf * 16, nkb, va);
       d[NA] = load_sf16(rb, ksf * 16, nkb, vb);
-#endif
       ++fetched;
       if (++ksf == nks) ksf = 0, wf += gridDim.x;
     };
@@ -539,9 +531,7 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
         *reinterpret_cast<uint32_t*>(sf + (mm * 2 + 1) * SF_TILE + sf_off) = cur[mm].z;
         *reinterpret_cast<uint32_t*>(sf + (mm * 2 + 1) * SF_TILE + 512 + sf_off) = cur[mm].w;
       }
-#ifndef CB_PF_NOFENCE
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
       __syncwarp();
       if (lane == 0) mbar_arrive(&full[s]);
       if (++s == NSTAGE) s = 0, ph ^= 1u, wrapped = true;
@@ -585,9 +575,6 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
         float wv = 0.f;
         if (NA == 2 && lane < 16 && j0 + lane < u.ntok) wv = A.gate_w[A.perm[u.row_start + j0 + lane]];
         tc_ld_wait();
-#ifdef CB_PF_NOEPI
-        if (A.total_rows >= 0) continue;
-#endif
         if (!rows_ok) continue;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
