@@ -277,8 +277,8 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
       bool wrapped = false, ok = true;
       long long c_wait = 0, c_issue = 0;
       // The shared-memory ring is only two or three stages deep, less than the HBM latency under load, so the
-      // weight tiles of the next PFD stages are asked into L2 ahead of their loads.
-      constexpr int PFD = NA == 2 ? 4 : 6;
+      // weight tiles of the next PFD stages are asked into L2 ahead of their loads (2 measured best of 0/2/4/8).
+      constexpr int PFD = 2;
       long long pw = blockIdx.x;  // prefetch cursor (item, stage)
       int pks = 0;
       auto prefetch_next = [&]() {
