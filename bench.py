@@ -53,6 +53,8 @@ def parse_args():
     p.add_argument("--distinct-layers", type=int, default=8)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-graph", action="store_true")
+    p.add_argument("--reduce", default="peer", choices=["peer", "nccl"],
+                   help="N > 1: how the ranks' partial layer outputs are summed (peer = the library's peer-memory kernel)")
     p.add_argument("--watchdog", type=int, default=0, help="dump all Python stacks and exit after this many seconds (0 = off)")
     return p.parse_args()
 
@@ -252,6 +254,27 @@ def run_ours(args):
     slots_all = torch.empty((LAYERS, B, K), dtype=torch.int32, device=dev)
     w_all = torch.empty((LAYERS, B, K), dtype=torch.float32, device=dev)
 
+    # cross-rank sum of the partial outputs: the library's peer-memory kernel, checked once against NCCL
+    peer_sum, reduce_kind = None, "none"
+    if world > 1:
+        reduce_kind = "nccl"
+        if args.reduce == "peer":
+            try:
+                peer_sum = ep.PeerSum(B * HIDDEN, dev)
+                probe = torch.randn((B, HIDDEN), generator=torch.Generator().manual_seed(100 + rank)).to(dev)
+                want = probe.clone()
+                dist.all_reduce(want)
+                got = peer_sum(probe.clone().view(-1), status=status).view(B, HIDDEN)
+                torch.cuda.synchronize(dev)
+                if int(status.item()) or not torch.allclose(got, want, rtol=1e-5, atol=1e-5):
+                    raise RuntimeError(f"peer sum differs from the NCCL sum (status {int(status.item())})")
+                reduce_kind = "peer"
+            except Exception as exc:  # no peer access / symmetric memory on this box: the library collective instead
+                if rank == 0:
+                    print(f"peer-memory sum unavailable ({exc}); using NCCL all_reduce", file=sys.stderr, flush=True)
+                peer_sum = None
+                status.zero_()
+
     def token_step():
         for l in range(LAYERS):
             if B == 1:   # routing tail and experts in one launch
@@ -260,7 +283,9 @@ def run_ours(args):
             else:
                 _, w, slots = cb.route_tail(logits[l], None, table, l % NL, K, 1.0, weights_bf16=False)
                 cb.moe_forward(x, slots, w, bank, swiglu_limit=SWIGLU_LIMIT, out=out, workspace=ws, status=status)
-            if world > 1:
+            if peer_sum is not None:
+                peer_sum(out.view(-1), status=status)
+            elif world > 1:
                 dist.all_reduce(out)
 
     def phase_step(phase):
@@ -390,12 +415,14 @@ def run_ours(args):
                              "algorithmic_bytes_per_launch": dn_alg, "traffic": NCU_TRAFFIC_BYTES.get((args.bank, B, "down"))}}
         launches = 4 * LAYERS * args.steps          # routing tail, row grouping, gate/up, down per layer
 
+    if peer_sum is not None:
+        launches += LAYERS * args.steps             # the peer-memory sum, one launch per layer
     line = {
         "metric": "moe_decode_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None,
         "dtype": "int2xbf16->f32" if args.bank == "affine2" else "e2m1xbf16->f32", "data": "synthetic",
-        "config": workload_config(args, {"parallelism": f"ep{world}", "cuda_graph": use_graph, "numerics_version": cb.NUMERICS_VERSION}),
+        "config": workload_config(args, {"parallelism": f"ep{world}", "partial_sum": reduce_kind, "cuda_graph": use_graph, "numerics_version": cb.NUMERICS_VERSION}),
         "clocks": clocks,
         "e2e": {"value": tok_s_e2e, "unit": "tok/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": int(x_host[0].numel() * 2 + logits_host[0].numel() * 4),

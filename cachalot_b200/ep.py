@@ -45,6 +45,47 @@ def reduce_partials(partial: torch.Tensor, group=None) -> torch.Tensor:
     return partial
 
 
+class PeerSum:
+    """Sum of the ranks' partial outputs through peer memory over NVLink (`cachalot_peer_sum`): one small
+    launch per rank instead of a library all-reduce.  The inboxes live in a symmetric allocation
+    (`torch.distributed._symmetric_memory`), mapped into every rank of the box.  `n` = floats per partial."""
+
+    def __init__(self, n: int, device: torch.device, group=None):
+        import ctypes
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from ._lib import lib
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank, self.n = dist.get_world_size(self.group), dist.get_rank(self.group), n
+        inbox = int(lib.cachalot_peer_sum_inbox_bytes(self.world, n))
+        flags = int(lib.cachalot_peer_sum_flag_bytes(self.world))
+        self._inbox_bytes = (inbox + 255) // 256 * 256
+        self.buf = symm.empty(self._inbox_bytes + flags, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, self.group)
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)   # every inbox is zeroed before anyone writes into it
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        arr = ctypes.c_void_p * self.world
+        self._inbox = arr(*ptrs)
+        self._flags = arr(*[p + self._inbox_bytes for p in ptrs])
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=device)
+
+    def __call__(self, partial: torch.Tensor, out: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+        from ._lib import check, lib
+
+        if partial.dtype != torch.float32 or partial.numel() != self.n or not partial.is_contiguous():
+            raise ValueError(f"partial must be contiguous float32 with {self.n} elements")
+        out = partial if out is None else out
+        stream = torch.cuda.current_stream(partial.device).cuda_stream
+        check(lib.cachalot_peer_sum(self._inbox, self._flags, self.world, self.rank, partial.data_ptr(), out.data_ptr(), self.n,
+                                    self.epoch.data_ptr(), status.data_ptr() if status is not None else None, stream))
+        return out
+
+
 def ep_moe_forward(x, slot_ids, gate_weights, bank, *, group=None, **kw) -> torch.Tensor:
     """moe_forward on this rank's shard followed by the cross-rank sum."""
     from .ops import moe_forward

@@ -237,6 +237,22 @@ CACHALOT_API int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc
                          void* workspace, size_t workspace_bytes, float* out, int* status,
                          cachalot_stream_t stream);
 
+/* ---- expert-parallel decode: sum of the ranks' partial outputs over peer memory ------------- */
+
+/* No counterpart in the reference (it is single-device).  Every rank r owns, in memory that all
+ * ranks of the box can write (CUDA IPC / a symmetric allocation made by the host), an inbox of
+ * cachalot_peer_sum_inbox_bytes(world, n) bytes and a flag array of cachalot_peer_sum_flag_bytes
+ * bytes, both zeroed once before the first call; inbox_ptrs[r] / flag_ptrs[r] (host arrays of
+ * device pointers, as mapped in THIS process) are rank r's.  epoch: u32 [2] in local device
+ * memory, zeroed once.  Every rank calls with its own partial f32 [n]; out f32 [n] receives the
+ * sum in rank order on every rank.  All ranks must make the same sequence of calls; a peer that
+ * does not show up makes the bounded wait expire (CACHALOT_STATUS_WAIT_EXPIRED in *status) and
+ * the call returns with an incomplete sum instead of hanging.  world <= 8, n a multiple of 4. */
+CACHALOT_API size_t cachalot_peer_sum_inbox_bytes(int world, int n);
+CACHALOT_API size_t cachalot_peer_sum_flag_bytes(int world);
+CACHALOT_API int cachalot_peer_sum(void* const* inbox_ptrs /* host */, void* const* flag_ptrs /* host */, int world, int rank,
+                      const float* partial, float* out, int n, uint32_t* epoch, int* status, cachalot_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
