@@ -11,7 +11,7 @@ _BANK = ("FP4_FORMAT", "ExpertFormat", "ResidentExpert", "SlabBank", "affine_for
 _OPS = (
     "QuantizedActivation", "RouterResult", "affine_routed_experts", "dequantize_affine", "dequantize_fp4_weight",
     "fp8_linear", "fp8_linear_quantized", "fused_routed_experts", "group_rows", "moe_forward", "moe_layer_decode",
-    "moe_prefill_grouped",
+    "combine_rows", "moe_prefill_grouped", "moe_prefill_rows",
     "quantize_fp8_activation", "quantize_mxfp4", "route_tail", "route_topk", "route_topk_fused", "route_topk_rows",
     "routed_expert_forward", "router_logits",
 )

@@ -62,6 +62,9 @@ SIGNATURES = {
     "cachalot_group_rows": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "cachalot_mxfp4_act_quant": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp]),
     "cachalot_moe_prefill_workspace_bytes": (_sz, [_desc, _i, _i, _i]),
+    "cachalot_moe_prefill_rows_workspace_bytes": (_sz, [_desc, C.c_longlong, _i]),
+    "cachalot_moe_prefill_rows": (_i, [_vp, _desc, _vp, _vp, _vp, _vp, _vp, _i, C.c_longlong, _f, _vp, _sz, _vp, _vp, _vp]),
+    "cachalot_moe_combine_rows": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
     "cachalot_peer_sum_inbox_bytes": (_sz, [_i, _i]),
     "cachalot_peer_sum_flag_bytes": (_sz, [_i]),
     "cachalot_peer_sum": (_i, [_vp, _vp, _i, _i, _vp, _vp, _i, _vp, _vp, _vp]),

@@ -68,6 +68,13 @@ int launch_prefill_tc(const BankView& v, const void* x_bf16, const int32_t* perm
                       const int32_t* slot_of_expert, const float* gate_w, int tokens, int k, int n_experts, float limit,
                       void* workspace, float* out, int* status, cudaStream_t stream);
 size_t prefill_tc_workspace_bytes(int hidden, int inter, int tokens, int k, int n_experts);
+// the same from already quantised rows laid out in segments, up to the per-row outputs (what an expert-parallel
+// rank runs between the dispatch and the combine exchange), and the slot-ordered sum of a token's rows
+int launch_prefill_rows(const BankView& v, const uint8_t* x_codes, const uint8_t* x_scales, const float* row_w,
+                        const int32_t* seg_offsets, const int32_t* seg_slot, int n_seg, long long rows, float limit, bool zero_absent,
+                        void* workspace, __nv_bfloat16* y, int* status, cudaStream_t stream);
+size_t prefill_rows_workspace_bytes(int inter, long long rows, int n_seg);
+int launch_combine_rows(const __nv_bfloat16* y, const int32_t* inv, int tokens, int k, int hidden, float* out, cudaStream_t stream);
 bool prefill_tc_supported(const BankView& v);
 
 }  // namespace cachalot

@@ -419,6 +419,39 @@ extern "C" int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc* 
   return launch_decode<CACHALOT_BANK_AFFINE>(v, x_in, slots, gate_w, tokens, k, swiglu_limit, num, hidden, out, CACHALOT_F32, status, s, mxfp4_act != 0);
 }
 
+extern "C" size_t cachalot_moe_prefill_rows_workspace_bytes(const cachalot_bank_desc* desc, long long rows, int n_segments) {
+  if (!desc || rows <= 0 || n_segments <= 0) return 0;
+  return prefill_rows_workspace_bytes(desc->inter, rows, n_segments);
+}
+
+extern "C" int cachalot_moe_prefill_rows(const void* bank, const cachalot_bank_desc* desc, const uint8_t* x_codes,
+                                         const uint8_t* x_scales, const float* row_weights, const int32_t* seg_offsets,
+                                         const int32_t* seg_slot, int n_segments, long long rows, float swiglu_limit,
+                                         void* workspace, size_t workspace_bytes, void* y_bf16, int* status,
+                                         cachalot_stream_t stream) {
+  BankView v;
+  int rc = make_view(bank, desc, &v, "moe_prefill_rows");
+  if (rc) return rc;
+  if (rows < 0 || n_segments < 0 || rows > 0x7fffffff) return fail(CACHALOT_EINVAL, "moe_prefill_rows: bad shape");
+  if (rows == 0 || n_segments == 0) return CACHALOT_OK;
+  if (!x_codes || !x_scales || !row_weights || !seg_offsets || !y_bf16) return fail(CACHALOT_EINVAL, "moe_prefill_rows: null pointer");
+  if (!prefill_tc_supported(v))
+    return fail(CACHALOT_EUNSUPPORTED, "moe_prefill_rows: needs an FP4 bank with hidden a multiple of 128 and inter a multiple of 64");
+  if (!aligned(x_codes, 16)) return fail(CACHALOT_EALIGN, "moe_prefill_rows: x_codes must be 16-byte aligned");
+  const size_t need = prefill_rows_workspace_bytes(v.inter, rows, n_segments);
+  if (!workspace || workspace_bytes < need) return fail(CACHALOT_ESCRATCH, "moe_prefill_rows: workspace %zu < %zu bytes", workspace_bytes, need);
+  if (!aligned(workspace, 256)) return fail(CACHALOT_EALIGN, "moe_prefill_rows: workspace must be 256-byte aligned");
+  return launch_prefill_rows(v, x_codes, x_scales, row_weights, seg_offsets, seg_slot, n_segments, rows, swiglu_limit, true, workspace,
+                             static_cast<__nv_bfloat16*>(y_bf16), status, (cudaStream_t)stream);
+}
+
+extern "C" int cachalot_moe_combine_rows(const void* y_bf16, const int32_t* inv, int tokens, int k, int hidden, float* out,
+                                         cachalot_stream_t stream) {
+  if (!y_bf16 || !inv || !out) return fail(CACHALOT_EINVAL, "moe_combine_rows: null pointer");
+  if (tokens < 0 || k <= 0 || hidden <= 0 || hidden % 2) return fail(CACHALOT_EINVAL, "moe_combine_rows: bad shape");
+  return launch_combine_rows(static_cast<const __nv_bfloat16*>(y_bf16), inv, tokens, k, hidden, out, (cudaStream_t)stream);
+}
+
 // ---- decode with built-in scratch (no allocation anywhere) ------------------------------------
 
 namespace cachalot {

@@ -4,7 +4,7 @@
 // weights as the M side of the MMA so that an expert with few rows wastes no tensor-core work:
 //
 //   gate/up : D_g, D_u [128 weight rows, <=96 routed rows] = W1/W3 tile . X^T      K = hidden
-//             epilogue  h = silu(min(g,L)) * clip(u) * gate_w  -> MXFP4 per 32 along the weight-row axis
+//             epilogue  h = silu(min(g,L)) * clip(u) * row weight  -> MXFP4 per 32 along the weight-row axis
 //   down    : D   [128 weight rows, <=96 routed rows]        = W2 tile . H^T        K = inter
 //             epilogue  y -> bf16, stored per routed row; a last kernel adds a token's k rows in slot order
 //
@@ -162,8 +162,7 @@ struct GemmArgs {
   int k_codes;                // K
   int total_rows;             // routed rows R
   // gate/up epilogue
-  const int32_t* perm;
-  const float* gate_w;
+  const float* row_w;         // f32 [R] router weight of every grouped row
   float limit;
   uint8_t* h_codes;           // u8 [R, N/2]
   uint8_t* h_scales;          // u8 [R, N/32]
@@ -573,7 +572,7 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
         tc_ld16(lane_base + buf * ACC_COLS + j0, g);
         if (NA == 2) tc_ld16(lane_base + buf * ACC_COLS + NTMAX + j0, up);
         float wv = 0.f;
-        if (NA == 2 && lane < 16 && j0 + lane < u.ntok) wv = A.gate_w[A.perm[u.row_start + j0 + lane]];
+        if (NA == 2 && lane < 16 && j0 + lane < u.ntok) wv = A.row_w[u.row_start + j0 + lane];
         tc_ld_wait();
         if (!rows_ok) continue;
 #pragma unroll
@@ -627,8 +626,9 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
 
 // one CTA per expert: inverse permutation and source token of every grouped row of a present expert
 __global__ void plan_rows_kernel(const int32_t* __restrict__ perm, const int32_t* __restrict__ offsets,
-                                 const int32_t* __restrict__ slot_of_expert, int n_slots, int k, int32_t* __restrict__ inv,
-                                 int32_t* __restrict__ src_token, int* __restrict__ status) {
+                                 const int32_t* __restrict__ slot_of_expert, int n_slots, int k, const float* __restrict__ gate_w,
+                                 int32_t* __restrict__ inv, int32_t* __restrict__ src_token, float* __restrict__ row_w,
+                                 int* __restrict__ status) {
   const int e = blockIdx.x;
   const int s = slot_of_expert ? slot_of_expert[e] : e;
   const bool present = s >= 0 && s < n_slots;
@@ -636,6 +636,7 @@ __global__ void plan_rows_kernel(const int32_t* __restrict__ perm, const int32_t
   for (int p = offsets[e] + threadIdx.x; p < offsets[e + 1]; p += blockDim.x) {
     const int r = perm[p];
     src_token[p] = r / k;
+    row_w[p] = gate_w[r];
     if (present) inv[r] = p;
   }
 }
@@ -680,6 +681,17 @@ __global__ void plan_units_kernel(const int32_t* __restrict__ offsets, const int
       units[at++] = u;
     }
   }
+}
+
+// one CTA per segment: rows of a segment whose expert is absent give zeros
+__global__ void zero_absent_rows_kernel(const int32_t* __restrict__ offsets, const int32_t* __restrict__ seg_slot, int n_slots,
+                                        int hidden, __nv_bfloat16* __restrict__ y) {
+  const int g = blockIdx.x;
+  const int s = seg_slot ? seg_slot[g] : g;
+  if (s >= 0 && s < n_slots) return;
+  uint32_t* base = reinterpret_cast<uint32_t*>(y + (size_t)offsets[g] * hidden);
+  const size_t words = (size_t)(offsets[g + 1] - offsets[g]) * hidden / 2;
+  for (size_t i = threadIdx.x; i < words; i += blockDim.x) base[i] = 0u;
 }
 
 // out[t, :] = sum over the token's route slots j = 0..k-1 (in that order) of its row of y
@@ -744,14 +756,36 @@ size_t smem_bytes(int na, int nstage, int nkb, bool raw) {
   return b;
 }
 
-struct Scratch {
-  uint8_t *x_codes, *x_scales, *h_codes, *h_scales;
-  __nv_bfloat16* y;
-  int32_t *inv, *src_token, *n_units;
+struct RowScratch {  // of the rows-level entry
+  uint8_t *h_codes, *h_scales;
+  int32_t* n_units;
   Unit* units;
   size_t total;
 };
+RowScratch carve_rows(uint8_t* base, int inter, size_t rows, int n_seg) {
+  RowScratch s;
+  size_t at = 0;
+  auto take = [&](size_t bytes) {
+    uint8_t* p = base ? base + at : nullptr;
+    at += align_up(bytes, 256);
+    return p;
+  };
+  s.h_codes = take(rows * (inter / 2));
+  s.h_scales = take(rows * (inter / 32) + 32);
+  s.units = reinterpret_cast<Unit*>(take((rows / NTMAX + n_seg + 1) * sizeof(Unit)));
+  s.n_units = reinterpret_cast<int32_t*>(take(256));
+  s.total = at;
+  return s;
+}
 
+struct Scratch {  // of the whole prefill call: quantised input, per-row arrays, then the rows-level scratch
+  uint8_t *x_codes, *x_scales;
+  __nv_bfloat16* y;
+  int32_t *inv, *src_token;
+  float* row_w;
+  uint8_t* rows_ws;
+  size_t total;
+};
 Scratch carve(uint8_t* base, int hidden, int inter, size_t rows, int n_experts) {
   Scratch s;
   size_t at = 0;
@@ -760,16 +794,13 @@ Scratch carve(uint8_t* base, int hidden, int inter, size_t rows, int n_experts) 
     at += align_up(bytes, 256);
     return p;
   };
-  // NTMAX rows of slack behind the code arrays: a unit's tile load always covers NTMAX rows
   s.x_codes = take(rows * (hidden / 2));
-  s.x_scales = take(rows * (hidden / 32));
-  s.h_codes = take(rows * (inter / 2));
-  s.h_scales = take(rows * (inter / 32));
+  s.x_scales = take(rows * (hidden / 32) + 32);
   s.y = reinterpret_cast<__nv_bfloat16*>(take(rows * hidden * 2));
   s.inv = reinterpret_cast<int32_t*>(take(rows * 4));
   s.src_token = reinterpret_cast<int32_t*>(take(rows * 4));
-  s.units = reinterpret_cast<Unit*>(take((rows / NTMAX + n_experts + 1) * sizeof(Unit)));
-  s.n_units = reinterpret_cast<int32_t*>(take(256));
+  s.row_w = reinterpret_cast<float*>(take(rows * 4));
+  s.rows_ws = take(carve_rows(nullptr, inter, rows, n_experts).total);
   s.total = at;
   return s;
 }
@@ -785,30 +816,28 @@ bool prefill_tc_supported(const BankView& v) {
 size_t prefill_tc_workspace_bytes(int hidden, int inter, int tokens, int k, int n_experts) {
   return carve(nullptr, hidden, inter, (size_t)tokens * k, n_experts).total;
 }
+size_t prefill_rows_workspace_bytes(int inter, long long rows, int n_seg) { return carve_rows(nullptr, inter, (size_t)rows, n_seg).total; }
 
-int launch_prefill_tc(const BankView& v, const void* x_bf16, const int32_t* perm, const int32_t* offsets,
-                      const int32_t* slot_of_expert, const float* gate_w, int tokens, int k, int n_experts, float limit,
-                      void* workspace, float* out, int* status, cudaStream_t stream) {
+// Grouped rows in, per-row expert outputs out: x_codes/x_scales = MXFP4 rows [rows, H/2] / [rows, H/32] laid out in
+// segments (seg_offsets i32 [n_seg+1], device), segment g belongs to bank slot seg_slot[g] (null: g; out of range or
+// negative: absent -> zero rows when zero_absent), row_w f32 [rows]; y bf16 [rows, H].
+int launch_prefill_rows(const BankView& v, const uint8_t* x_codes, const uint8_t* x_scales, const float* row_w,
+                        const int32_t* seg_offsets, const int32_t* seg_slot, int n_seg, long long rows, float limit, bool zero_absent,
+                        void* workspace, __nv_bfloat16* y, int* status, cudaStream_t stream) {
   if (!prefill_tc_supported(v)) return CACHALOT_EUNSUPPORTED;
+  if (rows <= 0 || n_seg <= 0) return CACHALOT_OK;
   const int H = v.hidden, I = v.inter;
-  const size_t rows = (size_t)tokens * k;
-  const Scratch s = carve(static_cast<uint8_t*>(workspace), H, I, rows, n_experts);
-
+  const RowScratch s = carve_rows(static_cast<uint8_t*>(workspace), I, (size_t)rows, n_seg);
   CUtensorMap m_w1, m_w3, m_w2, m_x, m_h;
   int rc;
   if ((rc = make_map(&m_w1, v.base + v.off[0], H / 2, H / 2, I, v.record_bytes, v.n_slots, BM))) return rc;
   if ((rc = make_map(&m_w3, v.base + v.off[4], H / 2, H / 2, I, v.record_bytes, v.n_slots, BM))) return rc;
   if ((rc = make_map(&m_w2, v.base + v.off[2], I / 2, I / 2, H, v.record_bytes, v.n_slots, BM))) return rc;
-  if ((rc = make_map(&m_x, s.x_codes, H / 2, H / 2, (int)rows, 0, 0, NTMAX))) return rc;
+  if ((rc = make_map(&m_x, x_codes, H / 2, H / 2, (int)rows, 0, 0, NTMAX))) return rc;
   if ((rc = make_map(&m_h, s.h_codes, I / 2, I / 2, (int)rows, 0, 0, NTMAX))) return rc;
-
-  cudaError_t e = cudaMemsetAsync(s.inv, 0xFF, rows * 4, stream);
-  if (e == cudaSuccess) e = cudaMemsetAsync(s.src_token, 0, rows * 4, stream);
-  if (e != cudaSuccess) return fail(CACHALOT_ECUDA, "moe_prefill: memset: %s", cudaGetErrorString(e));
-  plan_rows_kernel<<<n_experts, 128, 0, stream>>>(perm, offsets, slot_of_expert, v.n_slots, k, s.inv, s.src_token, status);
-  plan_units_kernel<<<1, 256, 256 * sizeof(int32_t), stream>>>(offsets, slot_of_expert, n_experts, v.n_slots, s.units, s.n_units);
+  plan_units_kernel<<<1, 256, 256 * sizeof(int32_t), stream>>>(seg_offsets, seg_slot, n_seg, v.n_slots, s.units, s.n_units);
+  if (zero_absent) zero_absent_rows_kernel<<<n_seg, 256, 0, stream>>>(seg_offsets, seg_slot, v.n_slots, H, y);
   if ((rc = check_launch("moe_prefill plan"))) return rc;
-  if ((rc = cachalot_mxfp4_act_quant(x_bf16, s.src_token, (int)rows, H, s.x_codes, s.x_scales, stream))) return rc;
 
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -825,17 +854,16 @@ int launch_prefill_tc(const BankView& v, const void* x_bf16, const int32_t* perm
   a.units = s.units;
   a.n_units = s.n_units;
   a.total_rows = (int)rows;
-  a.perm = perm;
-  a.gate_w = gate_w;
+  a.row_w = row_w;
   a.limit = limit;
   a.h_codes = s.h_codes;
   a.h_scales = s.h_scales;
-  a.y = s.y;
+  a.y = y;
   a.status = status;
   // gate/up: K = hidden, N = inter
   a.off_sc[0] = v.off[1];
   a.off_sc[1] = v.off[5];
-  a.act_scales = s.x_scales;
+  a.act_scales = x_scales;
   a.n_rows = I;
   a.k_codes = H;
   if (smem_bytes(2, STAGES_GU, H / 32, true) <= SMEM_LIMIT)
@@ -853,9 +881,36 @@ int launch_prefill_tc(const BankView& v, const void* x_bf16, const int32_t* perm
     launch(grouped_mxf4_kernel<1, STAGES_DN, KSUB, true>, 1, STAGES_DN, true, m_w2, m_w2, m_h, a);
   else
     launch(grouped_mxf4_kernel<1, STAGES_DN, KSUB, false>, 1, STAGES_DN, false, m_w2, m_w2, m_h, a);
-  if ((rc = check_launch("moe_prefill down (tcgen05)"))) return rc;
-  combine_kernel<<<tokens, 256, 0, stream>>>(s.y, s.inv, k, H, out);
+  return check_launch("moe_prefill down (tcgen05)");
+}
+
+int launch_combine_rows(const __nv_bfloat16* y, const int32_t* inv, int tokens, int k, int hidden, float* out, cudaStream_t stream) {
+  if (tokens <= 0) return CACHALOT_OK;
+  combine_kernel<<<tokens, 256, 0, stream>>>(y, inv, k, hidden, out);
   return check_launch("moe_prefill combine");
+}
+
+int launch_prefill_tc(const BankView& v, const void* x_bf16, const int32_t* perm, const int32_t* offsets,
+                      const int32_t* slot_of_expert, const float* gate_w, int tokens, int k, int n_experts, float limit,
+                      void* workspace, float* out, int* status, cudaStream_t stream) {
+  if (!prefill_tc_supported(v)) return CACHALOT_EUNSUPPORTED;
+  const int H = v.hidden, I = v.inter;
+  const size_t rows = (size_t)tokens * k;
+  const Scratch s = carve(static_cast<uint8_t*>(workspace), H, I, rows, n_experts);
+  cudaError_t e = cudaMemsetAsync(s.inv, 0xFF, rows * 4, stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(s.src_token, 0, rows * 4, stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(s.row_w, 0, rows * 4, stream);
+  if (e != cudaSuccess) return fail(CACHALOT_ECUDA, "moe_prefill: memset: %s", cudaGetErrorString(e));
+  plan_rows_kernel<<<n_experts, 128, 0, stream>>>(perm, offsets, slot_of_expert, v.n_slots, k, gate_w, s.inv, s.src_token, s.row_w,
+                                                 status);
+  int rc;
+  if ((rc = check_launch("moe_prefill plan rows"))) return rc;
+  if ((rc = cachalot_mxfp4_act_quant(x_bf16, s.src_token, (int)rows, H, s.x_codes, s.x_scales, stream))) return rc;
+  // rows of absent experts are skipped by the combine (inv = -1), so they need no zeroing
+  if ((rc = launch_prefill_rows(v, s.x_codes, s.x_scales, s.row_w, offsets, slot_of_expert, n_experts, (long long)rows, limit, false,
+                                s.rows_ws, s.y, status, stream)))
+    return rc;
+  return launch_combine_rows(s.y, s.inv, tokens, k, H, out, stream);
 }
 
 }  // namespace cachalot

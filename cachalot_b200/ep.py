@@ -91,3 +91,71 @@ def ep_moe_forward(x, slot_ids, gate_weights, bank, *, group=None, **kw) -> torc
     from .ops import moe_forward
 
     return reduce_partials(moe_forward(x, slot_ids, gate_weights, bank, **kw), group)
+
+
+def _all_to_all_rows(send: torch.Tensor, send_rows: list[int], recv_rows: list[int], group) -> torch.Tensor:
+    """Variable all-to-all over the leading dimension: block d of `send` (send_rows[d] rows) goes to rank d."""
+    import torch.distributed as dist
+
+    recv = torch.empty((sum(recv_rows), *send.shape[1:]), dtype=send.dtype, device=send.device)
+    dist.all_to_all_single(recv, send.contiguous(), output_split_sizes=recv_rows, input_split_sizes=send_rows, group=group)
+    return recv
+
+
+def ep_moe_prefill(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, bank, *, n_experts: int, layer: int = 0,
+                   swiglu_limit: float = 10.0, group=None, status: torch.Tensor | None = None, backend=None) -> torch.Tensor:
+    """Expert-parallel prefill of this rank's tokens: x bf16 [T_local,H], expert_ids int32 [T_local,k] (global
+    ids), weights float32 [T_local,k]; `bank` is this rank's shard whose slot table maps a global expert id to
+    a local slot (-1 for experts of other ranks).  Returns float32 [T_local,H].
+
+    Rows are grouped by global expert, quantised to MXFP4 (codes + scale bytes: 0.53 bytes per element cross
+    NVLink instead of 2), dispatched to the owners of their experts with a variable all-to-all, run through
+    the grouped FP4 GEMMs there, sent back as bf16 rows and summed per token in route-slot order -- the same
+    arithmetic and the same order as `moe_prefill_grouped(mxfp4_act=1)` on one GPU.
+
+    `backend` supplies group_rows / quantize_mxfp4 / moe_prefill_rows / combine_rows (default: this
+    package's CUDA operators; the CPU tests of the exchange pass stand-ins)."""
+    import torch.distributed as dist
+
+    if backend is None:
+        from . import ops as backend
+    group = group if group is not None else dist.group.WORLD
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    per = -(-n_experts // world)
+    t, k = expert_ids.shape
+    dev = x.device
+
+    perm, offsets = backend.group_rows(expert_ids, n_experts, status)
+    n_grouped = t * k
+    src_token = torch.div(perm, k, rounding_mode="floor")
+    codes, scales = backend.quantize_mxfp4(x, src_token)
+    row_w = weights.to(torch.float32).reshape(-1)[perm.long()]
+
+    counts = torch.zeros(world * per, dtype=torch.int64, device=dev)
+    counts[:n_experts] = (offsets[1:] - offsets[:-1]).to(torch.int64)
+    send_counts = counts.view(world, per)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts.contiguous(), group=group)
+    send_rows = send_counts.sum(1).tolist()   # host sync: the collective needs the split sizes
+    recv_rows = recv_counts.sum(1).tolist()
+    kept = sum(send_rows)                      # rows with an expert id in range (the others were dropped by the grouping)
+
+    r_codes = _all_to_all_rows(codes[:kept], send_rows, recv_rows, group)
+    r_scales = _all_to_all_rows(scales[:kept], send_rows, recv_rows, group)
+    r_w = _all_to_all_rows(row_w[:kept], send_rows, recv_rows, group)
+
+    # what arrived is ordered by source rank, then by local expert: one segment per (source, expert)
+    seg_offsets = torch.zeros(world * per + 1, dtype=torch.int32, device=dev)
+    seg_offsets[1:] = torch.cumsum(recv_counts.reshape(-1), 0).to(torch.int32)
+    lo = rank * per
+    local = torch.full((per,), -1, dtype=torch.int32, device=dev)
+    n_own = max(0, min(per, n_experts - lo))
+    if n_own:
+        local[:n_own] = bank.slot_table[layer, lo:lo + n_own].to(device=dev, dtype=torch.int32)
+    seg_slots = local.repeat(world)
+    y = backend.moe_prefill_rows(r_codes, r_scales, r_w, seg_offsets, seg_slots, bank, swiglu_limit=swiglu_limit, status=status)
+
+    y_home = _all_to_all_rows(y, recv_rows, send_rows, group)
+    inv = torch.full((n_grouped,), -1, dtype=torch.int32, device=dev)
+    inv[perm[:kept].long()] = torch.arange(kept, dtype=torch.int32, device=dev)
+    return backend.combine_rows(y_home, inv, t, k)

@@ -430,3 +430,38 @@ def moe_prefill_grouped(x: torch.Tensor, expert_ids: torch.Tensor, weights: torc
                                    _ptr(weights.to(torch.float32).contiguous()), t, k, e, float(swiglu_limit), int(mxfp4_act),
                                    base, ws.numel() - (base - ws.data_ptr()), _ptr(out), _ptr(status), _stream()))
     return out
+
+
+def moe_prefill_rows(x_codes: torch.Tensor, x_scales: torch.Tensor, row_weights: torch.Tensor, seg_offsets: torch.Tensor,
+                     seg_slots: torch.Tensor | None, bank: SlabBank, *, swiglu_limit: float = 10.0,
+                     status: torch.Tensor | None = None) -> torch.Tensor:
+    """Expert outputs of rows that are already MXFP4-quantised and laid out in segments (one expert per segment):
+    codes uint8 [R,H/2], scale bytes uint8 [R,H/32], row_weights float32 [R], seg_offsets int32 [S+1],
+    seg_slots int32 [S] bank slots (-1 = absent -> zero rows) -> bfloat16 [R,H].  The middle of
+    `moe_prefill_grouped`, which an expert-parallel rank runs between its dispatch and combine exchanges."""
+    _need_cuda(x_codes, x_scales, row_weights, seg_offsets)
+    rows = x_codes.shape[0]
+    n_seg = seg_offsets.numel() - 1
+    y = torch.empty((rows, bank.hidden), dtype=torch.bfloat16, device=x_codes.device)
+    if rows == 0 or n_seg <= 0:
+        return y
+    need = lib.cachalot_moe_prefill_rows_workspace_bytes(bank.desc_ptr, rows, n_seg)
+    ws = _workspace(x_codes.device, need + 256)
+    base = (ws.data_ptr() + 255) // 256 * 256
+    slots = None if seg_slots is None else seg_slots.to(torch.int32).contiguous()
+    check(lib.cachalot_moe_prefill_rows(_ptr(bank.slab), bank.desc_ptr, _ptr(x_codes.contiguous()), _ptr(x_scales.contiguous()),
+                                        _ptr(row_weights.to(torch.float32).contiguous()), _ptr(seg_offsets.to(torch.int32).contiguous()),
+                                        _ptr(slots), n_seg, rows, float(swiglu_limit), base, ws.numel() - (base - ws.data_ptr()),
+                                        _ptr(y), _ptr(status), _stream()))
+    return y
+
+
+def combine_rows(y: torch.Tensor, inv: torch.Tensor, tokens: int, k: int) -> torch.Tensor:
+    """out[t] = sum over route slots j = 0..k-1, in that order, of y[inv[t*k+j]] (inv < 0 skipped)
+    (model/moe_prefill_grouped.py:526-530): y bfloat16 [R,H], inv int32 [T*k] -> float32 [T,H]."""
+    _need_cuda(y, inv)
+    out = torch.empty((tokens, y.shape[1]), dtype=torch.float32, device=y.device)
+    if tokens:
+        check(lib.cachalot_moe_combine_rows(_ptr(y.contiguous()), _ptr(inv.to(torch.int32).contiguous()), tokens, k, y.shape[1],
+                                            _ptr(out), _stream()))
+    return out

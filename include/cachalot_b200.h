@@ -237,6 +237,24 @@ CACHALOT_API int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc
                          void* workspace, size_t workspace_bytes, float* out, int* status,
                          cachalot_stream_t stream);
 
+/* The two halves of cachalot_moe_prefill that an expert-parallel rank runs on either side of its
+ * exchanges (no counterpart in the single-device reference; the arithmetic is that of
+ * cachalot_moe_prefill with mxfp4_act = 1).
+ * cachalot_moe_prefill_rows: rows already quantised to MXFP4 (cachalot_mxfp4_act_quant) and laid
+ * out in segments -- seg_offsets i32 [n_segments+1] (device), segment g holds rows of the expert
+ * in bank slot seg_slot[g] (NULL: slot g; negative or out of range: absent, its rows come back as
+ * zeros); row_weights f32 [rows] = the router weight of every row -> y bf16 [rows, H], the
+ * expert output of every row (gate/up, SwiGLU, weight, MXFP4 of the hidden activation, down).
+ * FP4 bank only.  cachalot_moe_combine_rows: out[t,:] = sum over j = 0..k-1, in that order, of
+ * y[inv[t*k+j],:], skipping inv < 0. */
+CACHALOT_API size_t cachalot_moe_prefill_rows_workspace_bytes(const cachalot_bank_desc* desc /* host */, long long rows, int n_segments);
+CACHALOT_API int cachalot_moe_prefill_rows(const void* bank, const cachalot_bank_desc* desc /* host */, const uint8_t* x_codes,
+                              const uint8_t* x_scales, const float* row_weights, const int32_t* seg_offsets,
+                              const int32_t* seg_slot, int n_segments, long long rows, float swiglu_limit, void* workspace,
+                              size_t workspace_bytes, void* y_bf16, int* status, cachalot_stream_t stream);
+CACHALOT_API int cachalot_moe_combine_rows(const void* y_bf16, const int32_t* inv, int tokens, int k, int hidden, float* out,
+                              cachalot_stream_t stream);
+
 /* ---- expert-parallel decode: sum of the ranks' partial outputs over peer memory ------------- */
 
 /* No counterpart in the reference (it is single-device).  Every rank r owns, in memory that all

@@ -115,3 +115,68 @@ def test_prefill_tensor_core_path_matches_plain_kernels(tokens, hidden, inter, n
     assert int(status.item()) == 0
     err = (tc - plain).abs().amax(dim=1) / plain.abs().max()
     assert float((err < TOL).float().mean()) >= 0.9 and float(err.max()) < 5e-2
+
+
+def test_prefill_rows_and_combine_equal_the_whole_call():
+    """The two halves an expert-parallel rank runs (rows-level GEMMs, slot-ordered combine) reproduce
+    cachalot_moe_prefill bit for bit when fed the same grouping, also with an absent expert."""
+    import cachalot_b200 as cb
+    tokens, hidden, inter, n_exp, k = 200, 512, 320, 10, 6
+    x, ids, w, experts = configs.config3(seed=8, tokens=tokens, hidden=hidden, inter=inter, n_experts=n_exp, k=k,
+                                         materialise=range(n_exp))
+    bank = make_bank([experts[e] for e in range(n_exp)], cb.FP4_FORMAT, hidden, inter)
+    bank.slot_table[0, 2] = -1
+    xt, it, wt = bf16_tensor(x), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
+    whole = cb.moe_prefill_grouped(xt, it, wt, bank, mxfp4_act=1)
+    perm, offsets = cb.group_rows(it, n_exp)
+    codes, scales = cb.quantize_mxfp4(xt, perm // k)
+    row_w = wt.reshape(-1)[perm.long()]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = cb.moe_prefill_rows(codes, scales, row_w, offsets, bank.slot_table[0], bank, status=status)
+    inv = torch.empty(tokens * k, dtype=torch.int32, device="cuda")
+    inv[perm.long()] = torch.arange(tokens * k, dtype=torch.int32, device="cuda")
+    got = cb.combine_rows(y, inv, tokens, k)
+    assert int(status.item()) == 0
+    assert torch.equal(got, whole)
+    lo, hi = int(offsets[2]), int(offsets[3])
+    assert hi > lo and float(y[lo:hi].abs().max()) == 0.0
+
+
+def _ep_prefill_worker(rank, world, port, results):
+    import os
+
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import cachalot_b200 as cb
+    from cachalot_b200 import ep
+    tokens, hidden, inter, n_exp, k = 256, 512, 320, 10, 6
+    x, ids, w, experts = configs.config3(seed=9, tokens=tokens, hidden=hidden, inter=inter, n_experts=n_exp, k=k,
+                                         materialise=range(n_exp))
+    full = make_bank([experts[e] for e in range(n_exp)], cb.FP4_FORMAT, hidden, inter, device=dev)
+    lo, hi = ep.local_range(n_exp, rank, world)
+    shard = make_bank([experts[e] for e in range(lo, hi)], cb.FP4_FORMAT, hidden, inter, device=dev)
+    shard.slot_table = ep.local_slot_table(1, n_exp, rank, world).to(dev)
+    mine = slice(rank * tokens // world, (rank + 1) * tokens // world)
+    xt, it, wt = bf16_tensor(x[mine]).to(dev), torch.from_numpy(ids[mine]).to(dev), torch.from_numpy(w[mine]).to(dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    got = ep.ep_moe_prefill(xt, it, wt, shard, n_experts=n_exp, status=status)
+    want = cb.moe_prefill_grouped(xt, it, wt, full, mxfp4_act=1)
+    torch.cuda.synchronize(dev)
+    results[rank] = bool(torch.equal(got, want)) and int(status.item()) == 0
+    os._exit(0 if results[rank] else 1)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_prefill_on_two_gpus_equals_one_gpu():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    procs = [ctx.Process(target=_ep_prefill_worker, args=(r, 2, 29621, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+    assert all(p.exitcode == 0 for p in procs) and all(results.get(r) for r in range(2))
