@@ -460,29 +460,40 @@ def zipf_routing(rng, tokens, n_experts, k, s=1.1):
 
 def run_prefill(args):
     """One step = one chunk of `--tokens` prompt tokens through one MoE layer: expert-major grouping,
-    MXFP4 activation quantisation, the two grouped block-scaled FP4 GEMMs and the slot-ordered combine."""
+    MXFP4 activation quantisation, the two grouped block-scaled FP4 GEMMs and the slot-ordered combine.
+    N > 1: tokens and experts are both split over the ranks (expert parallel); rows travel to the owners of
+    their experts as MXFP4 codes + scales and come back as bf16 rows (two variable all-to-alls over NCCL)."""
     import numpy as np
     import torch
+    import torch.distributed as dist
 
     import cachalot_b200 as cb
+    from cachalot_b200 import ep
 
-    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
-        if int(os.environ.get("RANK", "0")) == 0:
-            print(json.dumps({"metric": "moe_prefill_tok_per_s", "unavailable": "the prefill workload is built for one GPU"}), flush=True)
-        return
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
     T, K, E = args.tokens, TOPK, args.experts
-    bank = cb.SlabBank(cb.FP4_FORMAT, HIDDEN, INTER, E, layers=1, n_experts=E, device=dev)
-    bank.fill_random(torch.Generator(device=dev).manual_seed(1234))
-    rng = np.random.default_rng(0)
+    lo, hi = ep.local_range(E, rank, world)
+    bank = cb.SlabBank(cb.FP4_FORMAT, HIDDEN, INTER, max(hi - lo, 1), layers=1, n_experts=E, device=dev)
+    if world > 1:
+        bank.slot_table = ep.local_slot_table(1, E, rank, world).to(dev)
+    bank.fill_random(torch.Generator(device=dev).manual_seed(1234 + rank))
+    rng = np.random.default_rng(0)                      # the same routing on every rank; a rank takes its slice of the tokens
     P = 4
-    g_in = torch.Generator().manual_seed(7)
-    x_host = torch.randn((P, T, HIDDEN), generator=g_in).to(torch.bfloat16).pin_memory()
+    t_lo, t_hi = rank * T // world, (rank + 1) * T // world
+    Tl = t_hi - t_lo
+    g_in = torch.Generator().manual_seed(7 + rank)
+    x_host = torch.randn((P, Tl, HIDDEN), generator=g_in).to(torch.bfloat16).pin_memory()
     routes = [zipf_routing(rng, T, E, K) for _ in range(P)]
-    ids_host = torch.stack([torch.from_numpy(r[0]) for r in routes]).pin_memory()
-    w_host = torch.stack([torch.from_numpy(r[1]) for r in routes]).pin_memory()
-    out_host = torch.empty((T, HIDDEN), dtype=torch.float32).pin_memory()
+    ids_host = torch.stack([torch.from_numpy(r[0][t_lo:t_hi]) for r in routes]).pin_memory()
+    w_host = torch.stack([torch.from_numpy(r[1][t_lo:t_hi]) for r in routes]).pin_memory()
+    out_host = torch.empty((Tl, HIDDEN), dtype=torch.float32).pin_memory()
     x_pool, ids_pool, w_pool = x_host.to(dev), ids_host.to(dev), w_host.to(dev)
     x, ids, w = x_pool[0].clone(), ids_pool[0].clone(), w_pool[0].clone()
     status = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -490,10 +501,18 @@ def run_prefill(args):
     result = [None]
 
     def step():
-        result[0] = cb.moe_prefill_grouped(x, ids, w, bank, swiglu_limit=SWIGLU_LIMIT, mxfp4_act=1, status=status)
+        if world > 1:
+            result[0] = ep.ep_moe_prefill(x, ids, w, bank, n_experts=E, swiglu_limit=SWIGLU_LIMIT, status=status)
+        else:
+            result[0] = cb.moe_prefill_grouped(x, ids, w, bank, swiglu_limit=SWIGLU_LIMIT, mxfp4_act=1, status=status)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
 
     def timed(steps, host):
-        torch.cuda.synchronize(dev)
+        barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(stream):
             e0.record(stream)
@@ -507,17 +526,29 @@ def run_prefill(args):
                     out_host.copy_(result[0], non_blocking=True)
                     stream.synchronize()
             e1.record(stream)
-        torch.cuda.synchronize(dev)
-        return e0.elapsed_time(e1)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
 
     timed(max(args.warmup, 3), False)
-    sampler = ClockSampler(0)
-    sampler.start()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     ms = timed(args.steps, False)
     ms_e2e = timed(args.steps, True)
-    clocks = sampler.stop()
-    if int(status.item()):
-        raise RuntimeError(f"device status {int(status.item())}")
+    clocks = sampler.stop() if rank == 0 else None
+    st = status.clone()
+    if world > 1:
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    if int(st.item()):
+        raise RuntimeError(f"device status {int(st.item())}")
+    if rank != 0:
+        _leave(world)
+        return
     touched = float(np.mean([len(set(r[0].reshape(-1).tolist())) for r in routes]))
     rows = T * K
     per_expert = 3 * (HIDDEN * INTER // 2 + HIDDEN * INTER // 32)
@@ -526,21 +557,27 @@ def run_prefill(args):
     us = ms * 1e3 / args.steps
     peak, which = measured_peak()
     flops = 6.0 * rows * INTER * HIDDEN
+    cfg = {"workload": f"prefill expert-major MoE layer: FP4 E2M1/E8M0 bank, {E} experts, {T} tokens, top-{K}, Zipf(1.1) expert "
+                       f"popularity, hidden {HIDDEN}, inter {INTER}, activations MXFP4 per 32",
+           "l2": f"inputs larger than L2: {E * 18.8e6 / 1e9:.1f} GB of expert weights are streamed per step",
+           "parallelism": f"ep{world}"}
+    if world > 1:
+        remote = rows * (world - 1) / world               # expected share of rows whose expert lives on another rank
+        cfg["exchange"] = {"dispatch_bytes": remote * (HIDDEN // 2 + HIDDEN // 32 + 4), "combine_bytes": remote * HIDDEN * 2,
+                           "collective": "NCCL all_to_all_single (variable splits), twice per step"}
     line = {
-        "metric": "moe_prefill_tok_per_s", "value": T / (us * 1e-6), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "fp4 (E2M1 x E2M1, E8M0 block scales, f32 accumulate)", "data": "synthetic",
-        "config": {"workload": f"prefill expert-major MoE layer: FP4 E2M1/E8M0 bank, {E} experts, {T} tokens, top-{K}, Zipf(1.1) expert "
-                               f"popularity, hidden {HIDDEN}, inter {INTER}, activations MXFP4 per 32",
-                   "l2": f"inputs larger than L2: {E * 18.8e6 / 1e9:.1f} GB of expert weights are streamed per step"},
-        "roofline": {"bound": "hbm", "achieved": alg / us / 1e3, "peak": peak, "unit": "GB/s", "frac": alg / us / 1e3 / peak,
-                     "traffic": None, "peak_source": which, "kernel": "whole call: grouping, quantiser, gate/up GEMM, down GEMM, combine",
-                     "tensor_tflops": flops / us / 1e6},
-        "e2e": {"value": T / (ms_e2e * 1e-3 / args.steps), "unit": "tok/s", "h2d_bytes_per_step": T * HIDDEN * 2 + rows * 8,
-                "d2h_bytes_per_step": T * HIDDEN * 4},
-        "gpu_launches": 10 * args.steps, "clocks": clocks,
+        "metric": "moe_prefill_tok_per_s", "value": T / (us * 1e-6), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp4 (E2M1 x E2M1, E8M0 block scales, f32 accumulate)", "data": "synthetic", "config": cfg,
+        "roofline": {"bound": "hbm", "achieved": alg / us / 1e3, "peak": peak * world, "unit": "GB/s", "frac": alg / us / 1e3 / (peak * world),
+                     "traffic": None, "peak_source": which, "kernel": "whole call: grouping, quantiser, gate/up GEMM, down GEMM, combine"
+                     + (", exchanges" if world > 1 else ""), "tensor_tflops": flops / us / 1e6},
+        "e2e": {"value": T / (ms_e2e * 1e-3 / args.steps), "unit": "tok/s", "h2d_bytes_per_step": Tl * HIDDEN * 2 + Tl * K * 8,
+                "d2h_bytes_per_step": Tl * HIDDEN * 4},
+        "gpu_launches": (10 if world == 1 else 9) * args.steps, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
+    _leave(world)
 
 
 def main():
