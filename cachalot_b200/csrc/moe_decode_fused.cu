@@ -680,7 +680,11 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
         if (numerics != CACHALOT_NUMERICS_F32) gv = bf16_round(gv), uv = bf16_round(uv);
         float h = swiglu(gv, uv, limit) * s_gw[p];
         if (numerics == CACHALOT_NUMERICS_BF16) h = bf16_round(h);
-        hidden[(size_t)s_route[p] * I + tile * 8 + (g >> 1) + 4 * (g & 1)] = h;
+        // bf16 numerics: h is a bf16 value already, so the hidden rows travel between the CTAs as bf16 (half the bytes
+        // every CTA reads back after the barrier)
+        const size_t hi_ = (size_t)s_route[p] * I + tile * 8 + (g >> 1) + 4 * (g & 1);
+        if (numerics == CACHALOT_NUMERICS_BF16) reinterpret_cast<__nv_bfloat16*>(hidden)[hi_] = __float2bfloat16_rn(h);
+        else hidden[hi_] = h;
       }
       CYC_ADD(cyc_b);
     }
@@ -701,7 +705,38 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
     // phase 1 operand: the hidden rows of the present experts (operand row p = p-th present expert)
     const int row_stride1 = G.act_stride[1];
     const int nsub1 = I / SUB;
-    {
+    if (numerics == CACHALOT_NUMERICS_BF16) {
+      constexpr int SB = 5;  // blocks per thread and round (one round at 6 experts x 2880); all loads first
+      const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(hidden);
+      const int nblk = I / 16, total = np * nblk;
+      for (int base = 0; base < total; base += SB * NCT) {
+        uint4 q[SB][2];
+        int rr[SB], bbk[SB];
+        bool ok[SB];
+#pragma unroll
+        for (int h = 0; h < SB; ++h) {
+          const int idx = base + h * NCT + tid;
+          ok[h] = idx < total;
+          rr[h] = ok[h] ? idx / nblk : 0;
+          bbk[h] = ok[h] ? idx - rr[h] * nblk : 0;
+          q[h][0] = q[h][1] = make_uint4(0, 0, 0, 0);
+          if (ok[h]) {
+            const uint4* src = reinterpret_cast<const uint4*>(hb + (size_t)s_route[rr[h]] * I + bbk[h] * 16);
+            q[h][0] = __ldcg(src), q[h][1] = __ldcg(src + 1);  // written by other CTAs in this launch: read from L2
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < SB; ++h) {
+          if (base + h * NCT < total) {  // warp-uniform
+            const uint32_t wds[8] = {q[h][0].x, q[h][0].y, q[h][0].z, q[h][0].w, q[h][1].x, q[h][1].y, q[h][1].z, q[h][1].w};
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[2 * i] = __uint_as_float(wds[i] << 16), v[2 * i + 1] = __uint_as_float(wds[i] & 0xffff0000u);
+            convert_block<FMT>(act + (size_t)rr[h] * row_stride1, pexs + rr[h] * nsub1, bbk[h], ok[h], v);
+          }
+        }
+      }
+    } else {
       constexpr int SB = 4;  // blocks per thread and round; all their loads are issued before any is used
       const int nblk = I / 16, total = np * nblk;
       for (int base = 0; base < total; base += SB * NCT) {
