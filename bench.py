@@ -166,10 +166,55 @@ def time_cpu(bank_kind: str, steps: int, warmup: int, threads: int):
     return dt, 1.0 / (dt * LAYERS)
 
 
+def time_cpu_prefill(args):
+    """The numpy oracle of the reference's prefill arithmetic on a bounded sample (a few tokens of the chunk:
+    every routed row costs one expert dequantisation on the host).  Returns (tok/s, seconds, description)."""
+    import numpy as np
+    from oracle import configs, prefill
+
+    sample, E = 4, args.experts
+    rng = np.random.default_rng(0)
+    ids, w = zipf_routing(rng, args.tokens, E, TOPK)
+    ids, w = ids[:sample], w[:sample]
+    x = configs.round_bf16(rng.standard_normal((sample, HIDDEN)).astype(np.float32))
+    cache = {}
+
+    def bank(e):
+        if e not in cache:
+            cache[e] = configs.fp4_expert(np.random.default_rng([0, int(e)]), HIDDEN, INTER)
+        return cache[e]
+
+    for e in set(ids.reshape(-1).tolist()):
+        bank(e)                                   # weight generation is not part of the timed work
+    t0 = time.perf_counter()
+    prefill.moe_prefill_fp4(x, ids, w, bank, n_experts=E, swiglu_limit=SWIGLU_LIMIT, act="mxfp4")
+    dt = time.perf_counter() - t0
+    desc = f"{sample} tokens ({sample * TOPK} routed rows, {len(cache)} experts dequantised from packed bytes) of the {args.tokens}-token chunk, numpy"
+    return sample / dt, dt / sample, desc
+
+
+def run_reference_prefill(args):
+    """CPU arm of the prefill workload."""
+    E = args.experts
+    tok_s, s_per_tok, desc = time_cpu_prefill(args)
+    line = {
+        "impl": "reference", "metric": "moe_prefill_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus, "steps": 1,
+        "warmup": 0, "ms_per_step": s_per_tok * args.tokens * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"prefill expert-major MoE layer: FP4 E2M1/E8M0 bank, {E} experts, {args.tokens} tokens, top-{TOPK}, "
+                               f"Zipf(1.1) expert popularity, hidden {HIDDEN}, inter {INTER}, activations MXFP4 per 32"},
+        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port", "sample": desc},
+        "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if args.workload == "prefill":
+        return run_reference_prefill(args)
     threads = min(TOPK, os.cpu_count() or 1)
     steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 1))
     dt, tok_s = time_cpu(args.bank, steps, warmup, threads)
@@ -576,6 +621,9 @@ def run_prefill(args):
                 "d2h_bytes_per_step": Tl * HIDDEN * 4},
         "gpu_launches": (10 if world == 1 else 9) * args.steps, "clocks": clocks,
     }
+    if world == 1 and not args.no_cpu_baseline:
+        cpu_tok_s, _, desc = time_cpu_prefill(args)
+        line["cpu_baseline"] = {"value": cpu_tok_s, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port", "sample": desc}
     print(json.dumps(line), flush=True)
     _leave(world)
 
