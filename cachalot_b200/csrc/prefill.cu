@@ -4,72 +4,94 @@
 
 namespace cachalot {
 
-__global__ void group_count_kernel(const int32_t* __restrict__ ids, int total, int n_experts,
-                                   int32_t* __restrict__ counts, int* __restrict__ status) {
-  int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total) return;
-  int e = ids[i];
-  if (e < 0 || e >= n_experts) {
-    if (status) atomicOr(status, CACHALOT_STATUS_ID_RANGE);
-    return;
+constexpr int GROUP_CHUNK = 1024;  // ids per CTA of the counting sort
+
+// CTA b counts the experts of ids [b*1024, (b+1)*1024): block_counts[b][e]
+__global__ void __launch_bounds__(GROUP_CHUNK)
+group_count_kernel(const int32_t* __restrict__ ids, int total, int n_experts, int32_t* __restrict__ block_counts,
+                   int* __restrict__ status) {
+  extern __shared__ int32_t hist[];
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int i = blockIdx.x * GROUP_CHUNK + threadIdx.x;
+  if (i < total) {
+    const int e = ids[i];
+    if (e < 0 || e >= n_experts) {
+      if (status) atomicOr(status, CACHALOT_STATUS_ID_RANGE);
+    } else {
+      atomicAdd(&hist[e], 1);
+    }
   }
-  atomicAdd(&counts[e], 1);
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) block_counts[(size_t)blockIdx.x * n_experts + e] = hist[e];
 }
 
-// single CTA: exclusive scan of counts[0..E) into offsets[0..E]
-__global__ void group_scan_kernel(const int32_t* __restrict__ counts, int n_experts, int32_t* __restrict__ offsets) {
-  extern __shared__ int32_t sh[];
+// single CTA: offsets[e] = rows of experts < e; block_counts[b][e] becomes the first position of CTA b's rows of
+// expert e (experts ascending, CTAs ascending inside an expert: the order a stable sort gives)
+__global__ void group_scan_kernel(int32_t* __restrict__ block_counts, int n_blocks, int n_experts, int32_t* __restrict__ offsets) {
+  extern __shared__ int32_t sh[];  // [n_experts] totals, then [blockDim.x] partial sums
+  int32_t* tot = sh;
+  int32_t* part = sh + n_experts;
   const int t = threadIdx.x, n = blockDim.x;
-  // each thread owns a contiguous span
+  for (int e = t; e < n_experts; e += n) {
+    int run = 0;
+    for (int b = 0; b < n_blocks; ++b) {
+      const int v = block_counts[(size_t)b * n_experts + e];
+      block_counts[(size_t)b * n_experts + e] = run;
+      run += v;
+    }
+    tot[e] = run;
+  }
+  __syncthreads();
   const int per = (n_experts + n - 1) / n;
   const int lo = min(t * per, n_experts), hi = min(lo + per, n_experts);
   int sum = 0;
-  for (int e = lo; e < hi; ++e) sum += counts[e];
-  sh[t] = sum;
+  for (int e = lo; e < hi; ++e) sum += tot[e];
+  part[t] = sum;
   __syncthreads();
   if (t == 0) {
     int run = 0;
     for (int i = 0; i < n; ++i) {
-      int v = sh[i];
-      sh[i] = run;
+      const int v = part[i];
+      part[i] = run;
       run += v;
     }
     offsets[n_experts] = run;
   }
   __syncthreads();
-  int run = sh[t];
+  int run = part[t];
   for (int e = lo; e < hi; ++e) {
     offsets[e] = run;
-    run += counts[e];
+    const int base = run;
+    run += tot[e];
+    tot[e] = base;
   }
+  __syncthreads();
+  for (int e = t; e < n_experts; e += n)
+    for (int b = 0; b < n_blocks; ++b) block_counts[(size_t)b * n_experts + e] += tot[e];
 }
 
-// one CTA per expert: walk the flattened id list in order and append matches, so rows of an
-// expert keep token-major, slot-minor order (what a stable sort gives)
-__global__ void group_place_kernel(const int32_t* __restrict__ ids, int total, const int32_t* __restrict__ offsets,
-                                   int32_t* __restrict__ perm) {
-  __shared__ int warp_count[32];
-  __shared__ int base;
-  const int e = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  if (threadIdx.x == 0) base = offsets[e];
+// CTA b places its ids in order: warps one after the other, lanes ranked inside a warp by match + popcount
+__global__ void __launch_bounds__(GROUP_CHUNK)
+group_place_kernel(const int32_t* __restrict__ ids, int total, int n_experts, const int32_t* __restrict__ block_base,
+                   int32_t* __restrict__ perm) {
+  extern __shared__ int32_t next[];  // next free position of every expert for this CTA
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) next[e] = block_base[(size_t)blockIdx.x * n_experts + e];
   __syncthreads();
-  if (offsets[e + 1] == offsets[e]) return;
-  for (int start = 0; start < total; start += blockDim.x) {
-    int i = start + threadIdx.x;
-    bool hit = i < total && ids[i] == e;
-    unsigned m = __ballot_sync(0xffffffffu, hit);
-    if (lane == 0) warp_count[warp] = __popc(m);
-    __syncthreads();
-    int before = 0, all = 0;
-    for (int w = 0; w < nwarps; ++w) {
-      int c = warp_count[w];
-      if (w < warp) before += c;
-      all += c;
+  const int i = blockIdx.x * GROUP_CHUNK + threadIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int e = i < total ? ids[i] : -1;
+  if (e >= n_experts) e = -1;
+  for (int w = 0; w < GROUP_CHUNK / 32; ++w) {
+    if (warp == w) {
+      const unsigned same = __match_any_sync(0xffffffffu, e);
+      if (e >= 0) {
+        const int rank = __popc(same & ((1u << lane) - 1u));
+        perm[next[e] + rank] = i;
+      }
+      __syncwarp();
+      if (e >= 0 && (same & ((1u << lane) - 1u)) == 0) next[e] += __popc(same);  // the group's first lane moves the cursor on
     }
-    if (hit) perm[base + before + __popc(m & ((1u << lane) - 1u))] = i;
-    __syncthreads();
-    if (threadIdx.x == 0) base += all;
     __syncthreads();
   }
 }
@@ -141,6 +163,12 @@ int launch_mxfp4_roundtrip_bf16(const __nv_bfloat16* in, __nv_bfloat16* out, lon
 
 using namespace cachalot;
 
+extern "C" size_t cachalot_group_rows_scratch_ints(int tokens, int k, int n_experts) {
+  if (tokens < 0 || k <= 0 || n_experts <= 0) return 0;
+  const long long total = (long long)tokens * k;
+  return (size_t)((total + GROUP_CHUNK - 1) / GROUP_CHUNK + 1) * (size_t)n_experts;
+}
+
 extern "C" int cachalot_group_rows(const int32_t* expert_ids, int tokens, int k, int n_experts, int32_t* perm,
                                    int32_t* offsets, int32_t* counts_scratch, int* status,
                                    cachalot_stream_t stream) {
@@ -150,11 +178,13 @@ extern "C" int cachalot_group_rows(const int32_t* expert_ids, int tokens, int k,
   if (total_ll > 0x7fffffff) return fail(CACHALOT_EINVAL, "group_rows: tokens*k too large");
   int total = (int)total_ll;
   cudaStream_t s = (cudaStream_t)stream;
-  cudaError_t e = cudaMemsetAsync(counts_scratch, 0, (size_t)(n_experts + 1) * sizeof(int32_t), s);
-  if (e != cudaSuccess) return fail(CACHALOT_ECUDA, "group_rows: memset: %s", cudaGetErrorString(e));
-  if (total > 0) group_count_kernel<<<(total + 255) / 256, 256, 0, s>>>(expert_ids, total, n_experts, counts_scratch, status);
-  group_scan_kernel<<<1, 256, 256 * sizeof(int32_t), s>>>(counts_scratch, n_experts, offsets);
-  if (total > 0) group_place_kernel<<<n_experts, 256, 0, s>>>(expert_ids, total, offsets, perm);
+  if (n_experts > 8192) return fail(CACHALOT_EUNSUPPORTED, "group_rows: more than 8192 experts");
+  const int n_blocks = (total + GROUP_CHUNK - 1) / GROUP_CHUNK;
+  if (n_blocks > 0)
+    group_count_kernel<<<n_blocks, GROUP_CHUNK, n_experts * sizeof(int32_t), s>>>(expert_ids, total, n_experts, counts_scratch, status);
+  group_scan_kernel<<<1, 256, (n_experts + 256) * sizeof(int32_t), s>>>(counts_scratch, n_blocks, n_experts, offsets);
+  if (n_blocks > 0)
+    group_place_kernel<<<n_blocks, GROUP_CHUNK, n_experts * sizeof(int32_t), s>>>(expert_ids, total, n_experts, counts_scratch, perm);
   return check_launch("group_rows");
 }
 

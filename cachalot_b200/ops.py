@@ -387,7 +387,7 @@ def group_rows(expert_ids: torch.Tensor, n_experts: int, status: torch.Tensor | 
     ids = expert_ids.to(torch.int32).contiguous()
     perm = torch.empty(t * k, dtype=torch.int32, device=ids.device)
     offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=ids.device)
-    scratch = torch.empty(n_experts + 1, dtype=torch.int32, device=ids.device)
+    scratch = torch.empty(max(int(lib.cachalot_group_rows_scratch_ints(t, k, n_experts)), 1), dtype=torch.int32, device=ids.device)
     if t * k == 0:
         return perm, offsets.zero_()
     check(lib.cachalot_group_rows(_ptr(ids), t, k, n_experts, _ptr(perm), _ptr(offsets), _ptr(scratch), _ptr(status), _stream()))

@@ -209,7 +209,9 @@ CACHALOT_API int cachalot_fp8_gemv(const uint8_t* codes, const float* act_scales
  * glm/experts.py:301-303): a stable sort of the flattened [tokens*k] expert ids.
  * perm i32 [tokens*k] = flattened (token*k + route slot) ids in expert-major order, offsets
  * i32 [E+1]; ids outside [0,E) are dropped from perm (offsets[E] < tokens*k) and flagged.
- * counts_scratch: i32 [E+1] device scratch. */
+ * A stable counting sort: 1024 ids per CTA, per-CTA histograms, one scan, in-order placement.
+ * counts_scratch: i32 [cachalot_group_rows_scratch_ints(tokens, k, E)] device scratch. */
+CACHALOT_API size_t cachalot_group_rows_scratch_ints(int tokens, int k, int n_experts);
 CACHALOT_API int cachalot_group_rows(const int32_t* expert_ids, int tokens, int k, int n_experts, int32_t* perm,
                         int32_t* offsets, int32_t* counts_scratch, int* status, cachalot_stream_t stream);
 

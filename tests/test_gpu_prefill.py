@@ -180,3 +180,23 @@ def test_expert_parallel_prefill_on_two_gpus_equals_one_gpu():
     for p in procs:
         p.join(180)
     assert all(p.exitcode == 0 for p in procs) and all(results.get(r) for r in range(2))
+
+
+def test_prefill_tensor_core_path_at_full_layer_dims():
+    """hidden 4096, inter 2880 (partial last 128-row tile, K tail of the down projection, scale rows of 90 bytes):
+    block-scaled MMAs against the per-row kernels on the same grouping; one expert has more rows than a unit holds."""
+    import cachalot_b200 as cb
+    tokens, hidden, inter, n_exp, k = 160, 4096, 2880, 8, 6
+    rng = np.random.default_rng(11)
+    bank = cb.SlabBank(cb.FP4_FORMAT, hidden, inter, n_exp)
+    bank.fill_random(torch.Generator(device="cuda").manual_seed(3))
+    x = bf16_tensor(round_bf16(rng.standard_normal((tokens, hidden)).astype(np.float32)))
+    ids = np.stack([rng.permutation(n_exp)[:k] for _ in range(tokens)]).astype(np.int32)   # ~120 rows per expert
+    w = rng.uniform(0.05, 0.3, (tokens, k)).astype(np.float32)
+    it, wt = torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tc = cb.moe_prefill_grouped(x, it, wt, bank, mxfp4_act=1, status=status)
+    plain = cb.moe_prefill_grouped(x, it, wt, bank, mxfp4_act=2)
+    assert int(status.item()) == 0
+    err = (tc - plain).abs().amax(dim=1) / plain.abs().max()
+    assert float((err < TOL).float().mean()) >= 0.9 and float(err.max()) < 5e-2
