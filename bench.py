@@ -409,7 +409,8 @@ def run_ours(args):
         for l in range(LAYERS):
             s = slots_all[l].reshape(-1)
             distinct += int(torch.unique(s[s >= 0]).numel())
-    fused = B == 1          # one token: gate/up, SwiGLU and down run as ONE launch per layer
+    PER_TOKEN_MAX = 64      # up to this many tokens the library runs the single-launch kernel once per token
+    fused = B <= PER_TOKEN_MAX   # gate/up, SwiGLU and down run as ONE launch per (layer, token)
     reps = max(3, args.steps // 2)
     if fused:
         run_layers = make_runner(lambda: phase_step(None))
@@ -440,7 +441,7 @@ def run_ours(args):
     tok_s_e2e = B * args.steps / (ms_e2e * 1e-3)
     layer_bytes = u_per_layer * (up_bytes + dn_bytes) + B * HIDDEN * 2 + B * HIDDEN * 4
     hbm_gbs_token = layer_bytes * LAYERS * args.steps / (ms * 1e-3) / 1e9
-    if fused:
+    if fused and B == 1:
         # the timed region is LAYERS launches of this kernel per step (plus two small copies per token)
         us_launch = ms * 1e3 / (args.steps * LAYERS)
         gbs = layer_bytes / (us_launch * 1e-6) / 1e9
@@ -450,6 +451,15 @@ def run_ours(args):
                     "traffic": NCU_TRAFFIC_BYTES.get((args.bank, B, "fused")),
                     "us_per_launch_routing_done_beforehand": ms_layer * 1e3}
         launches = LAYERS * args.steps              # routing tail + experts = one launch per layer
+    elif fused:
+        # a few tokens: per layer one routing launch and B launches of the single-token kernel (k experts each)
+        launch_bytes = K * (up_bytes + dn_bytes) / max(world, 1) + HIDDEN * 2 + HIDDEN * 4
+        us_launch = ms_layer * 1e3 / B
+        gbs = launch_bytes / (us_launch * 1e-6) / 1e9
+        roofline = {"kernel": "fused_decode_kernel, one launch per (layer, token) with the routing done beforehand",
+                    "bound": "hbm", "achieved": gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": gbs / peak,
+                    "us_per_launch": us_launch, "algorithmic_bytes_per_launch": launch_bytes, "traffic": None}
+        launches = (1 + B) * LAYERS * args.steps
     else:
         gu_gbs = gu_alg / (ms_gu * 1e-3) / 1e9
         dn_gbs = dn_alg / (ms_dn * 1e-3) / 1e9

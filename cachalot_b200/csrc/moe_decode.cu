@@ -262,6 +262,11 @@ static int launch_decode(const BankView& v, const void* x, const int32_t* slots,
 
 using namespace cachalot;
 
+#ifndef CB_FUSED_PER_TOKEN_MAX_ROWS
+#define CB_FUSED_PER_TOKEN_MAX_ROWS 64
+#endif
+static constexpr int FUSED_PER_TOKEN_MAX_ROWS = CB_FUSED_PER_TOKEN_MAX_ROWS;
+
 extern "C" size_t cachalot_moe_decode_workspace_bytes(const cachalot_bank_desc* desc, int rows, int k) {
   if (!desc || rows <= 0 || k <= 0) return 0;
   const size_t a = decode_mma_workspace_bytes(desc->hidden, desc->inter, rows, k);  // >= the simple kernels' rows*k*inter floats
@@ -286,9 +291,23 @@ extern "C" int cachalot_moe_decode(const void* bank, const cachalot_bank_desc* d
   size_t need = cachalot_moe_decode_workspace_bytes(desc, rows, k);
   if (!workspace || workspace_bytes < need) return fail(CACHALOT_ESCRATCH, "moe_decode: workspace %zu < %zu bytes", workspace_bytes, need);
   if (!aligned(workspace, 256) || !aligned(x_bf16, 16) || !aligned(out, 4)) return fail(CACHALOT_EALIGN, "moe_decode: workspace needs 256-byte, x 16-byte alignment");
-  if (!(numerics & (CACHALOT_DECODE_SIMPLE | CACHALOT_DECODE_UNFUSED | CACHALOT_DECODE_ONLY_GATE_UP | CACHALOT_DECODE_ONLY_DOWN)) &&
-      decode_fused_supported(v, rows, k))
+  const bool fused_ok = !(numerics & (CACHALOT_DECODE_SIMPLE | CACHALOT_DECODE_UNFUSED | CACHALOT_DECODE_ONLY_GATE_UP | CACHALOT_DECODE_ONLY_DOWN));
+  if (fused_ok && decode_fused_supported(v, rows, k))
     return launch_decode_fused(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, numerics, workspace, out, out_dtype, status, (cudaStream_t)stream);
+  // Up to 64 tokens: one single-launch kernel per token, back to back.  Tokens share few experts at these sizes (384
+  // routed rows touch about 244 of 384 experts), so grouping rows by expert saves less than the per-token kernel
+  // gains by streaming its experts about twice as fast as the grouped kernels (measured: FP4 bank, 8 tokens 0.34 ms
+  // per layer against 0.64 ms, 64 tokens 2.65 ms against 2.98 ms).
+  if (fused_ok && rows <= FUSED_PER_TOKEN_MAX_ROWS && decode_fused_supported(v, 1, k)) {
+    const size_t out_row = (size_t)v.hidden * (out_dtype == CACHALOT_BF16 ? 2 : 4);
+    for (int r = 0; r < rows; ++r) {
+      rc = launch_decode_fused(v, static_cast<const __nv_bfloat16*>(x_bf16) + (size_t)r * v.hidden, slots + (size_t)r * k,
+                               gate_w + (size_t)r * k, 1, k, swiglu_limit, numerics, workspace, static_cast<uint8_t*>(out) + r * out_row,
+                               out_dtype, status, (cudaStream_t)stream);
+      if (rc) return rc;
+    }
+    return CACHALOT_OK;
+  }
   if (!(numerics & CACHALOT_DECODE_SIMPLE) && decode_mma_supported(v, rows, k))
     return launch_decode_mma(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, numerics, workspace, out, out_dtype, status, (cudaStream_t)stream);
   if (desc->format == CACHALOT_BANK_FP4)

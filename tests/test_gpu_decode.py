@@ -147,7 +147,9 @@ def test_affine_small_shapes_batch(group, dims):
             u = round_bf16((x[t].astype(np.float64) @ dense(e, "w3", inter, hidden).T.astype(np.float64)).astype(np.float32))
             h = round_bf16((fp4.swiglu(g, u, 10.0) * w[t, j]).astype(np.float32))
             want[t] += round_bf16((h.astype(np.float64) @ dense(e, "w2", hidden, inter).T.astype(np.float64)).astype(np.float32))
-    assert max_rel(got, want) < TOL
+    # bf16 numerics: a value on a rounding boundary may land one bf16 step (2**-8 relative) away from the float64
+    # order of summation, so the bound is the one of the single-launch kernel tests, not the f32-numerics 2e-3
+    assert max_rel(got, want) < 2 ** -7
 
 
 def test_decode_full_size_properties():
@@ -181,11 +183,13 @@ def test_decode_full_size_properties():
     assert float((zero_w - dropped).abs().max()) <= 1e-5 * float(dropped.abs().max())
 
 
-@pytest.mark.parametrize("kind,rows", [("fp4", 1), ("fp4", 5), ("fp4", 16), ("affine", 1), ("affine", 7), ("affine", 64)])
+@pytest.mark.parametrize("kind,rows", [("fp4", 1), ("fp4", 5), ("fp4", 16), ("fp4", 80), ("affine", 1), ("affine", 7), ("affine", 64),
+                                       ("affine", 72)])
 def test_tensor_core_kernels_equal_simple_kernels(kind, rows):
     """The tensor-core decode kernels against the one-warp-per-output kernels on the same bank and
     routing, at the benchmark's shapes (the reference checks its fused kernels against the unfused
-    loop the same way); batches above one exercise the grouping of rows by expert."""
+    loop the same way); up to 64 tokens run the single-launch kernel once per token, larger batches
+    exercise the grouping of rows by expert."""
     import cachalot_b200 as cb
     g = torch.Generator(device="cuda").manual_seed(rows)
     hidden, inter, n_slots, k = 4096, 2880, 40, 6
@@ -203,8 +207,8 @@ def test_tensor_core_kernels_equal_simple_kernels(kind, rows):
     slow = cb.moe_forward(x, slots, w, bank, simple=True)
     assert int(status.item()) == 0
     scale = float(slow.abs().max())
-    # one token runs through the single-launch kernel (f16 hidden operand per 32-element block: a few 1e-4)
-    assert float((fast - slow).abs().max()) / scale < (2e-3 if kind == "affine" else (5e-4 if rows == 1 else 2e-5))
+    # the single-launch kernel keeps the hidden operand as f16 per 32-element block: a few 1e-4
+    assert float((fast - slow).abs().max()) / scale < (2e-3 if kind == "affine" else (5e-4 if rows <= 64 else 2e-5))
     again = cb.moe_forward(x, slots, w, bank)
     assert torch.equal(fast, again)
 
