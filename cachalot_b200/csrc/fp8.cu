@@ -62,24 +62,30 @@ __device__ __forceinline__ void qmma_e4m3(float (&d)[4], uint32_t a0, uint32_t a
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NTG, int BLOCK, int KS, typename OutT>
+// RT: 16-row tiles per warp.  With several token groups the activation fragments are the larger part of the loads;
+// two row tiles share them.
+template <int NTG, int BLOCK, int KS, int RT, typename OutT>
 __global__ void __launch_bounds__(KS * 32)
 fp8_gemv_mma_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ act_scales,
                     const uint8_t* __restrict__ weight, const void* __restrict__ w_scales, int scale_rule, int rows,
                     int n_out, int k, OutT* __restrict__ out) {
   constexpr int MPB = BLOCK / 32;  // MMAs per scale block
-  constexpr int UNR = BLOCK == 32 ? 8 : 2;  // scale blocks in flight: sixteen 8-byte weight loads per lane either way
-  __shared__ float red[KS][NTG][4][32];
+  constexpr int UNR = BLOCK == 32 ? 8 / RT : 2;  // scale blocks in flight: about sixteen 8-byte weight loads per lane
+  __shared__ float red[KS][RT][NTG][4][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * 16;
+  const int n0 = blockIdx.x * 16 * RT;
   const int nkb = k / BLOCK;
   // this warp's scale blocks
   const int kb_lo = nkb * warp / KS, kb_hi = nkb * (warp + 1) / KS;
   // rows past the end read the last row; their results are not stored
-  const int ra = min(n0 + g, n_out - 1), rb = min(n0 + g + 8, n_out - 1);
-  const uint8_t* wa = weight + (size_t)ra * k + t * 8;
-  const uint8_t* wb = weight + (size_t)rb * k + t * 8;
-  // weight scales: rows n0 .. n0+15 share a scale row when BLOCK is a multiple of 16 (it is: 32 or 128)
+  const uint8_t* wa[RT];
+  const uint8_t* wb[RT];
+#pragma unroll
+  for (int rt = 0; rt < RT; ++rt) {
+    wa[rt] = weight + (size_t)min(n0 + rt * 16 + g, n_out - 1) * k + t * 8;
+    wb[rt] = weight + (size_t)min(n0 + rt * 16 + g + 8, n_out - 1) * k + t * 8;
+  }
+  // weight scales: the CTA's 16*RT rows share a scale row (the block is 32 or 128 rows, n0 a multiple of 16*RT <= 32)
   const size_t srow = (size_t)(n0 / BLOCK) * nkb;
   // tokens of this lane: operand column g of group tg is token tg*8 + g; accumulator columns 2t, 2t+1
   const uint8_t* cb[NTG];
@@ -90,26 +96,35 @@ fp8_gemv_mma_kernel(const uint8_t* __restrict__ codes, const float* __restrict__
     tok_ok[tg] = tok < rows;
     cb[tg] = codes + (size_t)(tok_ok[tg] ? tok : 0) * k + t * 8;
   }
-  float acc[NTG][4];
+  float acc[RT][NTG][4];
 #pragma unroll
-  for (int tg = 0; tg < NTG; ++tg) acc[tg][0] = acc[tg][1] = acc[tg][2] = acc[tg][3] = 0.f;
+  for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+    for (int tg = 0; tg < NTG; ++tg) acc[rt][tg][0] = acc[rt][tg][1] = acc[rt][tg][2] = acc[rt][tg][3] = 0.f;
 
 #pragma unroll UNR
   for (int kb = kb_lo; kb < kb_hi; ++kb) {
-    float d[NTG][4];
+    float d[RT][NTG][4];
 #pragma unroll
-    for (int tg = 0; tg < NTG; ++tg) d[tg][0] = d[tg][1] = d[tg][2] = d[tg][3] = 0.f;
+    for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+      for (int tg = 0; tg < NTG; ++tg) d[rt][tg][0] = d[rt][tg][1] = d[rt][tg][2] = d[rt][tg][3] = 0.f;
 #pragma unroll
     for (int m = 0; m < MPB; ++m) {
       const int ko = kb * BLOCK + m * 32;
-      const uint2 va = ld_stream_u2(wa + ko), vb = ld_stream_u2(wb + ko);
-      const uint32_t a0 = e4m3x4_nan_to_zero(va.x), a2 = e4m3x4_nan_to_zero(va.y);
-      const uint32_t a1 = e4m3x4_nan_to_zero(vb.x), a3 = e4m3x4_nan_to_zero(vb.y);
+      uint32_t a[RT][4];
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) {
+        const uint2 va = ld_stream_u2(wa[rt] + ko), vb = ld_stream_u2(wb[rt] + ko);
+        a[rt][0] = e4m3x4_nan_to_zero(va.x), a[rt][2] = e4m3x4_nan_to_zero(va.y);
+        a[rt][1] = e4m3x4_nan_to_zero(vb.x), a[rt][3] = e4m3x4_nan_to_zero(vb.y);
+      }
 #pragma unroll
       for (int tg = 0; tg < NTG; ++tg) {
         uint2 b = make_uint2(0u, 0u);
         if (tok_ok[tg]) b = __ldg(reinterpret_cast<const uint2*>(cb[tg] + ko));
-        qmma_e4m3(d[tg], a0, a1, a2, a3, b.x, b.y);
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt) qmma_e4m3(d[rt][tg], a[rt][0], a[rt][1], a[rt][2], a[rt][3], b.x, b.y);
       }
     }
     const float ws = scale_rule == CACHALOT_SCALE_E8M0 ? e8m0_to_f32(reinterpret_cast<const uint8_t*>(w_scales)[srow + kb])
@@ -119,59 +134,65 @@ fp8_gemv_mma_kernel(const uint8_t* __restrict__ codes, const float* __restrict__
       const int t0 = tg * 8 + 2 * t;
       const float s0 = (t0 < rows ? act_scales[(size_t)t0 * nkb + kb] : 0.f) * ws;
       const float s1 = (t0 + 1 < rows ? act_scales[(size_t)(t0 + 1) * nkb + kb] : 0.f) * ws;
-      acc[tg][0] = fmaf(d[tg][0], s0, acc[tg][0]);
-      acc[tg][1] = fmaf(d[tg][1], s1, acc[tg][1]);
-      acc[tg][2] = fmaf(d[tg][2], s0, acc[tg][2]);
-      acc[tg][3] = fmaf(d[tg][3], s1, acc[tg][3]);
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) {
+        acc[rt][tg][0] = fmaf(d[rt][tg][0], s0, acc[rt][tg][0]);
+        acc[rt][tg][1] = fmaf(d[rt][tg][1], s1, acc[rt][tg][1]);
+        acc[rt][tg][2] = fmaf(d[rt][tg][2], s0, acc[rt][tg][2]);
+        acc[rt][tg][3] = fmaf(d[rt][tg][3], s1, acc[rt][tg][3]);
+      }
     }
   }
-  // add the K quarters (fixed order) and store
+  // add the K slices (fixed order) and store
 #pragma unroll
-  for (int tg = 0; tg < NTG; ++tg)
+  for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) red[warp][tg][i][lane] = acc[tg][i];
+    for (int tg = 0; tg < NTG; ++tg)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) red[warp][rt][tg][i][lane] = acc[rt][tg][i];
   __syncthreads();
-  if (warp == 0) {
+  // warp w adds and stores the (row tile, token group) pairs w, w + KS, ...
+  for (int pair = warp; pair < RT * NTG; pair += KS) {
+    const int rt = pair / NTG, tg = pair - rt * NTG;
 #pragma unroll
-    for (int tg = 0; tg < NTG; ++tg) {
+    for (int i = 0; i < 4; ++i) {
+      float v = red[0][rt][tg][i][lane];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float v = red[0][tg][i][lane];
-#pragma unroll
-        for (int w = 1; w < KS; ++w) v += red[w][tg][i][lane];
-        const int tok = tg * 8 + 2 * t + (i & 1), row = n0 + g + (i >> 1) * 8;
-        if (tok < rows && row < n_out) {
-          if constexpr (sizeof(OutT) == 2)
-            out[(size_t)tok * n_out + row] = __float2bfloat16_rn(v);
-          else
-            out[(size_t)tok * n_out + row] = v;
-        }
+      for (int w = 1; w < KS; ++w) v += red[w][rt][tg][i][lane];
+      const int tok = tg * 8 + 2 * t + (i & 1), row = n0 + rt * 16 + g + (i >> 1) * 8;
+      if (tok < rows && row < n_out) {
+        if constexpr (sizeof(OutT) == 2)
+          out[(size_t)tok * n_out + row] = __float2bfloat16_rn(v);
+        else
+          out[(size_t)tok * n_out + row] = v;
       }
     }
   }
 }
 
 template <int BLOCK, typename OutT>
-static void launch_gemv_mma(int ntg, dim3 grid, cudaStream_t s, const uint8_t* codes, const float* act_scales, const uint8_t* weight,
+static void launch_gemv_mma(int ntg, cudaStream_t s, const uint8_t* codes, const float* act_scales, const uint8_t* weight,
                             const void* w_scales, int scale_rule, int rows, int n, int k, OutT* out) {
   // warps per CTA: about twelve warps per SM in total (the reduction buffer limits it for many tokens)
   int sms = 148, dev = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const long long tiles = grid.x;
+  const int rt = ntg >= 3 && ntg <= 4 ? 2 : 1;   // 32-row CTAs once the activation fragments outweigh the weight loads (registers allow it up to 32 tokens)
+  const long long tiles = (n + 16 * rt - 1) / (16 * rt);
+  const dim3 grid((unsigned)tiles);
   int ks = 4;
   if (tiles * 4 < 12LL * sms && ntg <= 4) ks = 8;
   if (tiles * 8 < 12LL * sms && ntg <= 2) ks = 16;
-#define CACHALOT_GEMV(NTGV, KSV) \
-  fp8_gemv_mma_kernel<NTGV, BLOCK, KSV, OutT><<<grid, KSV * 32, 0, s>>>(codes, act_scales, weight, w_scales, scale_rule, rows, n, k, out)
+#define CACHALOT_GEMV(NTGV, KSV, RTV) \
+  fp8_gemv_mma_kernel<NTGV, BLOCK, KSV, RTV, OutT><<<grid, KSV * 32, 0, s>>>(codes, act_scales, weight, w_scales, scale_rule, rows, n, k, out)
   if (ntg == 1) {
-    if (ks == 16) CACHALOT_GEMV(1, 16); else if (ks == 8) CACHALOT_GEMV(1, 8); else CACHALOT_GEMV(1, 4);
+    if (ks == 16) CACHALOT_GEMV(1, 16, 1); else if (ks == 8) CACHALOT_GEMV(1, 8, 1); else CACHALOT_GEMV(1, 4, 1);
   } else if (ntg == 2) {
-    if (ks == 16) CACHALOT_GEMV(2, 16); else if (ks == 8) CACHALOT_GEMV(2, 8); else CACHALOT_GEMV(2, 4);
+    if (ks == 16) CACHALOT_GEMV(2, 16, 1); else if (ks == 8) CACHALOT_GEMV(2, 8, 1); else CACHALOT_GEMV(2, 4, 1);
   } else if (ntg <= 4) {
-    if (ks == 8) CACHALOT_GEMV(4, 8); else CACHALOT_GEMV(4, 4);
+    if (ks == 8) CACHALOT_GEMV(4, 8, 2); else CACHALOT_GEMV(4, 4, 2);
   } else {
-    CACHALOT_GEMV(8, 4);
+    CACHALOT_GEMV(8, 4, 1);
   }
 #undef CACHALOT_GEMV
 }
@@ -208,7 +229,6 @@ extern "C" int cachalot_fp8_gemv(const uint8_t* codes, const float* act_scales, 
   if (!aligned(weight, 8) || !aligned(codes, 8) || k % 8) return fail(CACHALOT_EALIGN, "fp8_gemv: weight and codes need 8-byte alignment");
   if (rows == 0) return CACHALOT_OK;
   cudaStream_t s = (cudaStream_t)stream;
-  const dim3 grid((n + 15) / 16);
   // 64 tokens per launch; more tokens take more launches over the same weights
   for (int r0 = 0; r0 < rows; r0 += 8 * GEMV_MAX_TG) {
     const int nr = rows - r0 < 8 * GEMV_MAX_TG ? rows - r0 : 8 * GEMV_MAX_TG;
@@ -217,12 +237,12 @@ extern "C" int cachalot_fp8_gemv(const uint8_t* codes, const float* act_scales, 
     const float* as = act_scales + (size_t)r0 * (k / block);
     if (out_dtype == CACHALOT_BF16) {
       __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)r0 * n;
-      if (block == 32) launch_gemv_mma<32>(ntg, grid, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
-      else launch_gemv_mma<128>(ntg, grid, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
+      if (block == 32) launch_gemv_mma<32>(ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
+      else launch_gemv_mma<128>(ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
     } else {
       float* o = (float*)out + (size_t)r0 * n;
-      if (block == 32) launch_gemv_mma<32>(ntg, grid, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
-      else launch_gemv_mma<128>(ntg, grid, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
+      if (block == 32) launch_gemv_mma<32>(ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
+      else launch_gemv_mma<128>(ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
     }
   }
   return check_launch("fp8_gemv");
