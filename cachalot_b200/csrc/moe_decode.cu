@@ -403,8 +403,9 @@ extern "C" int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc* 
   BankView v;
   int rc = make_view(bank, desc, &v, "moe_prefill");
   if (rc) return rc;
-  if (!x_bf16 || !perm || !offsets || !gate_w || !out) return fail(CACHALOT_EINVAL, "moe_prefill: null pointer");
   if (tokens < 0 || k <= 0 || n_experts <= 0) return fail(CACHALOT_EINVAL, "moe_prefill: bad shape");
+  if (tokens == 0) return CACHALOT_OK;  // an empty chunk: nothing to read or write
+  if (!x_bf16 || !perm || !offsets || !gate_w || !out) return fail(CACHALOT_EINVAL, "moe_prefill: null pointer");
   if ((long long)tokens * k > 65535) return fail(CACHALOT_EINVAL, "moe_prefill: tokens*k=%lld exceeds 65535 (chunk the prompt)", (long long)tokens * k);
   if (tokens == 0) return CACHALOT_OK;
   size_t need = cachalot_moe_prefill_workspace_bytes(desc, tokens, k, mxfp4_act);

@@ -423,6 +423,8 @@ def moe_prefill_grouped(x: torch.Tensor, expert_ids: torch.Tensor, weights: torc
     slot_of_expert = bank.slot_table[layer].contiguous()
     xb = x.to(torch.bfloat16).contiguous()
     out = torch.empty((t, bank.hidden), dtype=torch.float32, device=x.device)
+    if t == 0:
+        return out
     need = lib.cachalot_moe_prefill_workspace_bytes(bank.desc_ptr, t, k, int(mxfp4_act))
     ws = _workspace(x.device, need + 256)
     base = (ws.data_ptr() + 255) // 256 * 256

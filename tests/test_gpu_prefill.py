@@ -200,3 +200,35 @@ def test_prefill_tensor_core_path_at_full_layer_dims():
     assert int(status.item()) == 0
     err = (tc - plain).abs().amax(dim=1) / plain.abs().max()
     assert float((err < TOL).float().mean()) >= 0.9 and float(err.max()) < 5e-2
+
+
+@pytest.mark.parametrize("case", ["one_token", "one_expert_many_rows", "all_absent", "k1", "empty"])
+def test_prefill_tensor_core_path_edges(case):
+    """Ragged and degenerate groupings through the block-scaled MMAs: a single token, every row on one expert
+    (several 96-row units of the same weights), no expert resident (zeros), top-1 routing, an empty chunk."""
+    import cachalot_b200 as cb
+    hidden, inter, n_exp = 256, 192, 6
+    rng = np.random.default_rng(31)
+    experts = [configs.fp4_expert(rng, hidden, inter) for _ in range(n_exp)]
+    bank = make_bank(experts, cb.FP4_FORMAT, hidden, inter)
+    tokens, k = {"one_token": (1, 3), "one_expert_many_rows": (250, 2), "all_absent": (9, 3), "k1": (40, 1), "empty": (0, 3)}[case]
+    x = round_bf16(rng.standard_normal((tokens, hidden)).astype(np.float32))
+    ids = np.stack([rng.permutation(n_exp)[:k] for _ in range(tokens)]).astype(np.int32) if tokens else np.zeros((0, k), np.int32)
+    if case == "one_expert_many_rows":
+        ids[:, 0] = 4
+        ids[:, 1] = np.where(ids[:, 1] == 4, 5, ids[:, 1])
+    if case == "all_absent":
+        bank.slot_table[0, :] = -1
+    w = rng.uniform(0.1, 0.5, (tokens, k)).astype(np.float32)
+    xt, it, wt = bf16_tensor(x), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tc = cb.moe_prefill_grouped(xt, it, wt, bank, mxfp4_act=1, status=status)
+    assert int(status.item()) == 0 and tuple(tc.shape) == (tokens, hidden)
+    if case == "empty":
+        return
+    plain = cb.moe_prefill_grouped(xt, it, wt, bank, mxfp4_act=2)
+    if case == "all_absent":
+        assert float(tc.abs().max()) == 0.0 and float(plain.abs().max()) == 0.0
+        return
+    err = (tc - plain).abs().amax(dim=1) / plain.abs().max()
+    assert float((err < TOL).float().mean()) >= 0.9 and float(err.max()) < 5e-2
