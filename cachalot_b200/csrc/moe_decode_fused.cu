@@ -172,20 +172,17 @@ __device__ __forceinline__ void fp4_word(uint32_t w, uint32_t (&h)[4]) {
 
 // One arrival per CTA; returns false when the other CTAs do not show up within the wait limit.
 __device__ __forceinline__ bool grid_barrier(unsigned* word, unsigned n_ctas, bool master) {
-  __threadfence();
+  // release: the CTA's writes (ordered before this thread by the CTA barrier) are visible to whoever acquires the
+  // word; no separate fence, which would also wait for the producers' copies in flight
   const unsigned inc = master ? 0x80000000u - (n_ctas - 1u) : 1u;
-  const unsigned old = atomicAdd(word, inc);
-  bool ok = false;
+  unsigned old;
+  asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(word), "r"(inc) : "memory");
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
     unsigned cur;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(cur) : "l"(word) : "memory");
-    if ((old ^ cur) & 0x80000000u) {
-      ok = true;
-      break;
-    }
+    if ((old ^ cur) & 0x80000000u) return true;
   }
-  __threadfence();
-  return ok;
+  return false;
 }
 
 // split of the phase-0 units and phase-1 tiles over the CTAs
