@@ -296,8 +296,8 @@ extern "C" int cachalot_moe_decode(const void* bank, const cachalot_bank_desc* d
     return launch_decode_fused(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, numerics, workspace, out, out_dtype, status, (cudaStream_t)stream);
   // Up to 64 tokens: one single-launch kernel per token, back to back.  Tokens share few experts at these sizes (384
   // routed rows touch about 244 of 384 experts), so grouping rows by expert saves less than the per-token kernel
-  // gains by streaming its experts about twice as fast as the grouped kernels (measured: FP4 bank, 8 tokens 0.34 ms
-  // per layer against 0.64 ms, 64 tokens 2.65 ms against 2.98 ms).
+  // gains by streaming its experts about twice as fast as the grouped kernels (measured: FP4 bank, 8 tokens 0.29 ms
+  // per layer against 0.64 ms, 64 tokens 2.24 ms against 2.98 ms).
   if (fused_ok && rows <= FUSED_PER_TOKEN_MAX_ROWS && decode_fused_supported(v, 1, k)) {
     const size_t out_row = (size_t)v.hidden * (out_dtype == CACHALOT_BF16 ? 2 : 4);
     for (int r = 0; r < rows; ++r) {
