@@ -220,9 +220,9 @@ __device__ __forceinline__ void unpack16_bf16(const uint4 a, const uint4 b, floa
 // Converts one 16-element block of an activation row into operand form and stores it.  Operand
 // rows are laid out per step so that the eight lanes that load real data in one LDS.128 read 128
 // (FP4: 64) contiguous bytes:
-//   2-bit : step c = 512 B = [q 0..3][t 0..3][hi | lo][16 B]; the 16 values of (sub-block 4c+t,
+//   2-bit : step c = 512 B = [w 0..3][t 0..3][hi | lo][q 0..3][4 B]; the 16 values of (sub-block 4c+t,
 //           16-block q) are s8 in the 4x4-transposed order [0,4,8,12 | 1,5,9,13 | 2,6,10,14 | 3,7,11,15]
-//           (byte i of word c is code 4i+c of a weight word)
+//           (byte i of word w is code 4i+w of a weight word), and word w of the four blocks sits side by side
 //   FP4   : step c = 256 B = [q 0..3][t 0..3][16 B]; (sub-block 4c+t, chunk q) holds 8 f16 in natural order
 // and, for the first block of a sub-block, pexs = (2**-e [/64 for the 2-bit class sum], sum of x).
 // The lanes that share a sub-block (4 for 2-bit, 2 for FP4) are adjacent and call this together.
@@ -270,10 +270,15 @@ __device__ __forceinline__ void convert_block(uint8_t* act_row, float2* pexs_row
       ph[c] = __byte_perm(__byte_perm(hi[c], hi[c + 4], 0x0040), __byte_perm(hi[c + 8], hi[c + 12], 0x0040), 0x5410);
       pl[c] = __byte_perm(__byte_perm(lo[c], lo[c + 4], 0x0040), __byte_perm(lo[c + 8], lo[c + 12], 0x0040), 0x5410);
     }
+    // word c of block q goes to [c][sub-block][hi|lo][q]: a lane of the MMA loop reads its sub-block's 16 bytes of
+    // every c with one load and finds the words of blocks 0..3 side by side (two MMA operand register pairs)
     const int sub = b >> 2, q = b & 3;
-    uint8_t* dst = act_row + (sub >> 2) * 512 + q * 128 + (sub & 3) * 32;
-    *reinterpret_cast<uint4*>(dst) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-    *reinterpret_cast<uint4*>(dst + 16) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+    uint8_t* dst = act_row + (sub >> 2) * 512 + (sub & 3) * 32 + q * 4;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      *reinterpret_cast<uint32_t*>(dst + c * 128) = ph[c];
+      *reinterpret_cast<uint32_t*>(dst + c * 128 + 16) = pl[c];
+    }
     // the class sum of the IMMA accumulators carries a factor 64
     if (q == 0) pexs_row[sub] = make_float2(__uint_as_float((uint32_t)(127 - e - 6) << 23), sum);
   }
@@ -315,8 +320,9 @@ __device__ __forceinline__ void step_affine(float& accA, float& accB, const uint
 #pragma unroll
   for (int cl = 0; cl < 4; ++cl) {
     const uint32_t M = 0x03030303u << (2 * cl);
-    imma_u8s8_z(T[cl], wa[0] & M, wb[0] & M, wa[1] & M, wb[1] & M, bw[0][cl], bw[1][cl]);
-    imma_u8s8(T[cl], wa[2] & M, wb[2] & M, wa[3] & M, wb[3] & M, bw[2][cl], bw[3][cl]);
+    // b[cl] = word cl of the lane's four 16-element blocks: each MMA's two operand registers come out of one load
+    imma_u8s8_z(T[cl], wa[0] & M, wb[0] & M, wa[1] & M, wb[1] & M, bw[cl][0], bw[cl][1]);
+    imma_u8s8(T[cl], wa[2] & M, wb[2] & M, wa[3] & M, wb[3] & M, bw[cl][2], bw[cl][3]);
   }
   // 64 * (T0 + T1/4 + T2/16 + T3/64) per accumulator element, then 256*hi + lo
   int R[4];
