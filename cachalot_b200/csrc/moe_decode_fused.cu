@@ -66,6 +66,7 @@ struct Fm {
 
 #ifdef CB_FUSED_TRACE
 __device__ unsigned long long fused_trace[256][16];
+__device__ unsigned long long fused_trace2[256][40];
 __device__ __forceinline__ unsigned long long gtimer() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -587,26 +588,35 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
         const int tw = warp < 2 ? t_w1 : t_w3;
         const int n_arr = 2 * n_sc;  // arrays in stage order: W1's, then W3's
         int p = n0 > 0 ? u_begin / G.tiles0 : 0, tile = n0 > 0 ? u_begin - p * G.tiles0 : 0;
+        // One thread issues every copy of its warp, so its scalar code is on the critical path of the stream:
+        // stage index and round are counted, nothing is divided inside the loops.
+        const uint8_t* rec = n0 > 0 ? bank.base + (size_t)s_slot[p] * bank.record_bytes : bank.base;
+        const long long off_w = bank.off[tw] + (long long)(warp & 1) * 4 * rb;
+        long long off_s = -1;
+        if (warp < n_arr) {
+          const int m = warp / n_sc, a = warp - m * n_sc;
+          off_s = bank.off[(m == 0 ? t_w1 : t_w3) + 1 + a];
+        }
+        const uint32_t tx = (uint32_t)(4 * rb + (off_s >= 0 ? sb : 0));
+        const int dst_w = warp * (4 * rb + G.skew[0]), dst_s = G.sc_off[0] + warp * sb;
+        int idx = 0;
+        uint32_t round = 0;  // times the ring has wrapped
         for (int i = 0; i < n0 && !err; ++i) {
-          const int idx = i % nst0;
-          if (i >= nst0 && !mbar_wait(&empty0[idx], (uint32_t)((i / nst0) - 1) & 1u)) {
+          if (round > 0 && !mbar_wait(&empty0[idx], (round - 1u) & 1u)) {
             err = 1;  // the consumers stopped releasing stages: give up on the rest of the stream
             break;
           }
-          const uint8_t* rec = bank.base + (size_t)s_slot[p] * bank.record_bytes;
           uint8_t* dst = ring + (size_t)idx * G.stage_bytes[0];
           uint64_t* bar = &full0[idx];
           // stage: [W1 rows 0-3 | skew | W1 rows 4-7 | skew | W3 rows 0-3 | skew | W3 rows 4-7 | skew | scale arrays]
-          const uint8_t* src = rec + bank.off[tw] + (size_t)tile * 8 * rb + (size_t)(warp & 1) * 4 * rb;
-          const uint8_t* ssrc = nullptr;
-          if (warp < n_arr) {
-            const int m = warp / n_sc, a = warp - m * n_sc;
-            ssrc = rec + bank.off[(m == 0 ? t_w1 : t_w3) + 1 + a] + (size_t)tile * sb;
+          mbar_expect_tx(bar, tx);
+          bulk_g2s(dst + dst_w, rec + off_w + (size_t)tile * 8 * rb, (uint32_t)(4 * rb), bar);
+          if (off_s >= 0) bulk_g2s(dst + dst_s, rec + off_s + (size_t)tile * sb, (uint32_t)sb, bar);
+          if (++tile == G.tiles0) {
+            tile = 0, ++p;
+            if (i + 1 < n0) rec = bank.base + (size_t)s_slot[p] * bank.record_bytes;
           }
-          mbar_expect_tx(bar, (uint32_t)(4 * rb + (ssrc ? sb : 0)));
-          bulk_g2s(dst + warp * (4 * rb + G.skew[0]), src, (uint32_t)(4 * rb), bar);
-          if (ssrc) bulk_g2s(dst + G.sc_off[0] + warp * sb, ssrc, (uint32_t)sb, bar);
-          if (++tile == G.tiles0) tile = 0, ++p;
+          if (++idx == nst0) idx = 0, ++round;
         }
       }
       // phase 1: the ring is cut into nst1 stages of the smaller unit.  Before a stage is first used, the
@@ -615,28 +625,50 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
         const int rb = G.row_bytes[1], sb = G.sc_bytes[1];
         const int S0 = G.stage_bytes[0], S1 = G.stage_bytes[1];
         int p = 0, tile = t_begin;
+        // phase-0 stage s was used uses(s) = full + (s < rest) times
+        const int full = n0 / nst0, rest = n0 - full * nst0;
+        const long long off_w = bank.off[t_w2] + (long long)warp * 4 * rb;
+        const long long off_s = warp < n_sc ? bank.off[t_w2 + 1 + warp] : -1;
+        const uint32_t tx = (uint32_t)(4 * rb + (off_s >= 0 ? sb : 0));
+        int idx = 0;
+        uint32_t round = 0;
+        int waited = -1;   // phase-0 stages 0..waited are known to be free
+        int end_byte = 0;  // end of the current phase-1 stage inside the ring
+        int s_end = 0, s_end_byte = 0;  // first phase-0 stage that starts at or behind end_byte, and its start
+#ifdef CB_FUSED_TRACE
+        if (warp == 0) fused_trace[blockIdx.x][14] = gtimer();
+#endif
         for (int q = 0; q < n1 && !err; ++q) {
-          const int idx = q % nst1;
-          if (q >= nst1) {
-            if (!mbar_wait(&empty1[idx], (uint32_t)((q / nst1) - 1) & 1u)) err = 1;
+#ifdef CB_FUSED_TRACE
+          if (warp == 0 && q == 1) fused_trace[blockIdx.x][15] = gtimer();
+          if (warp == 0 && q < 12) fused_trace2[blockIdx.x][3 * q] = gtimer();
+#endif
+          if (round > 0) {
+            if (!mbar_wait(&empty1[idx], (round - 1u) & 1u)) err = 1;
           } else {
-            const int s_lo = idx * S1 / S0, s_hi = ((idx + 1) * S1 - 1) / S0;
-            for (int s0 = s_lo; s0 <= s_hi && s0 < nst0 && !err; ++s0) {
-              if (s0 >= n0) continue;                                 // never used in phase 0
-              const int i_last = s0 + ((n0 - 1 - s0) / nst0) * nst0;  // last phase-0 unit in that stage
-              if (!mbar_wait(&empty0[s0], (uint32_t)(i_last / nst0) & 1u)) err = 1;
+            end_byte += S1;
+            while (s_end_byte < end_byte) s_end_byte += S0, ++s_end;  // stages waited..s_end-1 overlap this or an earlier stage
+            for (int s0 = waited + 1; s0 < s_end && s0 < nst0 && !err; ++s0) {
+              const int uses = full + (s0 < rest ? 1 : 0);
+              if (uses > 0 && !mbar_wait(&empty0[s0], (uint32_t)(uses - 1) & 1u)) err = 1;
+              waited = s0;
             }
           }
           if (err) break;
+#ifdef CB_FUSED_TRACE
+          if (warp == 0 && q < 12) fused_trace2[blockIdx.x][3 * q + 1] = gtimer();
+#endif
           const uint8_t* rec = bank.base + (size_t)s_slot[p] * bank.record_bytes;
           uint8_t* dst = ring + (size_t)idx * S1;
           uint64_t* bar = &full1[idx];
-          const uint8_t* src = rec + bank.off[t_w2] + (size_t)tile * 16 * rb + (size_t)warp * 4 * rb;
-          const uint8_t* ssrc = warp < n_sc ? rec + bank.off[t_w2 + 1 + warp] + (size_t)tile * sb : nullptr;
-          mbar_expect_tx(bar, (uint32_t)(4 * rb + (ssrc ? sb : 0)));
-          bulk_g2s(dst + warp * 4 * rb, src, (uint32_t)(4 * rb), bar);
-          if (ssrc) bulk_g2s(dst + G.sc_off[1] + warp * sb, ssrc, (uint32_t)sb, bar);
+          mbar_expect_tx(bar, tx);
+          bulk_g2s(dst + warp * 4 * rb, rec + off_w + (size_t)tile * 16 * rb, (uint32_t)(4 * rb), bar);
+          if (off_s >= 0) bulk_g2s(dst + G.sc_off[1] + warp * sb, rec + off_s + (size_t)tile * sb, (uint32_t)sb, bar);
+#ifdef CB_FUSED_TRACE
+          if (warp == 0 && q < 12) fused_trace2[blockIdx.x][3 * q + 2] = gtimer();
+#endif
           if (++p == np) p = 0, ++tile;
+          if (++idx == nst1) idx = 0, ++round;
         }
       }
       if (err && status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
@@ -991,6 +1023,9 @@ bool layer_fused_supported(const BankView& v, int n_experts, int k) {
 }  // namespace cachalot
 
 #ifdef CB_FUSED_TRACE
+extern "C" __attribute__((visibility("default"))) int cachalot_debug_fused_trace2(unsigned long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, cachalot::fused_trace2, sizeof(unsigned long long) * 256 * 40);
+}
 extern "C" __attribute__((visibility("default"))) int cachalot_debug_fused_trace(unsigned long long* host) {
   return (int)cudaMemcpyFromSymbol(host, cachalot::fused_trace, sizeof(unsigned long long) * 256 * 16);
 }
