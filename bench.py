@@ -35,7 +35,7 @@ SWIGLU_LIMIT = 10.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # capture summarised under profiles/ (None until a capture exists for the workload)
-NCU_TRAFFIC_BYTES = {("affine2", 1, "fused"): 59836160 + 1223680}
+NCU_TRAFFIC_BYTES = {("affine2", 1, "fused"): 59832832 + 1246720}
 
 
 def parse_args():
