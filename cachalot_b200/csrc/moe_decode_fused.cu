@@ -191,6 +191,13 @@ __device__ __forceinline__ bool grid_barrier(unsigned* word, unsigned n_ctas, bo
 // split of the phase-0 units and phase-1 tiles over the CTAs
 __device__ __forceinline__ void cta_ranges(const Geo& G, int np, int b, int nb, int& u0, int& u1, int& t0, int& t1) {
   const long long U0 = (long long)np * G.tiles0;
+  if (!G.balance && U0 * nb < 0x7fffffffLL && (long long)G.tiles1 * nb < 0x7fffffffLL) {
+    // the usual case in 32-bit arithmetic: every thread does this before the first copy can be issued
+    const unsigned ub = (unsigned)b, un = (unsigned)nb, u32 = (unsigned)U0, t32 = (unsigned)G.tiles1;
+    t0 = (int)(t32 * ub / un), t1 = (int)(t32 * (ub + 1u) / un);
+    u0 = (int)(u32 * ub / un), u1 = (int)(u32 * (ub + 1u) / un);
+    return;
+  }
   t0 = (int)((long long)G.tiles1 * b / nb);
   t1 = (int)((long long)G.tiles1 * (b + 1) / nb);
   if (!G.balance) {
