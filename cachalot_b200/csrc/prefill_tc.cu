@@ -278,18 +278,20 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
       // The shared-memory ring is only two or three stages deep, less than the HBM latency under load, so the
       // weight tiles of the next PFD stages are asked into L2 ahead of their loads (2 measured best of 0/2/4/8).
       constexpr int PFD = 2;
-      long long pw = blockIdx.x;  // prefetch cursor (item, stage)
-      int pks = 0;
+      long long pw = blockIdx.x;  // prefetch cursor (item, stage); the item's slot and row are looked up once per item
+      int pks = 0, p_slot = 0, p_row = 0;
       auto prefetch_next = [&]() {
         if (pw >= total) return;
-        const Unit u = A.units[pw / n_mt];
-        const int mt = (int)(pw % n_mt);
+        if (pks == 0) {
+          p_slot = A.units[pw / n_mt].slot;
+          p_row = (int)(pw % n_mt) * BM;
+        }
 #pragma unroll
         for (int j = 0; j < KSUB; ++j) {
           const int kx = (pks * KSUB + j) * BKB;
           if (kx >= k_bytes) break;
-          tma_prefetch_3d(&map_a0, kx, mt * BM, u.slot);
-          if (NA == 2) tma_prefetch_3d(&map_a1, kx, mt * BM, u.slot);
+          tma_prefetch_3d(&map_a0, kx, p_row, p_slot);
+          if (NA == 2) tma_prefetch_3d(&map_a1, kx, p_row, p_slot);
         }
         if (++pks == nks) pks = 0, pw += gridDim.x;
       };
