@@ -12,4 +12,5 @@ void set_error(const char* fmt, ...) {
 }  // namespace cachalot
 
 extern "C" const char* cachalot_last_error(void) { return cachalot::g_error; }
-extern "C" int cachalot_version(void) { return 1; }
+// 2: cachalot_group_rows takes cachalot_group_rows_scratch_ints() of scratch; rows-level prefill, combine and peer sum added
+extern "C" int cachalot_version(void) { return 2; }

@@ -93,7 +93,7 @@ typedef struct {
 } cachalot_bank_desc;
 
 CACHALOT_API const char* cachalot_last_error(void);
-CACHALOT_API int cachalot_version(void);
+CACHALOT_API int cachalot_version(void); /* ABI revision, 2 for this header */
 
 /* ---- dequantisation (bit-exact against the reference's numpy path) ------------------------ */
 
