@@ -86,6 +86,12 @@ class ClockSampler:
                                           "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
+            # nvidia-smi needs some tens of milliseconds to deliver its first line; the timed region is not much
+            # longer, so wait for that line before the region starts
+            t_end = time.time() + 2.0
+            while not self.rows and time.time() < t_end:
+                time.sleep(0.005)
+            self.first = len(self.rows)
         except OSError:
             self.proc = None
 
