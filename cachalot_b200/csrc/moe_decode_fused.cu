@@ -703,9 +703,12 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
     // -------- phase 0 --------
     CYC_DECL;
     CYC_START;
+    // stage index and round of the pair's units are counted (no division per unit)
+    int idx = pr % nst0;
+    uint32_t rnd = (uint32_t)(pr / nst0);
+    int pu = n0 > 0 ? (u_begin + pr) / G.tiles0 : 0, tu = n0 > 0 ? (u_begin + pr) - pu * G.tiles0 : 0;  // expert and tile of unit i
     for (int i = pr; i < n0; i += NPAIR, ++n_done) {
-      const int idx = i % nst0;
-      if (!err && !mbar_wait(&full0[idx], (uint32_t)(i / nst0) & 1u)) err = 1;
+      if (!err && !mbar_wait(&full0[idx], rnd & 1u)) err = 1;
       CYC_ADD(cyc_a);
       if (cw == 0 && i == 0) TRACE(2);
       float2 r = unit_dot<FMT, 0, SDT>(ring + (size_t)idx * G.stage_bytes[0], G, act, pexs, zeros, g, t, part);
@@ -718,8 +721,7 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
       named_bar_sync(pair_bar, 64);
       if (part == 0 && t == 0) {
         const float2 o = xb2[g];
-        const int u = u_begin + i;
-        const int p = u / G.tiles0, tile = u - p * G.tiles0;
+        const int p = pu, tile = tu;
         float gv = r.x + o.x, uv = r.y + o.y;
         if (numerics != CACHALOT_NUMERICS_F32) gv = bf16_round(gv), uv = bf16_round(uv);
         float h = swiglu(gv, uv, limit) * s_gw[p];
@@ -731,6 +733,10 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
         else hidden[hi_] = h;
       }
       CYC_ADD(cyc_b);
+      idx += NPAIR;
+      while (idx >= nst0) idx -= nst0, ++rnd;
+      tu += NPAIR;
+      while (tu >= G.tiles0) tu -= G.tiles0, ++pu;
     }
     if (cw == 0) { TRACE(3); CYC_STORE(11, cyc_a); CYC_STORE(12, cyc_b); }
 
