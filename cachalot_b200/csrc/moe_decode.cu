@@ -231,12 +231,16 @@ static int launch_decode(const BankView& v, const void* x, const int32_t* slots,
   size_t smem_gu = (size_t)H * 4 + (FMT == CACHALOT_BANK_AFFINE ? (size_t)(H / CH) * 4 : 0);
   size_t smem_dn = (size_t)I * 4 + (FMT == CACHALOT_BANK_AFFINE ? (size_t)(I / CH) * 4 : 0);
   if (smem_gu > 200 * 1024 || smem_dn > 200 * 1024) return fail(CACHALOT_EINVAL, "moe_decode: hidden/inter too large for shared memory");
-  static bool attr_done[2] = {false, false};
-  if (!attr_done[FMT]) {
-    cudaFuncSetAttribute(gate_up_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    cudaFuncSetAttribute(down_kernel<FMT, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    cudaFuncSetAttribute(down_kernel<FMT, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    attr_done[FMT] = true;
+  // the shared-memory opt-in is a per-device attribute of a kernel: once per device and format
+  static bool attr_done[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(CACHALOT_ECUDA, "moe_decode: no current device");
+  if (!attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gate_up_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(down_kernel<FMT, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(down_kernel<FMT, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return fail(CACHALOT_ECUDA, "moe_decode: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attr_done[dev] = true;
   }
   int rc = CACHALOT_OK;
   if (do_gate_up) {
@@ -389,7 +393,8 @@ extern "C" size_t cachalot_moe_prefill_workspace_bytes(const cachalot_bank_desc*
   b += align_up(rows * sizeof(int32_t), 256);                     // slot per routed row
   if (mxfp4_act) b += align_up((size_t)tokens * desc->hidden * 2, 256);  // MXFP4-rounded x as bf16
   if (mxfp4_act == 1 && desc->format == CACHALOT_BANK_FP4) {
-    const size_t tc = prefill_tc_workspace_bytes(desc->hidden, desc->inter, tokens, k, /*n_experts<=*/tokens * k);
+    // experts without rows get no unit, so the unit list is bounded by the rows whatever the number of experts is
+    const size_t tc = prefill_tc_workspace_bytes(desc->hidden, desc->inter, tokens, k, tokens * k);
     if (tc > b) b = tc;
   }
   return b;
@@ -413,7 +418,7 @@ extern "C" int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc* 
   if (!aligned(workspace, 256)) return fail(CACHALOT_EALIGN, "moe_prefill: workspace must be 256-byte aligned");
   cudaStream_t s = (cudaStream_t)stream;
   const size_t rows = (size_t)tokens * k;
-  if (mxfp4_act == 1 && prefill_tc_supported(v) && (size_t)n_experts <= rows)
+  if (mxfp4_act == 1 && prefill_tc_supported(v))
     return launch_prefill_tc(v, x_bf16, perm, offsets, slot_of_expert, gate_w, tokens, k, n_experts, swiglu_limit, workspace, out,
                              status, s);
   uint8_t* ws = static_cast<uint8_t*>(workspace);

@@ -4,13 +4,12 @@
 //   grid barrier
 //   phase 1 : out[n]       = sum_j W2_j[n, :] . hidden[j, :]               j in routing order
 //
-// The kernel is a stream of weight bytes: HBM -> cp.async.bulk (one copy per tile of 8 or 16
-// weight rows, 8..23 KB) -> a ring of shared-memory stages -> registers -> mma.sync.  Warps 0 and 1
-// issue the copies and run ahead of the consumers by the depth of the ring; they keep issuing the
-// down-projection rows while the CTA waits at the grid barrier, so HBM stays busy across it.
-// Warps 3..11 each own a slice of the reduction dimension of every stage (their activation
-// operand stays in registers); warp 2 adds the nine partial sums of a stage, applies SwiGLU / the
-// sum over experts and writes the results.
+// The kernel is a stream of weight bytes: HBM -> cp.async.bulk (four copies of four weight rows per
+// unit, one per copy warp) -> a ring of shared-memory stages -> registers -> mma.sync.  Warps 0..3
+// issue the copies (one lane each) and run ahead of the consumers by the depth of the ring; they keep
+// issuing the down projection's rows while the CTA waits at the grid barrier, so HBM stays busy across it.
+// Warps 4..11 are four pairs of MMA warps.  A pair takes one unit; each warp of the pair does half
+// of the reduction dimension and the two partial sums meet in shared memory.
 //
 //   unit, phase 0 : 8 rows of W1 (MMA rows 0..7) + the same 8 rows of W3 (MMA rows 8..15) of one expert
 //   unit, phase 1 : 16 rows of W2 of one expert; a CTA owns whole 16-row output tiles and walks
@@ -31,6 +30,10 @@
 //                acc += s * 2**-e * (256*T_hi + T_lo) + b * sum(x).
 //   FP4 bank   : E2M1 byte -> f16x2 (cvt.rn.f16x2.e2m1x2), HMMA m16n8k16 with f16 activations
 //                scaled per sub-block by 2**e;  acc += 2**(scale-127) * 2**-e * T.
+#include <mutex>
+#include <set>
+#include <utility>
+
 #include "kernels.cuh"
 
 #ifndef CB_UNROLL
@@ -41,10 +44,6 @@ namespace cachalot {
 namespace {
 
 constexpr int kUnroll = CB_UNROLL;  // steps of the reduction loop unrolled together
-
-#ifndef CB_UNROLL
-#define CB_UNROLL 4
-#endif
 constexpr int NPROD = 4;                          // producer warps (one issuing lane each; a lane's copies do not overlap)
 constexpr int KMAX = 8;                           // routed experts per token
 constexpr int MAX_TILES = 8;                      // phase-1 output tiles one CTA may own
@@ -64,26 +63,6 @@ struct Fm {
   static constexpr int SUB = FMT == CACHALOT_BANK_FP4 ? 32 : 64;       // codes per sub-block (16 B)
 };
 
-#ifdef CB_FUSED_TRACE
-__device__ unsigned long long fused_trace[256][16];
-__device__ unsigned long long fused_trace2[256][40];
-__device__ __forceinline__ unsigned long long gtimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define TRACE(slot) do { if (lane == 0) fused_trace[blockIdx.x][slot] = gtimer(); } while (0)
-#define CYC_DECL long long cyc_a = 0, cyc_b = 0, cyc_c = 0, cyc_t = 0
-#define CYC_START do { cyc_t = clock64(); } while (0)
-#define CYC_ADD(acc) do { long long n_ = clock64(); acc += n_ - cyc_t; cyc_t = n_; } while (0)
-#define CYC_STORE(slot, acc) do { if (lane == 0) fused_trace[blockIdx.x][slot] = (unsigned long long)(acc); } while (0)
-#else
-#define TRACE(slot) do { } while (0)
-#define CYC_DECL do { } while (0)
-#define CYC_START do { } while (0)
-#define CYC_ADD(acc) do { } while (0)
-#define CYC_STORE(slot, acc) do { } while (0)
-#endif
 
 // Grid barrier word (sense reversal on the top bit, so it needs no reset): every device that loads
 // the library has its own copy, zero at load.  A launch uses it once; two launches cannot be at
@@ -438,6 +417,28 @@ __device__ __forceinline__ float2 unit_dot(const uint8_t* stage, const Geo& G, c
   return make_float2(accA, accB);
 }
 
+// One round of a warp-wide selection over up to three (order key, expert id) entries per lane: returns the id of
+// the best entry (larger key first; equal keys: the lower id when low_wins, else the higher id) and clears that
+// entry (key 0 = taken or absent), or -1 when nothing is left.  All lanes get the same answer.
+__device__ __forceinline__ int warp_arg_best(uint32_t (&ord)[3], int (&id)[3], bool low_wins) {
+  uint32_t bo = 0u;
+  int bi = -1;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    const bool better = ord[i] > bo || (ord[i] == bo && ord[i] != 0u && (low_wins ? id[i] < bi : id[i] > bi));
+    if (better) bo = ord[i], bi = id[i];
+  }
+  const uint32_t wo = __reduce_max_sync(0xffffffffu, bo);
+  if (wo == 0u) return -1;
+  const bool cand = bo == wo;
+  const int win = low_wins ? (int)__reduce_min_sync(0xffffffffu, cand ? (unsigned)bi : 0x7fffffffu)
+                           : (int)__reduce_max_sync(0xffffffffu, cand ? (unsigned)(bi + 1) : 0u) - 1;
+#pragma unroll
+  for (int i = 0; i < 3; ++i)
+    if (id[i] == win) ord[i] = 0u;
+  return win;
+}
+
 template <int FMT, int SDT, typename OutT>
 __global__ void __launch_bounds__(Fm<FMT>::NTHREADS, 1)
 fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ slots,
@@ -462,6 +463,13 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
   const int H = bank.hidden, I = bank.inter;
   int err = 0;
   if (threadIdx.x < 128) reinterpret_cast<uint32_t*>(smem + G.off_bar + 512)[threadIdx.x] = 0u;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 16; ++s) {
+      mbar_init(&full0[s], NPROD), mbar_init(&empty0[s], 2);
+      mbar_init(&full1[s], NPROD), mbar_init(&empty1[s], 2);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
 
   // consumers fetch their part of x before anything else (up to XB 16-element blocks per thread)
   constexpr int XB = 3;
@@ -483,6 +491,10 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
   uint32_t* r_ord = reinterpret_cast<uint32_t*>(smem + G.off_act + G.act_stride[0]);  // scratch behind x in the operand area
   float* r_score = reinterpret_cast<float*>(r_ord + 1024);
   int32_t* r_slot = reinterpret_cast<int32_t*>(r_ord + 2048);
+  uint32_t* c_ord = r_ord + 3072;                           // [warps][KMAX] every warp's k best: order key ...
+  int32_t* c_id = reinterpret_cast<int32_t*>(r_ord + 3200);  // ... and expert id (-1: none)
+  constexpr int NW = Fm<FMT>::NTHREADS / 32;
+  const bool low_wins = R.mode == CACHALOT_ROUTER_SIGMOID;  // ties: the sigmoid router prefers the lower index
   if (R.logits) {
     for (int e = threadIdx.x; e < R.n_experts; e += blockDim.x) {
       // the three loads are independent: one round trip to L2 for the whole routing tail
@@ -497,37 +509,42 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
       r_score[e] = sc, r_slot[e] = sl;
     }
     __syncthreads();
+    // first every warp picks the k best of its own span of experts (up to three per lane), then warp 0 picks
+    // the k best of the warps' candidates: the selection is a handful of warp reductions instead of k passes
+    // of one warp over all experts
+    const int span = (R.n_experts + NW - 1) / NW;
+    uint32_t ord[3];
+    int id[3];
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const int off = i * 32 + lane, e = warp * span + off;
+      const bool ok = off < span && e < R.n_experts;
+      ord[i] = ok ? r_ord[e] : 0u, id[i] = ok ? e : -1;
+    }
+    for (int r = 0; r < KMAX; ++r) {
+      const int win = r < k ? warp_arg_best(ord, id, low_wins) : -1;
+      if (lane == 0) c_id[warp * KMAX + r] = win, c_ord[warp * KMAX + r] = win >= 0 ? r_ord[win] : 0u;
+    }
+    __syncthreads();
   }
-  // warp 0: the present experts in routing order; its lane 0: the barriers
+  // warp 0: the present experts in routing order
   if (warp == 0) {
     int my_slot = -1;
     float my_w = 0.f;
     if (R.logits) {
-      // k rounds of a warp-wide arg-best.  Lane l keeps experts l, l + 32, ... in registers; a taken expert's
-      // order drops to 0 (below every real one).  Ties: the sigmoid router prefers the lower index, the other
-      // the larger one, as route_topk_kernel does.
-      const bool low_wins = R.mode == CACHALOT_ROUTER_SIGMOID;
+      // a taken candidate's order drops to 0 (below every real one)
       const bool ascending = !low_wins;  // the sqrt-softplus router writes the weakest first
-      uint32_t ord[32];
+      uint32_t ord[3];
+      int id[3];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) ord[i] = (i * 32 + lane < R.n_experts) ? r_ord[i * 32 + lane] : 0u;
+      for (int i = 0; i < 3; ++i) {
+        const int c = i * 32 + lane;
+        ord[i] = c < NW * KMAX ? c_ord[c] : 0u, id[i] = c < NW * KMAX ? c_id[c] : -1;
+      }
       int my_e = -1;
       for (int r = 0; r < k; ++r) {
-        uint32_t bo = 0u;
-        int bi = -1;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const bool better = low_wins ? ord[i] > bo : (ord[i] >= bo && ord[i] != 0u);
-          if (better) bo = ord[i], bi = i * 32 + lane;
-        }
-        const uint32_t wo = __reduce_max_sync(0xffffffffu, bo);
-        const bool cand = bo == wo && bi >= 0;
-        const int win = low_wins ? (int)__reduce_min_sync(0xffffffffu, cand ? (unsigned)bi : 0x7fffffffu)
-                                 : (int)__reduce_max_sync(0xffffffffu, cand ? (unsigned)(bi + 1) : 0u) - 1;
-        if (wo == 0u) break;  // fewer than k experts
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i * 32 + lane == win) ord[i] = 0u;
+        const int win = warp_arg_best(ord, id, low_wins);
+        if (win < 0) break;  // fewer than k experts
         if (lane == (ascending ? k - 1 - r : r)) my_e = win;
       }
       // lane r holds output position r; the total is added up in output order as route_topk_kernel does
@@ -565,17 +582,9 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
     }
     const bool oob = lane < k && my_slot >= bank.n_slots;
     if (__any_sync(0xffffffffu, oob) && lane == 0 && blockIdx.x == 0 && status) atomicOr(status, CACHALOT_STATUS_SLOT_RANGE);
-    if (lane == 0) {
-      s_np = __popc(pmask);
-      for (int s = 0; s < 16; ++s) {
-        mbar_init(&full0[s], NPROD), mbar_init(&empty0[s], 2);
-        mbar_init(&full1[s], NPROD), mbar_init(&empty1[s], 2);
-      }
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
+    if (lane == 0) s_np = __popc(pmask);
   }
   __syncthreads();
-  if (warp == NPROD) TRACE(0);
   const int np = s_np;
   int u_begin, u_end, t_begin, t_end;
   cta_ranges(G, np, blockIdx.x, gridDim.x, u_begin, u_end, t_begin, t_end);
@@ -642,14 +651,7 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
         int waited = -1;   // phase-0 stages 0..waited are known to be free
         int end_byte = 0;  // end of the current phase-1 stage inside the ring
         int s_end = 0, s_end_byte = 0;  // first phase-0 stage that starts at or behind end_byte, and its start
-#ifdef CB_FUSED_TRACE
-        if (warp == 0) fused_trace[blockIdx.x][14] = gtimer();
-#endif
         for (int q = 0; q < n1 && !err; ++q) {
-#ifdef CB_FUSED_TRACE
-          if (warp == 0 && q == 1) fused_trace[blockIdx.x][15] = gtimer();
-          if (warp == 0 && q < 12) fused_trace2[blockIdx.x][3 * q] = gtimer();
-#endif
           if (round > 0) {
             if (!mbar_wait(&empty1[idx], (round - 1u) & 1u)) err = 1;
           } else {
@@ -662,25 +664,18 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
             }
           }
           if (err) break;
-#ifdef CB_FUSED_TRACE
-          if (warp == 0 && q < 12) fused_trace2[blockIdx.x][3 * q + 1] = gtimer();
-#endif
           const uint8_t* rec = bank.base + (size_t)s_slot[p] * bank.record_bytes;
           uint8_t* dst = ring + (size_t)idx * S1;
           uint64_t* bar = &full1[idx];
           mbar_expect_tx(bar, tx);
           bulk_g2s(dst + warp * 4 * rb, rec + off_w + (size_t)tile * 16 * rb, (uint32_t)(4 * rb), bar);
           if (off_s >= 0) bulk_g2s(dst + G.sc_off[1] + warp * sb, rec + off_s + (size_t)tile * sb, (uint32_t)sb, bar);
-#ifdef CB_FUSED_TRACE
-          if (warp == 0 && q < 12) fused_trace2[blockIdx.x][3 * q + 2] = gtimer();
-#endif
           if (++p == np) p = 0, ++tile;
           if (++idx == nst1) idx = 0, ++round;
         }
       }
       if (err && status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
     }
-    if (warp < 2) TRACE(9 + warp);
   } else {
     // ---------------- consumers: pair `pr` takes units pr, pr + NPAIR, ... of the CTA's stream ----------------
     constexpr int NPAIR = Fm<FMT>::NPAIR;
@@ -697,20 +692,15 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
       }
     }
     named_bar_sync(1, NCT);
-    if (cw == 0) TRACE(1);
     int n_done = 0;  // units of this pair so far (selects the exchange buffer)
 
     // -------- phase 0 --------
-    CYC_DECL;
-    CYC_START;
     // stage index and round of the pair's units are counted (no division per unit)
     int idx = pr % nst0;
     uint32_t rnd = (uint32_t)(pr / nst0);
     int pu = n0 > 0 ? (u_begin + pr) / G.tiles0 : 0, tu = n0 > 0 ? (u_begin + pr) - pu * G.tiles0 : 0;  // expert and tile of unit i
     for (int i = pr; i < n0; i += NPAIR, ++n_done) {
       if (!err && !mbar_wait(&full0[idx], rnd & 1u)) err = 1;
-      CYC_ADD(cyc_a);
-      if (cw == 0 && i == 0) TRACE(2);
       float2 r = unit_dot<FMT, 0, SDT>(ring + (size_t)idx * G.stage_bytes[0], G, act, pexs, zeros, g, t, part);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty0[idx]);
@@ -732,23 +722,19 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
         if (numerics == CACHALOT_NUMERICS_BF16) reinterpret_cast<__nv_bfloat16*>(hidden)[hi_] = __float2bfloat16_rn(h);
         else hidden[hi_] = h;
       }
-      CYC_ADD(cyc_b);
       idx += NPAIR;
       while (idx >= nst0) idx -= nst0, ++rnd;
       tu += NPAIR;
       while (tu >= G.tiles0) tu -= G.tiles0, ++pu;
     }
-    if (cw == 0) { TRACE(3); CYC_STORE(11, cyc_a); CYC_STORE(12, cyc_b); }
 
     // -------- grid barrier: every CTA's hidden rows are written --------
     named_bar_sync(1, NCT);
     if (cw == 0) {
-      TRACE(4);
       if (lane == 0) {
         if (!grid_barrier(&grid_bar_word, gridDim.x, blockIdx.x == 0)) err = 2;
       }
       __syncwarp();
-      TRACE(5);
     }
     named_bar_sync(1, NCT);
 
@@ -820,15 +806,12 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
       }
     }
     named_bar_sync(1, NCT);
-    if (cw == 0) TRACE(6);
 
     // -------- phase 1: unit q of the CTA = (tile t_begin + q / np, expert q % np) --------
-    CYC_START;
     for (int q = pr; q < n1; q += NPAIR, ++n_done) {
       const int idx = q % nst1;
       const int tl = q / np, p = q - tl * np;
       if (!err && !mbar_wait(&full1[idx], (uint32_t)(q / nst1) & 1u)) err = 1;
-      CYC_ADD(cyc_c);
       float2 r = unit_dot<FMT, 1, SDT>(ring + (size_t)idx * G.stage_bytes[1], G, act + (size_t)p * row_stride1, pexs + p * nsub1, zeros, g, t, part);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty1[idx]);
@@ -846,7 +829,6 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
         ybuf[(tl * KMAX + p) * 16 + wr + 8] = y1;
       }
     }
-    if (cw == 0) { TRACE(7); CYC_STORE(13, cyc_c); }
     named_bar_sync(1, NCT);
     // sum over the experts in routing order
     for (int o = tid; o < (t_end - t_begin) * 16; o += NCT) {
@@ -858,12 +840,13 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
       else
         out[(t_begin + tl) * 16 + r] = tot;
     }
-    if (cw == 0) TRACE(8);
     if (err && lane == 0 && status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
   }
 }
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+constexpr int MAX_DEVICES = 64;
 
 template <int FMT>
 bool make_geo_fmt(const BankView& v, int k, Geo* out) {
@@ -952,10 +935,12 @@ static int launch_fused_fmt(const BankView& v, const Geo& G, const RouteArgs& R,
                             const float* gate_w, int k, float limit, int numerics, void* workspace, void* out, int out_dtype,
                             int* status, cudaStream_t stream) {
   float* hidden = static_cast<float*>(workspace);
-  int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return fail(CACHALOT_ECUDA, "moe_decode (fused): no current device");
+  static int sm_count[MAX_DEVICES] = {};
+  if (!sm_count[dev] && (cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count[dev] <= 0))
     return fail(CACHALOT_ECUDA, "moe_decode (fused): cannot read the SM count");
+  const int sms = sm_count[dev];
   const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
   Geo Gl = G;
   // the byte-balanced split needs every CTA's share to be larger than the phase-1 tiles it owns
@@ -972,7 +957,11 @@ static int launch_fused_fmt(const BankView& v, const Geo& G, const RouteArgs& R,
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)sms);
   cfg.blockDim = dim3(Fm<FMT>::NTHREADS);
-  cfg.dynamicSmemBytes = (size_t)G.total;
+  // Always the whole shared memory of an SM, also for small banks: one CTA per SM, so a second launch (from
+  // another stream) cannot become resident, and cannot touch the grid barrier word, before this launch's CTAs
+  // have passed their barrier and left.
+  cfg.dynamicSmemBytes = (size_t)(SMEM_LIMIT - 256);
+  (void)G.total;
   cfg.stream = stream;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident: the grid barrier cannot starve
@@ -981,8 +970,19 @@ static int launch_fused_fmt(const BankView& v, const Geo& G, const RouteArgs& R,
   cfg.numAttrs = 1;
   cudaError_t e = cudaSuccess;
   auto go = [&](auto kern, auto* outp) {
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT - 256);
-    if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, v, Gl, R, xb, slots, gate_w, k, limit, numerics, hidden, outp, status);
+    // the opt-in is an attribute of a kernel on a device: set once for each (the pointer types of different
+    // instantiations coincide, so the record is keyed by the pointer)
+    static std::mutex mu;
+    static std::set<std::pair<const void*, int>> done;
+    {
+      std::lock_guard<std::mutex> lock(mu);
+      if (!done.count({(const void*)kern, dev})) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT - 256);
+        if (e != cudaSuccess) return;
+        done.insert({(const void*)kern, dev});
+      }
+    }
+    e = cudaLaunchKernelEx(&cfg, kern, v, Gl, R, xb, slots, gate_w, k, limit, numerics, hidden, outp, status);
   };
   const bool bf16_scales = FMT == CACHALOT_BANK_AFFINE && v.scale_dtype == CACHALOT_BF16;
   if (out_dtype == CACHALOT_BF16) {
@@ -1015,7 +1015,7 @@ int launch_layer_fused(const BankView& v, const void* x, const float* logits, co
                        int32_t* indices_out, float* weights_out, int* status, cudaStream_t stream) {
   Geo G;
   if (!make_geo(v, k, &G) || n_experts > 1024) return CACHALOT_EUNSUPPORTED;
-  if (G.act_stride[1] * k < G.act_stride[0] + 12288) return CACHALOT_EUNSUPPORTED;  // the routing scratch sits behind x in the operand area
+  if (G.act_stride[1] * k < G.act_stride[0] + 13312) return CACHALOT_EUNSUPPORTED;  // the routing scratch sits behind x in the operand area
   const int numerics = numerics_flags & 0xff;
   RouteArgs R = {};
   R.logits = logits, R.bias = bias, R.slot_table = slot_table, R.indices_out = indices_out, R.weights_out = weights_out;
@@ -1030,16 +1030,8 @@ bool layer_fused_supported(const BankView& v, int n_experts, int k) {
   Geo G;
   if (k < 1 || k > KMAX || n_experts < k || n_experts > 1024) return false;
   if (v.format == CACHALOT_BANK_AFFINE && (v.group != 128 || v.bits != 2)) return false;
-  return make_geo(v, k, &G) && G.act_stride[1] * k >= G.act_stride[0] + 12288;
+  return make_geo(v, k, &G) && G.act_stride[1] * k >= G.act_stride[0] + 13312;
 }
 
 }  // namespace cachalot
 
-#ifdef CB_FUSED_TRACE
-extern "C" __attribute__((visibility("default"))) int cachalot_debug_fused_trace2(unsigned long long* host) {
-  return (int)cudaMemcpyFromSymbol(host, cachalot::fused_trace2, sizeof(unsigned long long) * 256 * 40);
-}
-extern "C" __attribute__((visibility("default"))) int cachalot_debug_fused_trace(unsigned long long* host) {
-  return (int)cudaMemcpyFromSymbol(host, cachalot::fused_trace, sizeof(unsigned long long) * 256 * 16);
-}
-#endif

@@ -38,17 +38,6 @@ constexpr int TMEM_COLS = 512;
 constexpr int SF_COL = 2 * 2 * NTMAX;  // scale columns start behind the (up to) four accumulators
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
 
-#ifdef CB_PF_TRACE
-// development build: per-CTA cycle counts of where each role waits
-__device__ unsigned long long pf_trace[2][256][16];
-#define PF_T0 long long t0_ = clock64()
-#define PF_ADD(acc) do { long long n_ = clock64(); acc += n_ - t0_; t0_ = n_; } while (0)
-#define PF_STORE(slot, v) pf_trace[NA - 1][blockIdx.x][slot] = (unsigned long long)(v)
-#else
-#define PF_T0 do { } while (0)
-#define PF_ADD(acc) do { } while (0)
-#define PF_STORE(slot, v) do { } while (0)
-#endif
 
 struct Unit {
   int32_t slot, row_start, ntok, pad;
@@ -274,7 +263,6 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
       int s = 0;
       uint32_t ph = 0;
       bool wrapped = false, ok = true;
-      long long c_wait = 0, c_issue = 0;
       // The shared-memory ring is only two or three stages deep, less than the HBM latency under load, so the
       // weight tiles of the next PFD stages are asked into L2 ahead of their loads (2 measured best of 0/2/4/8).
       constexpr int PFD = 2;
@@ -317,15 +305,12 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
       };
       long long item_no = 0;
       if (RAW && total > blockIdx.x) ok = raw_copy(blockIdx.x, 0);
-      PF_T0;
       for (long long w = blockIdx.x; w < total && ok; w += gridDim.x, ++item_no) {
         const Unit u = A.units[w / n_mt];
         const int mt = (int)(w % n_mt);
         if (RAW && w + gridDim.x < total && !raw_copy(w + gridDim.x, item_no + 1)) { ok = false; break; }
         for (int ks = 0; ks < nks; ++ks) {
-          PF_ADD(c_issue);
           if (wrapped && !mbar_wait(&empty[s], ph ^ 1u, abort)) { ok = false; break; }
-          PF_ADD(c_wait);
           uint8_t* st = smem + (size_t)s * STAGE_BYTES;
           mbar_expect_tx(&full[s], KSUB * (NA * A_TILE + B_TILE));
 #pragma unroll
@@ -340,8 +325,6 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
           prefetch_next();
         }
       }
-      PF_STORE(0, c_wait);
-      PF_STORE(1, c_issue);
     }
   } else if (warp == 1) {
     // ---- scale copies into TMEM and the MMAs -------------------------------------------------
@@ -355,11 +338,6 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
       const uint64_t d_op0 = desc_sw128(smem_u32(smem));
       const uint64_t d_sf0 = desc_sf(smem_u32(smem) + OFF_SF);
       const uint32_t t_sf = tmem + SF_COL;
-      long long c_acc = 0, c_full = 0, c_issue = 0;
-#ifdef CB_PF_TRACE
-      const long long t_begin = clock64();
-#endif
-      PF_T0;
       for (long long w = blockIdx.x; w < total && ok; w += gridDim.x, ++item) {
         const Unit u = A.units[w / n_mt];
         const int buf = (int)(item & 1);
@@ -367,14 +345,10 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
         const uint32_t id2 = id0 | (2u << 29) | (2u << 4);  // scale bytes 2,3 of the column for the second K=64 of a pair
         const uint32_t t_acc = tmem + buf * ACC_COLS;
         uint32_t accumulate = 0;
-        PF_ADD(c_issue);
         if (item >= 2 && !mbar_wait(&acc_empty[buf], (uint32_t)((item >> 1) - 1) & 1u, abort)) { ok = false; break; }
-        PF_ADD(c_acc);
         tc_fence_after();
         for (int ks = 0; ks < nks; ++ks) {
-          PF_ADD(c_issue);
           if (!mbar_wait(&full[s], ph, abort)) { ok = false; break; }
-          PF_ADD(c_full);
           tc_fence_after();
           const uint64_t so = (uint64_t)((uint32_t)(s * STAGE_BYTES) >> 4);
           const uint64_t dop = d_op0 + so, dsf = d_sf0 + so;
@@ -406,13 +380,6 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
         }
         if (ok) tc_commit(&acc_full[buf]);
       }
-      PF_STORE(2, c_acc);
-      PF_STORE(3, c_full);
-      PF_STORE(4, c_issue);
-#ifdef CB_PF_TRACE
-      PF_STORE(5, clock64() - t_begin);
-#endif
-      PF_STORE(6, item);
     }
   } else if (warp < 6) {
     // ---- scale bytes: bank rows -> the stage's 32x16-byte groups --------------------------------
@@ -515,15 +482,11 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
     int s = 0;
     uint32_t ph = 0;
     bool wrapped = false;
-    long long c_ld = 0, c_lw = 0;
-    PF_T0;
     // writes one stage from `cur` after asking for the stage two ahead into `far`; false when a wait gave up
     auto step = [&](uint4 (&cur)[NA + 1], uint4 (&far)[NA + 1]) -> bool {
       fetch(far);
       if (RAW && !raw_ok) return false;
-      PF_ADD(c_ld);
       if (wrapped && !__all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u, abort))) return false;
-      PF_ADD(c_lw);
       uint8_t* sf = smem + (size_t)s * STAGE_BYTES + OFF_SF;
 #pragma unroll
       for (int mm = 0; mm < NA + 1; ++mm) {
@@ -546,8 +509,6 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
       if (i + 2 < n_stage && !step(set_c, set_b)) break;
     }
     if (warp == 2 && lane == 0) {
-      PF_STORE(9, c_ld);
-      PF_STORE(10, c_lw);
     }
   } else {
     // ---- accumulators -> results ----------------------------------------------------------------
@@ -557,17 +518,13 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
     const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
     long long item = 0;
     bool ok = true;
-    long long c_wait = 0, c_work = 0;
-    PF_T0;
     for (long long w = blockIdx.x; w < total && ok; w += gridDim.x, ++item) {
       const Unit u = A.units[w / n_mt];
       const int mt = (int)(w % n_mt);
       const int buf = (int)(item & 1);
       const int n = mt * BM + q * 32 + lane;           // weight row = output index
       const bool rows_ok = mt * BM + q * 32 < A.n_rows;  // whole warps: n_rows is a multiple of 32
-      PF_ADD(c_work);
       if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (uint32_t)(item >> 1) & 1u, abort))) { ok = false; break; }
-      PF_ADD(c_wait);
       tc_fence_after();
       for (int j0 = 16 * half; j0 < u.ntok; j0 += 32) {
         uint32_t g[16], up[16];
@@ -605,8 +562,6 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
     if (warp == 6 && lane == 0) {
-      PF_STORE(7, c_wait);
-      PF_STORE(8, c_work);
     }
   }
 
@@ -774,7 +729,8 @@ RowScratch carve_rows(uint8_t* base, int inter, size_t rows, int n_seg) {
   };
   s.h_codes = take(rows * (inter / 2));
   s.h_scales = take(rows * (inter / 32) + 32);
-  s.units = reinterpret_cast<Unit*>(take((rows / NTMAX + n_seg + 1) * sizeof(Unit)));
+  // a segment with r rows gives ceil(r / NTMAX) units and an empty one none: at most rows / NTMAX + min(n_seg, rows)
+  s.units = reinterpret_cast<Unit*>(take((rows / NTMAX + ((size_t)n_seg < rows ? (size_t)n_seg : rows) + 1) * sizeof(Unit)));
   s.n_units = reinterpret_cast<int32_t*>(take(256));
   s.total = at;
   return s;
@@ -917,8 +873,3 @@ int launch_prefill_tc(const BankView& v, const void* x_bf16, const int32_t* perm
 
 }  // namespace cachalot
 
-#ifdef CB_PF_TRACE
-extern "C" __attribute__((visibility("default"))) int cachalot_debug_prefill_trace(unsigned long long* host) {
-  return (int)cudaMemcpyFromSymbol(host, cachalot::pf_trace, sizeof(unsigned long long) * 2 * 256 * 16);
-}
-#endif

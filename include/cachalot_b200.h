@@ -55,13 +55,15 @@ enum {
                                  (model/expert_affine.py:74-81, model/fp4_sgmm_metal.py:203-233) */
   CACHALOT_NUMERICS_BF16_H32 = 2 /* as BF16 but h stays fp32 (it is quantised to MXFP4 next) */
 };
-/* profiling aids, OR-ed into `numerics`: run only one of the two launches of cachalot_moe_decode */
+/* Kernel selection, OR-ed into `numerics`.  These exist for cross-checks and per-kernel timing; a caller that
+ * wants the result leaves them clear.
+ *   SIMPLE  : the one-warp-per-output kernels (any shape; the cross-check of the tensor-core kernels, as the
+ *             reference checks its fused kernels against the unfused loop)
+ *   UNFUSED : the two-launch kernels (rows grouped by expert) even where the single-launch kernel applies
+ *   ONLY_*  : development only, not part of the ABI contract: run one of the two launches of the two-launch path
+ *             (the output of such a call is not the layer's result) */
+enum { CACHALOT_DECODE_SIMPLE = 0x400, CACHALOT_DECODE_UNFUSED = 0x800 };
 enum { CACHALOT_DECODE_ONLY_GATE_UP = 0x100, CACHALOT_DECODE_ONLY_DOWN = 0x200 };
-/* OR-ed into `numerics`: use the simple one-warp-per-output kernels (any shape; the cross-check of the
- * tensor-core kernels, as the reference checks its fused kernels against the unfused loop) */
-enum { CACHALOT_DECODE_SIMPLE = 0x400 };
-/* OR-ed into `numerics`: use the two-launch tensor-core kernels even where the single-launch kernel applies */
-enum { CACHALOT_DECODE_UNFUSED = 0x800 };
 enum { CACHALOT_ROUTER_SQRT_SOFTPLUS = 0, CACHALOT_ROUTER_SIGMOID = 1 };
 enum { CACHALOT_SCALE_E8M0 = 0, CACHALOT_SCALE_F32 = 1 };
 

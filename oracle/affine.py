@@ -117,3 +117,16 @@ def affine_routed_experts(x, experts, weights, *, bits, group_size, swiglu_limit
         total = total + affine_expert_forward(x, mats, bits=bits, group_size=group_size, weight=w,
                                               swiglu_limit=swiglu_limit, acc=acc)
     return total
+
+
+def affine_routed_experts_plain(x, experts, weights, *, bits, group_size, swiglu_limit=10.0):
+    """The same experts without any of the bf16 rounding points, accumulated in float64: the bound for a kernel
+    run with its rounding points switched off (x is still the bf16 input)."""
+    xv = np.asarray(x, dtype=np.float64)
+    total = np.zeros(xv.shape, dtype=np.float64)
+    for mats, w in zip(experts, np.asarray(weights, dtype=np.float32).reshape(-1)):
+        m = {p: dequantize_affine(mats[f"{p}.weight"], mats[f"{p}.scales"], mats[f"{p}.biases"], bits=bits,
+                                  group_size=group_size).astype(np.float64) for p in ("w1", "w2", "w3")}
+        g, u = m["w1"] @ xv, m["w3"] @ xv
+        total += m["w2"] @ (swiglu(g, u, swiglu_limit) * float(w))
+    return total

@@ -6,7 +6,7 @@ pytestmark = pytest.mark.gpu
 
 torch = pytest.importorskip("torch")
 from oracle import affine, configs, fp4, router  # noqa: E402
-from tests.helpers import bf16_tensor, make_bank, max_rel  # noqa: E402
+from tests.helpers import bf16_tensor, expert_from_bank, make_bank, max_rel  # noqa: E402
 
 TOL = 2e-3  # max relative error of layer outputs against the fp32-accumulated oracle
 
@@ -148,8 +148,9 @@ def test_affine_small_shapes_batch(group, dims):
             h = round_bf16((fp4.swiglu(g, u, 10.0) * w[t, j]).astype(np.float32))
             want[t] += round_bf16((h.astype(np.float64) @ dense(e, "w2", hidden, inter).T.astype(np.float64)).astype(np.float32))
     # bf16 numerics: a value on a rounding boundary may land one bf16 step (2**-8 relative) away from the float64
-    # order of summation, so the bound is the one of the single-launch kernel tests, not the f32-numerics 2e-3
-    assert max_rel(got, want) < 2 ** -7
+    # order of summation: such elements are counted and bounded by one step; all others meet 2e-3
+    err = np.abs(got - want) / np.max(np.abs(want))
+    assert err.max() < 2 ** -7 and np.count_nonzero(err >= TOL) <= max(2, err.size // 64)
 
 
 def test_decode_full_size_properties():
@@ -195,8 +196,7 @@ def test_tensor_core_kernels_equal_simple_kernels(kind, rows):
     hidden, inter, n_slots, k = 4096, 2880, 40, 6
     fmt = cb.FP4_FORMAT if kind == "fp4" else cb.affine_format(hidden, inter)
     bank = cb.SlabBank(fmt, hidden, inter, n_slots)
-    from bench import fill_bank
-    fill_bank(bank, g)
+    bank.fill_random(g)
     x = (torch.randn((rows, hidden), device="cuda", generator=g) * 2).to(torch.bfloat16)
     slots = torch.stack([torch.randperm(n_slots, device="cuda", generator=g)[:k] for _ in range(rows)]).to(torch.int32)
     if rows > 1:
@@ -255,8 +255,13 @@ def test_single_launch_kernel_matches_oracle(kind, dims):
     xs, ws = bf16_tensor(x), torch.from_numpy(w[None]).cuda()
     got = cb.moe_forward(xs, torch.from_numpy(ids[None]).cuda(), ws, bank, status=status).cpu().numpy()[0]
     assert int(status.item()) == 0
-    assert max_rel(got, oracle(np.arange(k))) < tol_op
+    want = oracle(np.arange(k))
+    assert max_rel(got, want) < tol_op
     if kind == "affine":
+        # ... and the elements that did move across a boundary are few, each by one bf16 step of one expert's output
+        moved = int(np.count_nonzero(np.abs(got - want) >= TOL * np.max(np.abs(want))))
+        print(f"affine {dims}: {moved} of {hidden} output elements on the other side of a bf16 boundary")
+        assert moved <= max(2, hidden // 64)
         exact = cb.moe_forward(xs, torch.from_numpy(ids[None]).cuda(), ws, bank, numerics="f32").cpu().numpy()[0]
         assert max_rel(exact, plain_affine(np.arange(k))) < TOL
     two = cb.moe_forward(xs, torch.from_numpy(ids[None]).cuda(), ws, bank, unfused=True).cpu().numpy()[0]
@@ -334,3 +339,56 @@ def test_fp4_scale_window_and_calibration():
     got = cb.moe_forward(bf16_tensor(x), slots, w, bank, swiglu_limit=0.0, status=status, unfused=True).cpu().numpy()
     assert int(status.item()) == 0
     assert max_rel(got, want) < TOL
+
+
+@pytest.mark.parametrize("kind", ["fp4", "affine"])
+@pytest.mark.parametrize("rows", [8, 64])
+def test_config2_batches_at_full_dims_meet_the_oracle(kind, rows):
+    """Batches of 8 and 64 tokens at hidden 4096 / inter 2880, tokens sharing experts (48 slots for up to 384 routed
+    rows): three sampled tokens against the oracle through every kernel family -- whatever cachalot_moe_decode picks,
+    the two-launch kernels that group rows by expert (`unfused`) and the one-warp-per-output kernels (`simple`).
+    FP4 runs in its own numerics (fp32 throughout): 2e-3.  The 2-bit bank is held to 2e-3 with the rounding points
+    off, and with them on (g, u, h and each expert's output through bf16) an output element may land on the other side
+    of a bf16 rounding boundary of one expert's contribution: those elements are counted, and bounded by one step."""
+    import cachalot_b200 as cb
+    hidden, inter, n_slots, k = 4096, 2880, 48, 6
+    g = torch.Generator(device="cuda").manual_seed(100 + rows)
+    fmt = cb.FP4_FORMAT if kind == "fp4" else cb.affine_format(hidden, inter)
+    bank = cb.SlabBank(fmt, hidden, inter, n_slots)
+    bank.fill_random(g)
+    x = torch.randn((rows, hidden), device="cuda", generator=g).to(torch.bfloat16)
+    slots = torch.stack([torch.randperm(n_slots, device="cuda", generator=g)[:k] for _ in range(rows)]).to(torch.int32)
+    slots[rows // 2, 4] = -1                                   # one absent expert among the sampled rows
+    w = torch.rand((rows, k), device="cuda", generator=g) * 0.3 + 0.02
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    outs = {"default": cb.moe_forward(x, slots, w, bank, status=status),
+            "unfused": cb.moe_forward(x, slots, w, bank, status=status, unfused=True),
+            "simple": cb.moe_forward(x, slots, w, bank, status=status, simple=True)}
+    exact = {name: cb.moe_forward(x, slots, w, bank, status=status, numerics="f32", **kw)
+             for name, kw in (("default", {}), ("unfused", {"unfused": True}), ("simple", {"simple": True}))} if kind == "affine" else {}
+    assert int(status.item()) == 0
+    xh, sh, wh = x.float().cpu().numpy(), slots.cpu().numpy(), w.cpu().numpy()
+    cache = {}
+
+    def expert(slot):
+        if slot not in cache:
+            cache[slot] = expert_from_bank(bank, int(slot))
+        return cache[slot]
+
+    for t in (0, rows // 2, rows - 1):
+        sel = [j for j in range(k) if sh[t, j] >= 0]
+        ex, wt = [expert(sh[t, j]) for j in sel], wh[t, sel]
+        if kind == "fp4":
+            want = fp4.routed_topk_forward(xh[t], ex, wt, swiglu_limit=10.0, acc=np.float64)
+            for name, o in outs.items():
+                assert max_rel(o[t].cpu().numpy(), want) < TOL, (name, t)
+            continue
+        want = affine.affine_routed_experts(xh[t], ex, wt, bits=2, group_size=128, swiglu_limit=10.0, acc=np.float64)
+        plain = affine.affine_routed_experts_plain(xh[t], ex, wt, bits=2, group_size=128, swiglu_limit=10.0)
+        ref = float(np.max(np.abs(want)))
+        for name, o in outs.items():
+            err = np.abs(o[t].cpu().numpy().astype(np.float64) - want) / ref
+            outside = int(np.count_nonzero(err >= TOL))
+            print(f"{kind} rows={rows} token {t} {name}: {outside} of {hidden} elements moved across a bf16 boundary, max {err.max():.2e}")
+            assert err.max() < 2 ** -7 and outside <= hidden // 64, (name, t, outside)
+            assert max_rel(exact[name][t].cpu().numpy(), plain) < TOL, (name, t)

@@ -7,7 +7,7 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 from oracle import configs, mxfp4, prefill  # noqa: E402
 from oracle.bf16 import round_bf16  # noqa: E402
-from tests.helpers import bf16_tensor, make_bank, max_rel  # noqa: E402
+from tests.helpers import bf16_tensor, check_prefill_rows, expert_from_bank, make_bank, max_rel  # noqa: E402
 
 TOL = 2e-3
 
@@ -74,12 +74,13 @@ def test_prefill_small_matches_oracle(mx):
     if not mx:
         assert max_rel(got, want) < TOL
         return
-    # The MXFP4 quantiser of the hidden activation is discontinuous: where fp32 and float64
-    # accumulation put a value on different sides of a bf16 or E2M1 rounding boundary, one element
-    # of h moves by a whole E2M1 step and that (token, slot) row of outputs moves with it.  So the
-    # bound is per row: nearly every row inside the tolerance, and no row far outside it.
-    err = np.max(np.abs(got - want), axis=1) / np.max(np.abs(want))
-    assert np.mean(err < TOL) >= 0.9 and err.max() < 5e-2
+    # The MXFP4 quantiser of the hidden activation is discontinuous, so the comparison is made per routed row with
+    # the deviation each element's own boundary cases admit (an element of g or u within rounding noise of a bf16
+    # midpoint, an element of h within it of an E2M1 threshold); everything else must meet the tolerance.
+    xt, it, wt = bf16_tensor(x), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
+    y, perm, offsets, inv = check_prefill_rows(bank, lambda e: experts[e], xt, it, wt, n_experts=n_exp, k=k, tol=TOL)
+    # the whole call is the slot-ordered sum of exactly those rows
+    assert torch.equal(cb.combine_rows(y, inv, tokens, k), torch.from_numpy(got).cuda())
 
 
 def test_prefill_equals_decode_row_by_row():
@@ -98,10 +99,12 @@ def test_prefill_equals_decode_row_by_row():
     assert float((fast - dec).abs().max()) <= 2e-3 * float(dec.abs().max())
 
 
-@pytest.mark.parametrize("tokens,hidden,inter,n_exp", [(48, 256, 192, 16), (300, 512, 320, 12), (64, 1024, 2880 // 5, 40)])
-def test_prefill_tensor_core_path_matches_plain_kernels(tokens, hidden, inter, n_exp):
-    """mxfp4_act=1 (block-scaled FP4 MMAs, weights as the M side) against mxfp4_act=2 (per-row kernels):
-    same codes in, same rounding points, different summation order."""
+@pytest.mark.parametrize("tokens,hidden,inter,n_exp", [(48, 256, 192, 16), (300, 512, 320, 12), (64, 1024, 2880 // 5, 40), (8, 256, 192, 40)])
+def test_prefill_tensor_core_path_matches_oracle_row_by_row(tokens, hidden, inter, n_exp):
+    """mxfp4_act=1 (block-scaled FP4 MMAs, weights as the M side) against the oracle, every routed row, with an absent
+    expert; the last case has more experts than routed rows (a short chunk of layer-major prefill).  The per-row
+    kernels (mxfp4_act=2: the same arithmetic in a fixed summation order) must agree with the same sum to the bound
+    that rounding-boundary cases allow."""
     import cachalot_b200 as cb
     k = 6
     x, ids, w, experts = configs.config3(seed=5, tokens=tokens, hidden=hidden, inter=inter, n_experts=n_exp, k=k,
@@ -109,12 +112,14 @@ def test_prefill_tensor_core_path_matches_plain_kernels(tokens, hidden, inter, n
     bank = make_bank([experts[e] for e in range(n_exp)], cb.FP4_FORMAT, hidden, inter)
     bank.slot_table[0, 3] = -1  # an absent expert contributes zeros on both paths
     xt, it, wt = bf16_tensor(x), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
+    y, perm, offsets, inv = check_prefill_rows(bank, lambda e: experts[e], xt, it, wt, n_experts=n_exp, k=k, tol=TOL)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     tc = cb.moe_prefill_grouped(xt, it, wt, bank, mxfp4_act=1, status=status)
-    plain = cb.moe_prefill_grouped(xt, it, wt, bank, mxfp4_act=2)
     assert int(status.item()) == 0
+    assert torch.equal(tc, cb.combine_rows(y, inv, tokens, k))
+    plain = cb.moe_prefill_grouped(xt, it, wt, bank, mxfp4_act=2)
     err = (tc - plain).abs().amax(dim=1) / plain.abs().max()
-    assert float((err < TOL).float().mean()) >= 0.9 and float(err.max()) < 5e-2
+    assert float(err.max()) < 5e-2   # a cross-check only: the rows above are held to the oracle
 
 
 def test_prefill_rows_and_combine_equal_the_whole_call():
@@ -184,7 +189,8 @@ def test_expert_parallel_prefill_on_two_gpus_equals_one_gpu():
 
 def test_prefill_tensor_core_path_at_full_layer_dims():
     """hidden 4096, inter 2880 (partial last 128-row tile, K tail of the down projection, scale rows of 90 bytes):
-    block-scaled MMAs against the per-row kernels on the same grouping; one expert has more rows than a unit holds."""
+    routed rows against the oracle, sampled where the tiling has its edges: the first and last row of every expert
+    and both sides of every 96-row unit boundary (one expert has more rows than a unit holds)."""
     import cachalot_b200 as cb
     tokens, hidden, inter, n_exp, k = 160, 4096, 2880, 8, 6
     rng = np.random.default_rng(11)
@@ -194,12 +200,55 @@ def test_prefill_tensor_core_path_at_full_layer_dims():
     ids = np.stack([rng.permutation(n_exp)[:k] for _ in range(tokens)]).astype(np.int32)   # ~120 rows per expert
     w = rng.uniform(0.05, 0.3, (tokens, k)).astype(np.float32)
     it, wt = torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
+    counts = np.bincount(ids.reshape(-1), minlength=n_exp)
+    starts = np.concatenate([[0], np.cumsum(counts)])
+    sample = []
+    for e in range(n_exp):
+        sample += [starts[e], starts[e + 1] - 1]
+        sample += [starts[e] + p for p in (95, 96, 97) if p < counts[e]]
+        sample += [starts[e] + int(p) for p in rng.integers(0, counts[e], 2)]
+    y, perm, offsets, inv = check_prefill_rows(bank, lambda e: expert_from_bank(bank, e), x, it, wt, n_experts=n_exp, k=k,
+                                               sample=sample, tol=TOL)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     tc = cb.moe_prefill_grouped(x, it, wt, bank, mxfp4_act=1, status=status)
-    plain = cb.moe_prefill_grouped(x, it, wt, bank, mxfp4_act=2)
     assert int(status.item()) == 0
+    assert torch.equal(tc, cb.combine_rows(y, inv, tokens, k))
+    plain = cb.moe_prefill_grouped(x, it, wt, bank, mxfp4_act=2)
     err = (tc - plain).abs().amax(dim=1) / plain.abs().max()
-    assert float((err < TOL).float().mean()) >= 0.9 and float(err.max()) < 5e-2
+    assert float(err.max()) < 5e-2
+
+
+def test_config3_full_size_sampled_rows_match_oracle():
+    """Config 3 itself: 4096 tokens, 384 experts, Zipf(1.1) popularity, hidden 4096, inter 2880.  The whole call
+    equals the slot-ordered sum of the rows-level outputs bit for bit, and sampled routed rows (all six rows of
+    four tokens; the edges of the heaviest expert's 96-row units; the lightest experts) meet the oracle."""
+    import cachalot_b200 as cb
+    tokens, hidden, inter, n_exp, k = 4096, 4096, 2880, 384, 6
+    rng = np.random.default_rng(0)
+    ids, w = configs.zipf_routing(rng, tokens, n_exp, k)
+    x = bf16_tensor(round_bf16(rng.standard_normal((tokens, hidden)).astype(np.float32)))
+    bank = cb.SlabBank(cb.FP4_FORMAT, hidden, inter, n_exp)
+    bank.fill_random(torch.Generator(device="cuda").manual_seed(7))
+    it, wt = torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
+    flat = ids.reshape(-1)
+    counts = np.bincount(flat, minlength=n_exp)
+    starts = np.concatenate([[0], np.cumsum(counts)])
+    order = np.argsort(flat, kind="stable")
+    where = np.empty_like(order)
+    where[order] = np.arange(order.size)             # grouped position of routed row (token*k + slot)
+    sample = [int(where[t * k + j]) for t in (0, 1777, 4095) for j in range(k)]
+    heavy = int(np.argmax(counts))
+    sample += [int(starts[heavy] + p) for p in (0, 95, 96, 191, 192, counts[heavy] - 1)]
+    for e in np.argsort(counts)[:3]:
+        if counts[e]:
+            sample.append(int(starts[e]))
+    y, perm, offsets, inv = check_prefill_rows(bank, lambda e: expert_from_bank(bank, e), x, it, wt, n_experts=n_exp, k=k,
+                                               sample=sample, tol=TOL)
+    assert np.array_equal(perm.cpu().numpy(), order)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    whole = cb.moe_prefill_grouped(x, it, wt, bank, mxfp4_act=1, status=status)
+    assert int(status.item()) == 0
+    assert torch.equal(whole, cb.combine_rows(y, inv, tokens, k))
 
 
 @pytest.mark.parametrize("case", ["one_token", "one_expert_many_rows", "all_absent", "k1", "empty"])
@@ -231,4 +280,6 @@ def test_prefill_tensor_core_path_edges(case):
         assert float(tc.abs().max()) == 0.0 and float(plain.abs().max()) == 0.0
         return
     err = (tc - plain).abs().amax(dim=1) / plain.abs().max()
-    assert float((err < TOL).float().mean()) >= 0.9 and float(err.max()) < 5e-2
+    assert float(err.max()) < 5e-2
+    y, perm, offsets, inv = check_prefill_rows(bank, lambda e: experts[e], xt, it, wt, n_experts=n_exp, k=k, tol=TOL, max_exempt=0.5)
+    assert torch.equal(tc, cb.combine_rows(y, inv, tokens, k))
