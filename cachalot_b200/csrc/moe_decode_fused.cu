@@ -30,6 +30,7 @@
 //                acc += s * 2**-e * (256*T_hi + T_lo) + b * sum(x).
 //   FP4 bank   : E2M1 byte -> f16x2 (cvt.rn.f16x2.e2m1x2), HMMA m16n8k16 with f16 activations
 //                scaled per sub-block by 2**e;  acc += 2**(scale-127) * 2**-e * T.
+#include <cstdlib>
 #include <mutex>
 #include <set>
 #include <utility>
@@ -417,28 +418,6 @@ __device__ __forceinline__ float2 unit_dot(const uint8_t* stage, const Geo& G, c
   return make_float2(accA, accB);
 }
 
-// One round of a warp-wide selection over up to three (order key, expert id) entries per lane: returns the id of
-// the best entry (larger key first; equal keys: the lower id when low_wins, else the higher id) and clears that
-// entry (key 0 = taken or absent), or -1 when nothing is left.  All lanes get the same answer.
-__device__ __forceinline__ int warp_arg_best(uint32_t (&ord)[3], int (&id)[3], bool low_wins) {
-  uint32_t bo = 0u;
-  int bi = -1;
-#pragma unroll
-  for (int i = 0; i < 3; ++i) {
-    const bool better = ord[i] > bo || (ord[i] == bo && ord[i] != 0u && (low_wins ? id[i] < bi : id[i] > bi));
-    if (better) bo = ord[i], bi = id[i];
-  }
-  const uint32_t wo = __reduce_max_sync(0xffffffffu, bo);
-  if (wo == 0u) return -1;
-  const bool cand = bo == wo;
-  const int win = low_wins ? (int)__reduce_min_sync(0xffffffffu, cand ? (unsigned)bi : 0x7fffffffu)
-                           : (int)__reduce_max_sync(0xffffffffu, cand ? (unsigned)(bi + 1) : 0u) - 1;
-#pragma unroll
-  for (int i = 0; i < 3; ++i)
-    if (id[i] == win) ord[i] = 0u;
-  return win;
-}
-
 template <int FMT, int SDT, typename OutT>
 __global__ void __launch_bounds__(Fm<FMT>::NTHREADS, 1)
 fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ slots,
@@ -462,6 +441,10 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int H = bank.hidden, I = bank.inter;
   int err = 0;
+  // Under programmatic dependent launch the next kernel of the stream may be set up while this one runs (it cannot
+  // become resident before this CTA leaves: a CTA fills the SM).  Until griddepcontrol.wait returns, only shared
+  // memory is touched: the inputs may still be in the making by the previous kernel.  Both are no-ops otherwise.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x < 128) reinterpret_cast<uint32_t*>(smem + G.off_bar + 512)[threadIdx.x] = 0u;
   if (threadIdx.x == 0) {
     for (int s = 0; s < 16; ++s) {
@@ -470,6 +453,7 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // consumers fetch their part of x before anything else (up to XB 16-element blocks per thread)
   constexpr int XB = 3;
@@ -491,10 +475,6 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
   uint32_t* r_ord = reinterpret_cast<uint32_t*>(smem + G.off_act + G.act_stride[0]);  // scratch behind x in the operand area
   float* r_score = reinterpret_cast<float*>(r_ord + 1024);
   int32_t* r_slot = reinterpret_cast<int32_t*>(r_ord + 2048);
-  uint32_t* c_ord = r_ord + 3072;                           // [warps][KMAX] every warp's k best: order key ...
-  int32_t* c_id = reinterpret_cast<int32_t*>(r_ord + 3200);  // ... and expert id (-1: none)
-  constexpr int NW = Fm<FMT>::NTHREADS / 32;
-  const bool low_wins = R.mode == CACHALOT_ROUTER_SIGMOID;  // ties: the sigmoid router prefers the lower index
   if (R.logits) {
     for (int e = threadIdx.x; e < R.n_experts; e += blockDim.x) {
       // the three loads are independent: one round trip to L2 for the whole routing tail
@@ -509,42 +489,37 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
       r_score[e] = sc, r_slot[e] = sl;
     }
     __syncthreads();
-    // first every warp picks the k best of its own span of experts (up to three per lane), then warp 0 picks
-    // the k best of the warps' candidates: the selection is a handful of warp reductions instead of k passes
-    // of one warp over all experts
-    const int span = (R.n_experts + NW - 1) / NW;
-    uint32_t ord[3];
-    int id[3];
-#pragma unroll
-    for (int i = 0; i < 3; ++i) {
-      const int off = i * 32 + lane, e = warp * span + off;
-      const bool ok = off < span && e < R.n_experts;
-      ord[i] = ok ? r_ord[e] : 0u, id[i] = ok ? e : -1;
-    }
-    for (int r = 0; r < KMAX; ++r) {
-      const int win = r < k ? warp_arg_best(ord, id, low_wins) : -1;
-      if (lane == 0) c_id[warp * KMAX + r] = win, c_ord[warp * KMAX + r] = win >= 0 ? r_ord[win] : 0u;
-    }
-    __syncthreads();
   }
   // warp 0: the present experts in routing order
   if (warp == 0) {
     int my_slot = -1;
     float my_w = 0.f;
     if (R.logits) {
-      // a taken candidate's order drops to 0 (below every real one)
+      // k rounds of a warp-wide arg-best.  Lane l keeps experts l, l + 32, ... in registers; a taken expert's
+      // order drops to 0 (below every real one).  Ties: the sigmoid router prefers the lower index, the other
+      // the larger one, as route_topk_kernel does.
+      const bool low_wins = R.mode == CACHALOT_ROUTER_SIGMOID;
       const bool ascending = !low_wins;  // the sqrt-softplus router writes the weakest first
-      uint32_t ord[3];
-      int id[3];
+      uint32_t ord[32];
 #pragma unroll
-      for (int i = 0; i < 3; ++i) {
-        const int c = i * 32 + lane;
-        ord[i] = c < NW * KMAX ? c_ord[c] : 0u, id[i] = c < NW * KMAX ? c_id[c] : -1;
-      }
+      for (int i = 0; i < 32; ++i) ord[i] = (i * 32 + lane < R.n_experts) ? r_ord[i * 32 + lane] : 0u;
       int my_e = -1;
       for (int r = 0; r < k; ++r) {
-        const int win = warp_arg_best(ord, id, low_wins);
-        if (win < 0) break;  // fewer than k experts
+        uint32_t bo = 0u;
+        int bi = -1;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const bool better = low_wins ? ord[i] > bo : (ord[i] >= bo && ord[i] != 0u);
+          if (better) bo = ord[i], bi = i * 32 + lane;
+        }
+        const uint32_t wo = __reduce_max_sync(0xffffffffu, bo);
+        const bool cand = bo == wo && bi >= 0;
+        const int win = low_wins ? (int)__reduce_min_sync(0xffffffffu, cand ? (unsigned)bi : 0x7fffffffu)
+                                 : (int)__reduce_max_sync(0xffffffffu, cand ? (unsigned)(bi + 1) : 0u) - 1;
+        if (wo == 0u) break;  // fewer than k experts
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i * 32 + lane == win) ord[i] = 0u;
         if (lane == (ascending ? k - 1 - r : r)) my_e = win;
       }
       // lane r holds output position r; the total is added up in output order as route_topk_kernel does
@@ -963,11 +938,15 @@ static int launch_fused_fmt(const BankView& v, const Geo& G, const RouteArgs& R,
   cfg.dynamicSmemBytes = (size_t)(SMEM_LIMIT - 256);
   (void)G.total;
   cfg.stream = stream;
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident: the grid barrier cannot starve
   at[0].val.cooperative = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // the prologue may overlap the previous kernel's tail
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  // on unless CACHALOT_PDL=0 is set (the switch exists to time the difference: about 0.9 us per layer)
+  static const bool pdl = [] { const char* e = std::getenv("CACHALOT_PDL"); return !(e && e[0] == '0'); }();
   cfg.attrs = at;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl ? 2 : 1;
   cudaError_t e = cudaSuccess;
   auto go = [&](auto kern, auto* outp) {
     // the opt-in is an attribute of a kernel on a device: set once for each (the pointer types of different
@@ -1015,7 +994,7 @@ int launch_layer_fused(const BankView& v, const void* x, const float* logits, co
                        int32_t* indices_out, float* weights_out, int* status, cudaStream_t stream) {
   Geo G;
   if (!make_geo(v, k, &G) || n_experts > 1024) return CACHALOT_EUNSUPPORTED;
-  if (G.act_stride[1] * k < G.act_stride[0] + 13312) return CACHALOT_EUNSUPPORTED;  // the routing scratch sits behind x in the operand area
+  if (G.act_stride[1] * k < G.act_stride[0] + 12288) return CACHALOT_EUNSUPPORTED;  // the routing scratch sits behind x in the operand area
   const int numerics = numerics_flags & 0xff;
   RouteArgs R = {};
   R.logits = logits, R.bias = bias, R.slot_table = slot_table, R.indices_out = indices_out, R.weights_out = weights_out;
@@ -1030,7 +1009,7 @@ bool layer_fused_supported(const BankView& v, int n_experts, int k) {
   Geo G;
   if (k < 1 || k > KMAX || n_experts < k || n_experts > 1024) return false;
   if (v.format == CACHALOT_BANK_AFFINE && (v.group != 128 || v.bits != 2)) return false;
-  return make_geo(v, k, &G) && G.act_stride[1] * k >= G.act_stride[0] + 13312;
+  return make_geo(v, k, &G) && G.act_stride[1] * k >= G.act_stride[0] + 12288;
 }
 
 }  // namespace cachalot
