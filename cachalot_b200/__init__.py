@@ -13,7 +13,9 @@ _OPS = (
     "fp8_linear", "fp8_linear_quantized", "fused_routed_experts", "group_rows", "moe_forward", "moe_layer_decode",
     "combine_rows", "moe_prefill_grouped", "moe_prefill_rows",
     "quantize_fp8_activation", "quantize_mxfp4", "route_tail", "route_topk", "route_topk_fused", "route_topk_rows",
-    "routed_expert_forward", "router_logits",
+    "routed_expert_forward", "router_logits", "routed_expert_forward_batched", "routed_expert_forward_sgmm",
+    "affine_expert_forward_batched", "SlabExperts", "shared_expert_forward", "shared_expert_forward_fused",
+    "shared_expert_forward_batched", "fp8_linear_rows", "fused_qr_kv_linear", "moe_layer_forward",
 )
 __all__ = [*_BANK, *_OPS, "NUMERICS_VERSION"]
 

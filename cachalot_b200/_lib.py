@@ -39,6 +39,12 @@ class BankDesc(C.Structure):
     ]
 
 
+class PeerCtx(C.Structure):
+    """Mirror of `cachalot_peer_ctx`."""
+
+    _fields_ = [("inbox", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("epoch", C.c_void_p), ("world", C.c_int32), ("rank", C.c_int32)]
+
+
 _vp, _i, _f, _sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
 _desc = C.POINTER(BankDesc)
 
@@ -59,6 +65,8 @@ SIGNATURES = {
     "cachalot_moe_decode_static": (_i, [_vp, _desc, _vp, _vp, _vp, _i, _i, _f, _i, _vp, _i, _vp, _vp]),
     "cachalot_fp8_act_quant": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp]),
     "cachalot_fp8_gemv": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
+    "cachalot_shared_expert_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "cachalot_shared_expert": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp, _vp, _sz, _vp, _vp]),
     "cachalot_group_rows_scratch_ints": (_sz, [_i, _i, _i]),
     "cachalot_group_rows": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "cachalot_mxfp4_act_quant": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp]),
@@ -69,6 +77,10 @@ SIGNATURES = {
     "cachalot_peer_sum_inbox_bytes": (_sz, [_i, _i]),
     "cachalot_peer_sum_flag_bytes": (_sz, [_i]),
     "cachalot_peer_sum": (_i, [_vp, _vp, _i, _i, _vp, _vp, _i, _vp, _vp, _vp]),
+    "cachalot_peer_layer_inbox_bytes": (_sz, [_i, _i]),
+    "cachalot_peer_layer_flag_bytes": (_sz, [_i]),
+    "cachalot_moe_layer_decode_peer": (_i, [_vp, _desc, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _i, _i, _f, _i, _vp, _sz, _vp, _i,
+                                            _vp, _vp, _vp, _vp, _vp]),
     "cachalot_moe_prefill": (_i, [_vp, _desc, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp, _sz, _vp, _vp, _vp]),
 }
 

@@ -40,6 +40,41 @@ __global__ void act_quant_kernel(const __nv_bfloat16* __restrict__ x, int rows, 
   if (lane == 0) scales[warp] = scale;
 }
 
+// SwiGLU of the shared expert fused with the act_quant of its result (model/shared_expert_metal.py:165-180):
+// gate, up bf16 -> f32; up = clip(up, +-L), gate = min(gate, L) when L > 0; h = silu(gate) * up -> bf16 (the
+// activation dtype) -> act_quant per block.  One warp per (row, block), as act_quant_kernel.
+template <int PER>
+__global__ void swiglu_act_quant_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up, long long ld,
+                                        int rows, int k, int scale_rule, float limit, uint8_t* __restrict__ codes,
+                                        float* __restrict__ scales) {
+  constexpr int BLOCK = 32 * PER;
+  const int nblk = k / BLOCK;
+  long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= (long long)rows * nblk) return;
+  const long long row = warp / nblk;
+  const int col = (int)(warp - row * nblk) * BLOCK + lane * PER;
+  float v[PER];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    float g = __bfloat162float(gate[row * ld + col + i]), u = __bfloat162float(up[row * ld + col + i]);
+    v[i] = bf16_round(swiglu(g, u, limit));
+    amax = fmaxf(amax, fabsf(v[i]));
+  }
+  amax = fmaxf(warp_max(amax), 1e-4f);
+  float raw = __fdiv_rn(amax, 448.0f);
+  float scale = raw;
+  if (scale_rule == CACHALOT_SCALE_E8M0) scale = __uint_as_float((uint32_t)(ceil_log2(raw) + 127) << 23);
+  const size_t base = (size_t)row * k + col;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    float q = fminf(fmaxf(__fdiv_rn(v[i], scale), -448.0f), 448.0f);
+    codes[base + i] = (uint8_t)__nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3);
+  }
+  if (lane == 0) scales[warp] = scale;
+}
+
 // ---- GEMV on the tensor cores -------------------------------------------------------------------
 // Both operands are E4M3 codes, so the products can be formed by mma.sync.m16n8k32.e4m3 (exact in
 // fp32) without decoding anything: weight bytes go from global memory straight into the A operand.
@@ -68,7 +103,7 @@ template <int NTG, int BLOCK, int KS, int RT, typename OutT>
 __global__ void __launch_bounds__(KS * 32)
 fp8_gemv_mma_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ act_scales,
                     const uint8_t* __restrict__ weight, const void* __restrict__ w_scales, int scale_rule, int rows,
-                    int n_out, int k, OutT* __restrict__ out) {
+                    int n_out, int k, OutT* __restrict__ out, long long ldo, const float* __restrict__ addend) {
   constexpr int MPB = BLOCK / 32;  // MMAs per scale block
   constexpr int UNR = BLOCK == 32 ? 8 / RT : 2;  // scale blocks in flight: about sixteen 8-byte weight loads per lane
   __shared__ float red[KS][RT][NTG][4][32];
@@ -161,10 +196,13 @@ fp8_gemv_mma_kernel(const uint8_t* __restrict__ codes, const float* __restrict__
       for (int w = 1; w < KS; ++w) v += red[w][rt][tg][i][lane];
       const int tok = tg * 8 + 2 * t + (i & 1), row = n0 + rt * 16 + g + (i >> 1) * 8;
       if (tok < rows && row < n_out) {
+        // with an addend the linear's own result is rounded to bf16 first (it is a bf16 tensor in the reference),
+        // then added in fp32: (routed + shared.astype(f32)).astype(bf16) of model/moe_layer_metal.py:394-403
+        if (addend) v = bf16_round(v) + addend[(size_t)tok * n_out + row];
         if constexpr (sizeof(OutT) == 2)
-          out[(size_t)tok * n_out + row] = __float2bfloat16_rn(v);
+          out[(size_t)tok * ldo + row] = __float2bfloat16_rn(v);
         else
-          out[(size_t)tok * n_out + row] = v;
+          out[(size_t)tok * ldo + row] = v;
       }
     }
   }
@@ -172,7 +210,8 @@ fp8_gemv_mma_kernel(const uint8_t* __restrict__ codes, const float* __restrict__
 
 template <int BLOCK, typename OutT>
 static void launch_gemv_mma(int ntg, cudaStream_t s, const uint8_t* codes, const float* act_scales, const uint8_t* weight,
-                            const void* w_scales, int scale_rule, int rows, int n, int k, OutT* out) {
+                            const void* w_scales, int scale_rule, int rows, int n, int k, OutT* out, long long ldo,
+                            const float* addend) {
   // warps per CTA: about twelve warps per SM in total (the reduction buffer limits it for many tokens)
   int sms = 148, dev = 0;
   cudaGetDevice(&dev);
@@ -184,7 +223,7 @@ static void launch_gemv_mma(int ntg, cudaStream_t s, const uint8_t* codes, const
   if (tiles * 4 < 12LL * sms && ntg <= 4) ks = 8;
   if (tiles * 8 < 12LL * sms && ntg <= 2) ks = 16;
 #define CACHALOT_GEMV(NTGV, KSV, RTV) \
-  fp8_gemv_mma_kernel<NTGV, BLOCK, KSV, RTV, OutT><<<grid, KSV * 32, 0, s>>>(codes, act_scales, weight, w_scales, scale_rule, rows, n, k, out)
+  fp8_gemv_mma_kernel<NTGV, BLOCK, KSV, RTV, OutT><<<grid, KSV * 32, 0, s>>>(codes, act_scales, weight, w_scales, scale_rule, rows, n, k, out, ldo, addend)
   if (ntg == 1) {
     if (ks == 16) CACHALOT_GEMV(1, 16, 1); else if (ks == 8) CACHALOT_GEMV(1, 8, 1); else CACHALOT_GEMV(1, 4, 1);
   } else if (ntg == 2) {
@@ -218,32 +257,91 @@ extern "C" int cachalot_fp8_act_quant(const void* x_bf16, int rows, int k, int b
   return check_launch("fp8_act_quant");
 }
 
-extern "C" int cachalot_fp8_gemv(const uint8_t* codes, const float* act_scales, const uint8_t* weight,
-                                 const void* w_scales, int scale_rule, int block, int rows, int n, int k, void* out,
-                                 int out_dtype, cachalot_stream_t stream) {
-  if (!codes || !act_scales || !weight || !w_scales || !out) return fail(CACHALOT_EINVAL, "fp8_gemv: null pointer");
-  if (block != 32 && block != 128) return fail(CACHALOT_EUNSUPPORTED, "fp8_gemv: block=%d (32 or 128)", block);
+static int gemv_checked(const char* who, const uint8_t* codes, const float* act_scales, const uint8_t* weight, const void* w_scales,
+                        int scale_rule, int block, int rows, int n, int k, void* out, int out_dtype, long long ldo,
+                        const float* addend, cudaStream_t s) {
+  if (!codes || !act_scales || !weight || !w_scales || !out) return fail(CACHALOT_EINVAL, "%s: null pointer", who);
+  if (block != 32 && block != 128) return fail(CACHALOT_EUNSUPPORTED, "%s: block=%d (32 or 128)", who, block);
   if (rows < 0 || n <= 0 || k <= 0 || k % block) return fail(CACHALOT_EINVAL, "K=%d is not divisible by %d", k, block);
-  if (scale_rule != CACHALOT_SCALE_E8M0 && scale_rule != CACHALOT_SCALE_F32) return fail(CACHALOT_EINVAL, "fp8_gemv: unknown scale rule");
-  if (out_dtype != CACHALOT_BF16 && out_dtype != CACHALOT_F32) return fail(CACHALOT_EINVAL, "fp8_gemv: out dtype must be bf16 or f32");
-  if (!aligned(weight, 8) || !aligned(codes, 8) || k % 8) return fail(CACHALOT_EALIGN, "fp8_gemv: weight and codes need 8-byte alignment");
+  if (scale_rule != CACHALOT_SCALE_E8M0 && scale_rule != CACHALOT_SCALE_F32) return fail(CACHALOT_EINVAL, "%s: unknown scale rule", who);
+  if (out_dtype != CACHALOT_BF16 && out_dtype != CACHALOT_F32) return fail(CACHALOT_EINVAL, "%s: out dtype must be bf16 or f32", who);
+  if (!aligned(weight, 8) || !aligned(codes, 8) || k % 8) return fail(CACHALOT_EALIGN, "%s: weight and codes need 8-byte alignment", who);
+  if (ldo < n) return fail(CACHALOT_EINVAL, "%s: output row pitch %lld < %d", who, ldo, n);
   if (rows == 0) return CACHALOT_OK;
-  cudaStream_t s = (cudaStream_t)stream;
   // 64 tokens per launch; more tokens take more launches over the same weights
   for (int r0 = 0; r0 < rows; r0 += 8 * GEMV_MAX_TG) {
     const int nr = rows - r0 < 8 * GEMV_MAX_TG ? rows - r0 : 8 * GEMV_MAX_TG;
     const int ntg = (nr + 7) / 8;
     const uint8_t* c = codes + (size_t)r0 * k;
     const float* as = act_scales + (size_t)r0 * (k / block);
+    const float* ad = addend ? addend + (size_t)r0 * n : nullptr;
     if (out_dtype == CACHALOT_BF16) {
-      __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)r0 * n;
-      if (block == 32) launch_gemv_mma<32>(ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
-      else launch_gemv_mma<128>(ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
+      __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)r0 * ldo;
+      if (block == 32) launch_gemv_mma<32>(ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o, ldo, ad);
+      else launch_gemv_mma<128>(ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o, ldo, ad);
     } else {
-      float* o = (float*)out + (size_t)r0 * n;
-      if (block == 32) launch_gemv_mma<32>(ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
-      else launch_gemv_mma<128>(ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o);
+      float* o = (float*)out + (size_t)r0 * ldo;
+      if (block == 32) launch_gemv_mma<32>(ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o, ldo, ad);
+      else launch_gemv_mma<128>(ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o, ldo, ad);
     }
   }
-  return check_launch("fp8_gemv");
+  return check_launch(who);
+}
+
+extern "C" int cachalot_fp8_gemv(const uint8_t* codes, const float* act_scales, const uint8_t* weight,
+                                 const void* w_scales, int scale_rule, int block, int rows, int n, int k, void* out,
+                                 int out_dtype, cachalot_stream_t stream) {
+  return gemv_checked("fp8_gemv", codes, act_scales, weight, w_scales, scale_rule, block, rows, n, k, out, out_dtype, n, nullptr,
+                      (cudaStream_t)stream);
+}
+
+static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+extern "C" size_t cachalot_shared_expert_workspace_bytes(int rows, int hidden, int inter, int block) {
+  if (rows <= 0 || hidden <= 0 || inter <= 0 || block <= 0) return 0;
+  const size_t kmax = (size_t)(hidden > inter ? hidden : inter);
+  // codes and scales of the larger of the two activations (x, then h in the same place), gate|up as bf16
+  return align256((size_t)rows * kmax) + align256((size_t)rows * (kmax / block + 1) * 4) + align256((size_t)rows * 2 * inter * 2);
+}
+
+extern "C" int cachalot_shared_expert(const void* x_bf16, int rows, int hidden, int inter, const uint8_t* w1,
+                                      const void* w1_scales, const uint8_t* w3, const void* w3_scales, const uint8_t* w2,
+                                      const void* w2_scales, int scale_rule, int block, float swiglu_limit,
+                                      const float* addend, void* workspace, size_t workspace_bytes, void* out_bf16,
+                                      cachalot_stream_t stream) {
+  if (!x_bf16 || !w1 || !w1_scales || !w2 || !w2_scales || !out_bf16) return fail(CACHALOT_EINVAL, "shared_expert: null pointer");
+  if (w3 && !w3_scales) return fail(CACHALOT_EINVAL, "shared_expert: w3 without scales");
+  if (rows < 0 || hidden <= 0 || inter <= 0) return fail(CACHALOT_EINVAL, "shared_expert: bad shape");
+  if (block != 32 && block != 128) return fail(CACHALOT_EUNSUPPORTED, "shared_expert: block=%d (32 or 128)", block);
+  if (hidden % block || inter % block) return fail(CACHALOT_EINVAL, "shared_expert: hidden %d and inter %d must be multiples of the block %d", hidden, inter, block);
+  if (rows == 0) return CACHALOT_OK;
+  const size_t need = cachalot_shared_expert_workspace_bytes(rows, hidden, inter, block);
+  if (!workspace || workspace_bytes < need) return fail(CACHALOT_ESCRATCH, "shared_expert: workspace %zu < %zu bytes", workspace_bytes, need);
+  if (!aligned(workspace, 256)) return fail(CACHALOT_EALIGN, "shared_expert: workspace must be 256-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t kmax = (size_t)(hidden > inter ? hidden : inter);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  uint8_t* codes = ws;
+  float* scales = reinterpret_cast<float*>(ws + align256((size_t)rows * kmax));
+  __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(ws + align256((size_t)rows * kmax) + align256((size_t)rows * (kmax / block + 1) * 4));
+  // one act_quant for both projections (model/shared_expert_metal.py:94-107, 160-163)
+  int rc = cachalot_fp8_act_quant(x_bf16, rows, hidden, block, scale_rule, codes, scales, stream);
+  if (rc) return rc;
+  const long long ld = 2LL * inter;
+  if (w3) {
+    rc = gemv_checked("shared_expert w1", codes, scales, w1, w1_scales, scale_rule, block, rows, inter, hidden, gu, CACHALOT_BF16, ld, nullptr, s);
+    if (rc) return rc;
+    rc = gemv_checked("shared_expert w3", codes, scales, w3, w3_scales, scale_rule, block, rows, inter, hidden, gu + inter, CACHALOT_BF16, ld, nullptr, s);
+  } else {  // w1 holds [2*inter, hidden] = w1 rows, then w3 rows
+    rc = gemv_checked("shared_expert w13", codes, scales, w1, w1_scales, scale_rule, block, rows, 2 * inter, hidden, gu, CACHALOT_BF16, ld, nullptr, s);
+  }
+  if (rc) return rc;
+  {
+    const long long warps = (long long)rows * (inter / block);
+    const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+    if (block == 32) swiglu_act_quant_kernel<1><<<blocks, 256, 0, s>>>(gu, gu + inter, ld, rows, inter, scale_rule, swiglu_limit, codes, scales);
+    else swiglu_act_quant_kernel<4><<<blocks, 256, 0, s>>>(gu, gu + inter, ld, rows, inter, scale_rule, swiglu_limit, codes, scales);
+    if ((rc = check_launch("shared_expert swiglu"))) return rc;
+  }
+  return gemv_checked("shared_expert w2", codes, scales, w2, w2_scales, scale_rule, block, rows, hidden, inter, out_bf16, CACHALOT_BF16, hidden, addend, s);
 }

@@ -49,6 +49,18 @@ size_t decode_mma_workspace_bytes(int hidden, int inter, int rows, int k);
 bool decode_mma_supported(const BankView& v, int rows, int k);
 
 
+// Expert-parallel exchange done in the tail of the single-launch decode kernel: every rank's inbox (f32
+// [2 slots][world][hidden]) and flag array (u32 [2 slots][world][PEER_LINK_CTAS]) as mapped in this process, the
+// device-resident exchange counter, and this rank.  world == 0: no exchange.
+constexpr int PEER_LINK_MAX = 8;
+constexpr int PEER_LINK_CTAS = 256;
+struct PeerLink {
+  float* inbox[PEER_LINK_MAX];
+  uint32_t* flags[PEER_LINK_MAX];
+  uint32_t* epoch;  // u32 [2]: exchanges done, arrival ticket
+  int world, rank;
+};
+
 // Single-launch decode for one token (moe_decode_fused.cu).  Same contract as launch_decode_mma.
 int launch_decode_fused(const BankView& v, const void* x, const int32_t* slots, const float* gate_w, int rows, int k,
                         float limit, int numerics_flags, void* workspace, void* out, int out_dtype, int* status,
@@ -59,7 +71,8 @@ bool decode_fused_supported(const BankView& v, int rows, int k);
 int launch_layer_fused(const BankView& v, const void* x, const float* logits, const float* bias, const int32_t* slot_table,
                        int layer, int n_experts, int k, int mode, float gate_temp, float route_scale, int norm,
                        int weights_bf16, float limit, int numerics_flags, void* workspace, void* out, int out_dtype,
-                       int32_t* indices_out, float* weights_out, int* status, cudaStream_t stream);
+                       int32_t* indices_out, float* weights_out, int* status, cudaStream_t stream,
+                       const PeerLink* peer = nullptr);
 bool layer_fused_supported(const BankView& v, int n_experts, int k);
 
 

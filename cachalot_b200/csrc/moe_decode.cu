@@ -362,6 +362,49 @@ extern "C" int cachalot_moe_layer_decode(const void* bank, const cachalot_bank_d
                              status, stream);
 }
 
+extern "C" size_t cachalot_peer_layer_inbox_bytes(int world, int hidden) { return (size_t)2 * world * hidden * sizeof(float); }
+extern "C" size_t cachalot_peer_layer_flag_bytes(int world) { return (size_t)2 * world * PEER_LINK_CTAS * sizeof(uint32_t); }
+
+extern "C" int cachalot_moe_layer_decode_peer(const void* bank, const cachalot_bank_desc* desc, const void* x_bf16,
+                                              const float* logits, const float* bias, const int32_t* slot_table, int layer,
+                                              int n_experts, int k, int mode, float gate_temp, float route_scale,
+                                              int norm_topk_prob, int weights_bf16, float swiglu_limit, int numerics,
+                                              void* workspace, size_t workspace_bytes, void* out, int out_dtype,
+                                              int32_t* indices_out, float* weights_out, const cachalot_peer_ctx* peer,
+                                              int* status, cachalot_stream_t stream) {
+  BankView v;
+  int rc = make_view(bank, desc, &v, "moe_layer_decode_peer");
+  if (rc) return rc;
+  if (!x_bf16 || !logits || !out || !peer) return fail(CACHALOT_EINVAL, "moe_layer_decode_peer: null pointer");
+  if (peer->world < 1 || peer->world > PEER_LINK_MAX || peer->rank < 0 || peer->rank >= peer->world || !peer->epoch)
+    return fail(CACHALOT_EINVAL, "moe_layer_decode_peer: world %d (1..%d), rank %d", peer->world, PEER_LINK_MAX, peer->rank);
+  if (n_experts <= 0 || n_experts > 1024) return fail(CACHALOT_EINVAL, "moe_layer_decode_peer: E=%d must be in 1..1024", n_experts);
+  if (k < 1 || k > n_experts) return fail(CACHALOT_EINVAL, "Invalid topk=%d for %d experts", k, n_experts);
+  if (mode != CACHALOT_ROUTER_SQRT_SOFTPLUS && mode != CACHALOT_ROUTER_SIGMOID) return fail(CACHALOT_EINVAL, "moe_layer_decode_peer: unknown router mode %d", mode);
+  if (layer < 0) return fail(CACHALOT_EINVAL, "moe_layer_decode_peer: bad layer");
+  if ((numerics & 0xff) > CACHALOT_NUMERICS_BF16_H32 || (numerics & ~0xff)) return fail(CACHALOT_EINVAL, "moe_layer_decode_peer: unknown numerics %d", numerics);
+  if (out_dtype != CACHALOT_F32 && out_dtype != CACHALOT_BF16) return fail(CACHALOT_EINVAL, "moe_layer_decode_peer: out dtype must be f32 or bf16");
+  const size_t need = cachalot_moe_layer_decode_workspace_bytes(desc, k);
+  if (!workspace || workspace_bytes < need) return fail(CACHALOT_ESCRATCH, "moe_layer_decode_peer: workspace %zu < %zu bytes", workspace_bytes, need);
+  if (!aligned(workspace, 256) || !aligned(x_bf16, 16) || !aligned(out, 4)) return fail(CACHALOT_EALIGN, "moe_layer_decode_peer: workspace needs 256-byte, x 16-byte alignment");
+  if (!layer_fused_supported(v, n_experts, k))
+    return fail(CACHALOT_EUNSUPPORTED, "moe_layer_decode_peer: the single-launch kernel does not cover this bank shape or top-k; use cachalot_moe_layer_decode and cachalot_peer_sum");
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms > PEER_LINK_CTAS) return fail(CACHALOT_EUNSUPPORTED, "moe_layer_decode_peer: %d SMs exceed the %d flag columns", sms, PEER_LINK_CTAS);
+  PeerLink P = {};
+  for (int r = 0; r < peer->world; ++r) {
+    P.inbox[r] = static_cast<float*>(peer->inbox[r]);
+    P.flags[r] = static_cast<uint32_t*>(peer->flags[r]);
+    if (!P.inbox[r] || !P.flags[r] || !aligned(P.inbox[r], 16)) return fail(CACHALOT_EINVAL, "moe_layer_decode_peer: rank %d's inbox or flags pointer is null or misaligned", r);
+  }
+  P.epoch = peer->epoch, P.world = peer->world, P.rank = peer->rank;
+  return launch_layer_fused(v, x_bf16, logits, bias, slot_table, layer, n_experts, k, mode, gate_temp, route_scale, norm_topk_prob,
+                            weights_bf16, swiglu_limit, numerics, workspace, out, out_dtype, indices_out, weights_out, status,
+                            (cudaStream_t)stream, &P);
+}
+
 // ---- prefill -------------------------------------------------------------------------------
 
 namespace cachalot {

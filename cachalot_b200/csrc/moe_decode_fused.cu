@@ -422,7 +422,7 @@ template <int FMT, int SDT, typename OutT>
 __global__ void __launch_bounds__(Fm<FMT>::NTHREADS, 1)
 fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ slots,
                     const float* __restrict__ gate_w, int k, float limit, int numerics, float* __restrict__ hidden,
-                    OutT* __restrict__ out, int* __restrict__ status) {
+                    OutT* __restrict__ out, int* __restrict__ status, PeerLink P) {
   constexpr int SUB = Fm<FMT>::SUB, NCW = Fm<FMT>::NCW, NCT = NCW * 32;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int s_route[KMAX];   // routing position of the p-th present expert
@@ -454,6 +454,8 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // number of this exchange: every CTA reads the counter before any CTA can move it on (the last one to finish does)
+  const uint32_t xe = P.world > 0 ? *reinterpret_cast<volatile const uint32_t*>(P.epoch) + 1u : 0u;
 
   // consumers fetch their part of x before anything else (up to XB 16-element blocks per thread)
   constexpr int XB = 3;
@@ -806,14 +808,70 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
     }
     named_bar_sync(1, NCT);
     // sum over the experts in routing order
-    for (int o = tid; o < (t_end - t_begin) * 16; o += NCT) {
-      const int tl = o >> 4, r = o & 15;
-      float tot = 0.f;
-      for (int p = 0; p < np; ++p) tot += ybuf[(tl * KMAX + p) * 16 + r];
-      if constexpr (sizeof(OutT) == 2)
-        out[(t_begin + tl) * 16 + r] = __float2bfloat16_rn(tot);
-      else
-        out[(t_begin + tl) * 16 + r] = tot;
+    const int n_mine = (t_end - t_begin) * 16;
+    if (P.world <= 0) {
+      for (int o = tid; o < n_mine; o += NCT) {
+        const int tl = o >> 4, r = o & 15;
+        float tot = 0.f;
+        for (int p = 0; p < np; ++p) tot += ybuf[(tl * KMAX + p) * 16 + r];
+        if constexpr (sizeof(OutT) == 2)
+          out[(t_begin + tl) * 16 + r] = __float2bfloat16_rn(tot);
+        else
+          out[(t_begin + tl) * 16 + r] = tot;
+      }
+    } else if (n_mine > 0) {
+      // Expert parallel: this rank's sum is a partial one.  The CTA stores its rows into row `rank` of every rank's
+      // inbox (plain stores over NVLink; every rank splits the output rows over its CTAs in the same way), raises its
+      // flag on every rank, waits with a bound for the same CTA of every rank and adds the rows in rank order: no
+      // second launch, and every rank ends with the same bits.  Two inbox slots alternate: a rank cannot be two
+      // exchanges ahead of a peer, because finishing one takes every peer's flag of it.
+      const int slot = (int)(xe & 1u), H1 = bank.hidden;
+      for (int o = tid; o < n_mine; o += NCT) {
+        const int tl = o >> 4, r = o & 15;
+        float tot = 0.f;
+        for (int p = 0; p < np; ++p) tot += ybuf[(tl * KMAX + p) * 16 + r];
+        const size_t at = ((size_t)slot * P.world + P.rank) * H1 + (size_t)t_begin * 16 + o;
+        for (int q = 0; q < P.world; ++q) P.inbox[q][at] = tot;
+      }
+      named_bar_sync(1, NCT);
+      if (tid < P.world) {
+        const size_t mine = ((size_t)slot * P.world + P.rank) * PEER_LINK_CTAS + blockIdx.x;
+        // release at system scope: the CTA's stores (ordered before this thread by the CTA barrier) first
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(P.flags[tid] + mine), "r"(xe) : "memory");
+        const uint32_t* f = P.flags[P.rank] + ((size_t)slot * P.world + tid) * PEER_LINK_CTAS + blockIdx.x;
+        uint32_t i = 0, got;
+        for (;;) {
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(f) : "memory");
+          if (got == xe) break;
+          if (++i >= (1u << 22)) {  // a peer did not show up: flag it and carry on with what is there
+            if (status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
+            break;
+          }
+          if (i > 64) __nanosleep(64);
+        }
+      }
+      named_bar_sync(1, NCT);
+      const float* rows = P.inbox[P.rank] + (size_t)slot * P.world * H1 + (size_t)t_begin * 16;
+      for (int o = tid; o < n_mine; o += NCT) {
+        float tot = __ldcg(rows + o);  // written by other GPUs: read past L1
+        for (int q = 1; q < P.world; ++q) tot += __ldcg(rows + (size_t)q * H1 + o);
+        if constexpr (sizeof(OutT) == 2)
+          out[t_begin * 16 + o] = __float2bfloat16_rn(tot);
+        else
+          out[t_begin * 16 + o] = tot;
+      }
+    }
+    if (P.world > 0) {
+      // the exchange counter moves on once per launch: by the CTA that takes the last ticket
+      named_bar_sync(1, NCT);
+      if (tid == 0) {
+        const unsigned ticket = atomicAdd(P.epoch + 1, 1u);
+        if (ticket == gridDim.x - 1) {
+          P.epoch[1] = 0;
+          __threadfence();
+          P.epoch[0] = xe;
+        }
+      }
     }
     if (err && lane == 0 && status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
   }
@@ -908,7 +966,9 @@ size_t decode_fused_workspace_bytes(int hidden, int inter, int rows, int k) {
 template <int FMT>
 static int launch_fused_fmt(const BankView& v, const Geo& G, const RouteArgs& R, const void* x, const int32_t* slots,
                             const float* gate_w, int k, float limit, int numerics, void* workspace, void* out, int out_dtype,
-                            int* status, cudaStream_t stream) {
+                            int* status, cudaStream_t stream, const PeerLink* peer = nullptr) {
+  PeerLink P = {};
+  if (peer) P = *peer;
   float* hidden = static_cast<float*>(workspace);
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return fail(CACHALOT_ECUDA, "moe_decode (fused): no current device");
@@ -961,7 +1021,7 @@ static int launch_fused_fmt(const BankView& v, const Geo& G, const RouteArgs& R,
         done.insert({(const void*)kern, dev});
       }
     }
-    e = cudaLaunchKernelEx(&cfg, kern, v, Gl, R, xb, slots, gate_w, k, limit, numerics, hidden, outp, status);
+    e = cudaLaunchKernelEx(&cfg, kern, v, Gl, R, xb, slots, gate_w, k, limit, numerics, hidden, outp, status, P);
   };
   const bool bf16_scales = FMT == CACHALOT_BANK_AFFINE && v.scale_dtype == CACHALOT_BF16;
   if (out_dtype == CACHALOT_BF16) {
@@ -991,7 +1051,7 @@ int launch_decode_fused(const BankView& v, const void* x, const int32_t* slots, 
 int launch_layer_fused(const BankView& v, const void* x, const float* logits, const float* bias, const int32_t* slot_table,
                        int layer, int n_experts, int k, int mode, float gate_temp, float route_scale, int norm,
                        int weights_bf16, float limit, int numerics_flags, void* workspace, void* out, int out_dtype,
-                       int32_t* indices_out, float* weights_out, int* status, cudaStream_t stream) {
+                       int32_t* indices_out, float* weights_out, int* status, cudaStream_t stream, const PeerLink* peer) {
   Geo G;
   if (!make_geo(v, k, &G) || n_experts > 1024) return CACHALOT_EUNSUPPORTED;
   if (G.act_stride[1] * k < G.act_stride[0] + 12288) return CACHALOT_EUNSUPPORTED;  // the routing scratch sits behind x in the operand area
@@ -1001,8 +1061,8 @@ int launch_layer_fused(const BankView& v, const void* x, const float* logits, co
   R.layer = layer, R.n_experts = n_experts, R.mode = mode, R.norm = norm, R.weights_bf16 = weights_bf16;
   R.gate_temp = gate_temp, R.route_scale = route_scale;
   if (v.format == CACHALOT_BANK_FP4)
-    return launch_fused_fmt<CACHALOT_BANK_FP4>(v, G, R, x, nullptr, nullptr, k, limit, numerics, workspace, out, out_dtype, status, stream);
-  return launch_fused_fmt<CACHALOT_BANK_AFFINE>(v, G, R, x, nullptr, nullptr, k, limit, numerics, workspace, out, out_dtype, status, stream);
+    return launch_fused_fmt<CACHALOT_BANK_FP4>(v, G, R, x, nullptr, nullptr, k, limit, numerics, workspace, out, out_dtype, status, stream, peer);
+  return launch_fused_fmt<CACHALOT_BANK_AFFINE>(v, G, R, x, nullptr, nullptr, k, limit, numerics, workspace, out, out_dtype, status, stream, peer);
 }
 
 bool layer_fused_supported(const BankView& v, int n_experts, int k) {

@@ -467,3 +467,177 @@ def combine_rows(y: torch.Tensor, inv: torch.Tensor, tokens: int, k: int) -> tor
         check(lib.cachalot_moe_combine_rows(_ptr(y.contiguous()), _ptr(inv.to(torch.int32).contiguous()), tokens, k, y.shape[1],
                                             _ptr(out), _stream()))
     return out
+
+
+# ---- the reference's per-expert prefill entries ---------------------------------------------------
+
+def _one_expert_rows(x, tensors, fmt, weights, swiglu_limit, numerics):
+    """[M,H] rows through ONE expert given as loose tensors: the tensors are copied into a one-slot bank and every
+    row is routed to it with its own weight (k = 1)."""
+    if x.dim() != 2:
+        raise ValueError(f"x must be [M, H], got {tuple(x.shape)}")
+    m = x.shape[0]
+    if weights.numel() != m:
+        raise ValueError(f"{weights.numel()} router weights for {m} rows")
+    if fmt.kind == "fp4":
+        inter = tensors["w1.scale"].shape[0]
+        hidden = tensors["w1.weight"].numel() * 2 // inter
+    else:
+        inter, hidden = fmt.shapes["w1.weight"][0], fmt.shapes["w2.weight"][0]
+    bank = SlabBank(fmt, hidden, inter, 1, device=x.device)
+    bank.write_expert(0, tensors)
+    slots = torch.zeros((m, 1), dtype=torch.int32, device=x.device)
+    return moe_forward(x, slots, weights.reshape(m, 1), bank, swiglu_limit=swiglu_limit, numerics=numerics)
+
+
+def routed_expert_forward_batched(x: torch.Tensor, *, w1_packed, w1_scales, w2_packed, w2_scales, w3_packed, w3_scales,
+                                  weights: torch.Tensor, swiglu_limit: float = 10.0) -> torch.Tensor:
+    """One FP4 expert over a batch of rows with the reference's prefill rounding points (g, u -> bf16; h -> bf16;
+    output -> bf16 -> f32): model/moe_prefill_batched.py:31-61.  x [M,H], weights [M] -> float32 [M,H]."""
+    t = {"w1.weight": w1_packed, "w1.scale": w1_scales, "w2.weight": w2_packed, "w2.scale": w2_scales,
+         "w3.weight": w3_packed, "w3.scale": w3_scales}
+    return _one_expert_rows(x, t, FP4_FORMAT, weights, swiglu_limit, "bf16")
+
+
+routed_expert_forward_sgmm = routed_expert_forward_batched   # same contract (model/fp4_sgmm_metal.py:318-333)
+
+
+def affine_expert_forward_batched(x: torch.Tensor, arrays: dict, fmt: ExpertFormat, weights: torch.Tensor,
+                                  swiglu_limit: float = 10.0) -> torch.Tensor:
+    """One affine-quantised expert over a batch of rows (model/expert_affine.py:84-99): x [M,H], `arrays` = the
+    expert's nine tensors by the format's names, weights [M] -> float32 [M,H]."""
+    if fmt.kind != "affine":
+        raise ValueError("affine_expert_forward_batched needs an affine format")
+    return _one_expert_rows(x, arrays, fmt, weights, swiglu_limit, "bf16")
+
+
+class SlabExperts:
+    """The routed experts of any layer from a slot index array on the device, each expert's output kept apart
+    (minimax/gpu_select.py:279-327): `SlabExperts(bank)(x[1,D], slots int32 [k]) -> [k, D]`.  The reference passes
+    the activation as a callable between its two kernels; here the two projections are one launch, so only the
+    SwiGLU of the routed experts is offered (`activation` None, or a float = its clamp limit)."""
+
+    def __init__(self, pool: SlabBank, fmt: ExpertFormat | None = None) -> None:
+        if fmt is not None and fmt.kind != pool.fmt.kind:
+            raise ValueError("format does not match the pool")
+        self.pool = pool
+
+    def __call__(self, x: torch.Tensor, slots: torch.Tensor, activation=None) -> torch.Tensor:
+        if callable(activation):
+            raise NotImplementedError("a custom activation between the projections is not built; pass None or the clamp limit")
+        limit = 0.0 if activation is None else float(activation)
+        k = slots.numel()
+        xs = x.reshape(1, -1).expand(k, -1)
+        ones = torch.ones((k, 1), dtype=torch.float32, device=x.device)
+        return moe_forward(xs, slots.reshape(k, 1), ones, self.pool, swiglu_limit=limit).to(x.dtype)
+
+
+# ---- shared FP8 expert and the whole MoE layer -------------------------------------------------------
+
+def _fp8_rule(scales: torch.Tensor, n: int, k: int):
+    if scales.dtype == torch.uint8:
+        return "e8m0", 32
+    if scales.dtype != torch.float32:
+        raise ValueError(f"weight scales must be uint8 (E8M0) or float32, got {scales.dtype}")
+    return "f32", k // scales.shape[1]
+
+
+def _shared(x2, w1, w1s, w3, w3s, w2, w2s, swiglu_limit, addend):
+    rows, hidden = x2.shape
+    inter = w2.shape[1]
+    rule, block = _fp8_rule(w2s, hidden, inter)
+    if tuple(w2.shape) != (hidden, inter) or w1.shape[1] != hidden or w1.shape[0] != (inter if w3 is not None else 2 * inter):
+        raise ValueError(f"shared expert shapes do not fit: x {tuple(x2.shape)}, w1 {tuple(w1.shape)}, w2 {tuple(w2.shape)}")
+    xb = x2.to(torch.bfloat16).contiguous()
+    out = torch.empty((rows, hidden), dtype=torch.bfloat16, device=x2.device)
+    if rows == 0:
+        return out
+    need = lib.cachalot_shared_expert_workspace_bytes(rows, hidden, inter, block)
+    ws = _workspace(x2.device, need + 256)
+    base = (ws.data_ptr() + 255) // 256 * 256
+    ad = None if addend is None else addend.to(torch.float32).contiguous()
+    check(lib.cachalot_shared_expert(_ptr(xb), rows, hidden, inter, _ptr(w1.contiguous()), _ptr(w1s.contiguous()),
+                                     _ptr(None if w3 is None else w3.contiguous()), _ptr(None if w3s is None else w3s.contiguous()),
+                                     _ptr(w2.contiguous()), _ptr(w2s.contiguous()), _RULE[rule], block, float(swiglu_limit),
+                                     _ptr(ad), base, ws.numel() - (base - ws.data_ptr()), _ptr(out), _stream()))
+    return out
+
+
+def shared_expert_forward(x: torch.Tensor, *, w1, w1_scales, w2, w2_scales, w3, w3_scales, swiglu_limit: float = 10.0) -> torch.Tensor:
+    """The resident FP8 expert for one decode token (model/shared_expert_metal.py:45-134): bf16 [H]."""
+    if x.dim() != 1:
+        raise ValueError(f"x must be 1D for decode, got {tuple(x.shape)}")
+    return _shared(x[None], w1, w1_scales, w3, w3_scales, w2, w2_scales, swiglu_limit, None)[0]
+
+
+def shared_expert_forward_fused(x: torch.Tensor, *, w13, w13_scales, w2, w2_scales, swiglu_limit: float = 10.0) -> torch.Tensor:
+    """The same with w1 and w3 concatenated along the rows, one GEMV (model/shared_expert_metal.py:137-188)."""
+    if x.dim() != 1:
+        raise ValueError(f"x must be 1D for decode, got {tuple(x.shape)}")
+    return _shared(x[None], w13, w13_scales, None, None, w2, w2_scales, swiglu_limit, None)[0]
+
+
+def shared_expert_forward_batched(x: torch.Tensor, *, w1, w1_scales, w2, w2_scales, w3, w3_scales, swiglu_limit: float = 10.0) -> torch.Tensor:
+    """The shared expert over a prompt chunk (model/moe_prefill_batched.py:100-125): x [M,H] -> bf16 [M,H]."""
+    if x.dim() != 2:
+        raise ValueError(f"x must be [M, H], got {tuple(x.shape)}")
+    return _shared(x, w1, w1_scales, w3, w3_scales, w2, w2_scales, swiglu_limit, None)
+
+
+def fp8_linear_rows(x: torch.Tensor, weight: torch.Tensor, weight_scales: torch.Tensor) -> torch.Tensor:
+    """x [T,K] -> bf16 [T,N] (model/moe_prefill_batched.py:93-97): act_quant per row, then the GEMV's arithmetic."""
+    return fp8_linear(x, weight, weight_scales)
+
+
+_fused_rows_cache: dict = {}
+
+
+def fused_qr_kv_linear(x: torch.Tensor, wq_a, wq_a_scales, wkv, wkv_scales):
+    """qr = fp8_linear(x, wq_a), window_kv = fp8_linear(x, wkv) as ONE act_quant and ONE GEMV over the rows of both
+    matrices (model/attention_qkv_fusion.py:46-68); the concatenation is built once per pair of weights."""
+    key = (wq_a.data_ptr(), wkv.data_ptr())
+    hit = _fused_rows_cache.get(key)
+    if hit is None or hit[0] is not wq_a or hit[1] is not wkv:
+        hit = (wq_a, wkv, torch.cat([wq_a, wkv], 0).contiguous(), torch.cat([wq_a_scales, wkv_scales], 0).contiguous())
+        _fused_rows_cache[key] = hit
+    block = 32 if wq_a_scales.dtype == torch.uint8 else wq_a.shape[1] // wq_a_scales.shape[1]
+    if wq_a.shape[0] % block:
+        raise ValueError(f"{wq_a.shape[0]} rows of the first matrix are not whole scale blocks of {block}")
+    out = fp8_linear(x, hit[2], hit[3])
+    rows = wq_a.shape[0]
+    return out[..., :rows], out[..., rows:]
+
+
+def moe_layer_forward(x: torch.Tensor, *, layer_id: int, gate_weight: torch.Tensor, gate_bias: torch.Tensor,
+                      expert_store: SlabBank, shared_w1, shared_w1_scales, shared_w2, shared_w2_scales, shared_w3,
+                      shared_w3_scales, expert_index=None, topk: int = 6, gate_temp: float = 1.0, route_scale: float = 1.5,
+                      norm_topk_prob: bool = True, swiglu_limit: float = 10.0, fused: bool | None = None,
+                      scores: bool = True, status: torch.Tensor | None = None):
+    """The whole MoE block of one decode token, keyword for keyword the reference's entry
+    (model/moe_layer_metal.py:133-405): bf16 x [H] -> fp32 router (gate GEMV, sqrt-softplus scores, top-k) ->
+    routed experts over the resident bank -> shared FP8 expert -> (routed + shared.f32) -> bf16 [H].  Returns
+    (output, RouterResult).  Nothing here waits for the device: the selected ids go from the routing tail to the
+    expert kernel on the GPU (an expert whose slot is -1 contributes zeros), so `expert_index` -- the reference's
+    host-side (layer, expert) -> entry map -- is only checked for the layer's presence when given.
+    `expert_store` is the SlabBank; `shared_w3 = None` means `shared_w1` holds the w1 || w3 concatenation.
+    `fused` is accepted for signature parity (there is one path).  `scores=False` skips the [E] score vector."""
+    if x.dim() != 1:
+        raise ValueError(f"x must be 1D for decode, got {tuple(x.shape)}")
+    bank = expert_store
+    e = gate_weight.shape[0]
+    if tuple(gate_bias.shape) != (e,):
+        raise ValueError(f"bias shape {tuple(gate_bias.shape)} != ({e},)")
+    if expert_index is not None and not any(k[0] == layer_id for k in expert_index):
+        raise KeyError(f"Missing routed expert layer={layer_id}")
+    logits = router_logits(x, gate_weight)[0]
+    routed, idx, w = moe_layer_decode(x, logits, bank, layer=layer_id, topk=topk, bias=gate_bias, router="sqrt_softplus",
+                                      gate_temp=gate_temp, route_scale=route_scale, norm_topk_prob=norm_topk_prob,
+                                      swiglu_limit=swiglu_limit, status=status, want_routing=True)
+    sc = None
+    if scores:
+        _, _, _, s2 = _route(logits[None], gate_bias, None, 0, topk, _lib.ROUTER_SQRT_SOFTPLUS, gate_temp, route_scale,
+                             norm_topk_prob, False, True)
+        sc = s2[0]
+    out = _shared(x[None], shared_w1, shared_w1_scales, shared_w3, shared_w3_scales, shared_w2, shared_w2_scales, swiglu_limit,
+                  routed[None])[0]
+    return out, RouterResult(indices=idx, weights=w, scores=sc)

@@ -205,6 +205,21 @@ CACHALOT_API int cachalot_fp8_gemv(const uint8_t* codes, const float* act_scales
                       int scale_rule, int block, int rows, int n, int k, void* out, int out_dtype,
                       cachalot_stream_t stream);
 
+/* Replaces model/shared_expert_metal.py:45-188 shared_expert_forward / shared_expert_forward_fused (decode, rows = 1)
+ * and model/moe_prefill_batched.py:100-125 shared_expert_forward_batched (rows = M): the resident FP8 expert
+ *   qx = act_quant(x);  gate = bf16(w1 qx), up = bf16(w3 qx)  (one act_quant for both);
+ *   up = clip(up, +-L), gate = min(gate, L) when L > 0;  h = bf16(silu(gate) * up);  y = bf16(w2 act_quant(h))
+ * and, when `addend` (f32 [rows, hidden], the routed experts' sum) is given, the layer's closing line
+ * out = bf16(addend + f32(y)) of model/moe_layer_metal.py:394-403.  x bf16 [rows, hidden]; w1, w3 u8 [inter, hidden],
+ * w2 u8 [hidden, inter] raw E4M3; scales as in cachalot_fp8_gemv.  w3 == NULL: w1 holds the [2*inter, hidden]
+ * concatenation w1 || w3 with its scales (the reference's fused form; one GEMV).  hidden and inter must be
+ * multiples of `block`.  out bf16 [rows, hidden]. */
+CACHALOT_API size_t cachalot_shared_expert_workspace_bytes(int rows, int hidden, int inter, int block);
+CACHALOT_API int cachalot_shared_expert(const void* x_bf16, int rows, int hidden, int inter, const uint8_t* w1,
+                           const void* w1_scales, const uint8_t* w3, const void* w3_scales, const uint8_t* w2,
+                           const void* w2_scales, int scale_rule, int block, float swiglu_limit, const float* addend,
+                           void* workspace, size_t workspace_bytes, void* out_bf16, cachalot_stream_t stream);
+
 /* ---- prefill: expert-major grouping, MXFP4 activations, grouped FFN ------------------------ */
 
 /* Replaces the host-side grouping of model/moe_prefill_grouped.py:201-225 (and
@@ -274,6 +289,32 @@ CACHALOT_API size_t cachalot_peer_sum_inbox_bytes(int world, int n);
 CACHALOT_API size_t cachalot_peer_sum_flag_bytes(int world);
 CACHALOT_API int cachalot_peer_sum(void* const* inbox_ptrs /* host */, void* const* flag_ptrs /* host */, int world, int rank,
                       const float* partial, float* out, int n, uint32_t* epoch, int* status, cachalot_stream_t stream);
+
+/* No counterpart in the reference.  cachalot_moe_layer_decode for an expert-parallel rank with the sum over the ranks
+ * done in the tail of the same launch: every CTA stores the output rows it owns into row `rank` of every rank's inbox
+ * (plain peer stores over NVLink, no multicast), raises a flag per (rank, CTA), waits with a bound for the same CTA of
+ * every peer and adds the rows in rank order, so `out` holds the full layer output on every rank and all ranks hold
+ * the same bits.  The ranks must run on GPUs with the same number of SMs and make the same sequence of calls; a
+ * peer that does not show up makes the wait expire (CACHALOT_STATUS_WAIT_EXPIRED) and the call returns with an
+ * incomplete sum.  inbox[r] / flags[r] (device pointers as mapped in THIS process): rank r's inbox of
+ * cachalot_peer_layer_inbox_bytes(world, hidden) bytes and flag array of cachalot_peer_layer_flag_bytes(world)
+ * bytes in memory every rank can write, zeroed once; epoch: u32 [2] in local device memory, zeroed once.  Only bank
+ * shapes and top-k the single-launch kernel covers (else CACHALOT_EUNSUPPORTED: use cachalot_peer_sum). */
+typedef struct {
+  void* inbox[8];
+  void* flags[8];
+  uint32_t* epoch;
+  int32_t world, rank;
+} cachalot_peer_ctx;
+CACHALOT_API size_t cachalot_peer_layer_inbox_bytes(int world, int hidden);
+CACHALOT_API size_t cachalot_peer_layer_flag_bytes(int world);
+CACHALOT_API int cachalot_moe_layer_decode_peer(const void* bank, const cachalot_bank_desc* desc /* host */, const void* x_bf16,
+                                   const float* logits, const float* bias, const int32_t* slot_table, int layer,
+                                   int n_experts, int k, int mode, float gate_temp, float route_scale, int norm_topk_prob,
+                                   int weights_bf16, float swiglu_limit, int numerics, void* workspace,
+                                   size_t workspace_bytes, void* out, int out_dtype, int32_t* indices_out,
+                                   float* weights_out, const cachalot_peer_ctx* peer /* host */, int* status,
+                                   cachalot_stream_t stream);
 
 #ifdef __cplusplus
 }
