@@ -1,19 +1,23 @@
-"""Benchmark of the routed-expert MoE decode path.
+"""Benchmark of the routed-expert MoE hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--bank affine2|fp4] [--batch B] [--distinct-layers NL]
+                    [--workload decode|prefill|fp8] [--bank affine2|fp4] [--batch B] [--distinct-layers NL]
 
-One step = one decoded token = LAYERS (40) MoE layer passes: per layer the sigmoid top-6 routing
-tail with slot lookup and the routed experts (gate/up, SwiGLU, down, weighted sum) over the
-resident bank -- one kernel launch per layer for one token.  The default workload is the 2-bit affine g128 bank, batch 1, 384 experts per
-layer; the bank holds NL distinct layers (default 8, 30.6 GB) that the 40 passes cycle through
-with fresh random routing, so the bytes a pass reads were last touched hundreds of MB ago (the
-working set is far larger than L2).  Prints ONE JSON line (rank 0).
+decode (default): one step = one decoded token = LAYERS (40) MoE layer passes: per layer the sigmoid top-6 routing
+tail with slot lookup and the routed experts (gate/up, SwiGLU, down, weighted sum) over the resident bank -- one
+kernel launch per layer for one token.  The default workload is the 2-bit affine g128 bank, batch 1, 384 experts
+per layer; the bank holds NL distinct layers (default 8, 30.6 GB) that the 40 passes cycle through with fresh
+random routing, so the bytes a pass reads were last touched hundreds of MB ago (the working set is far larger than
+L2).  The K-step timed region is repeated (at least five times, at least half a second in total) and the median
+is reported.  Prints ONE JSON line (rank 0).
 
-N > 1 shards the experts of every layer over the ranks (expert parallel, replicated input,
-partial outputs summed with an NCCL all-reduce); total work is fixed ("strong" scaling).
-`--impl reference` times the CPU path (the numpy oracle port of the reference's arithmetic)
-on the host cores for the same metric.
+N > 1 shards the experts of every layer over the ranks (expert parallel, replicated input); the partial outputs
+are summed through peer memory over NVLink in the tail of the expert kernel (`--reduce fused`, batch 1), by the
+library's stand-alone peer-memory kernel (`--reduce peer`) or by an NCCL all-reduce (`--reduce nccl`); total work
+is fixed ("strong" scaling).  Before timing, every rank checks a small sharded layer against the same layer on a
+whole bank and the run stops with a non-zero exit code if they differ.
+`--impl reference` times the CPU path (the numpy oracle port of the reference's arithmetic) on the host cores for
+the same metric; the same function gives the `cpu_baseline` of the GPU arm.
 """
 from __future__ import annotations
 
@@ -46,15 +50,17 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--bank", default="affine2", choices=["affine2", "fp4"])
     p.add_argument("--batch", type=int, default=1)
-    p.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+    p.add_argument("--workload", default="decode", choices=["decode", "prefill", "fp8"],
                    help="prefill: one 4096-token chunk through one FP4 layer, Zipf(1.1) expert popularity (1 GPU)")
     p.add_argument("--tokens", type=int, default=4096, help="prefill chunk length")
     p.add_argument("--experts", type=int, default=EXPERTS, help="prefill: experts in the layer (smaller = a case sized for profiling)")
     p.add_argument("--distinct-layers", type=int, default=8)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-graph", action="store_true")
-    p.add_argument("--reduce", default="peer", choices=["peer", "nccl"],
-                   help="N > 1: how the ranks' partial layer outputs are summed (peer = the library's peer-memory kernel)")
+    p.add_argument("--reduce", default="fused", choices=["fused", "peer", "nccl"],
+                   help="N > 1: how the ranks' partial layer outputs are summed (fused = in the tail of the expert kernel, "
+                        "peer = the library's stand-alone peer-memory kernel, nccl = all_reduce)")
+    p.add_argument("--repeats", type=int, default=0, help="repeats of the K-step timed region (0 = at least 5 and 0.5 s in total)")
     p.add_argument("--watchdog", type=int, default=0, help="dump all Python stacks and exit after this many seconds (0 = off)")
     return p.parse_args()
 
@@ -161,15 +167,27 @@ def cpu_layer_pass(bank_kind: str, x, w, experts, threads: int):
     return total
 
 
-def time_cpu(bank_kind: str, steps: int, warmup: int, threads: int):
+def cpu_threads() -> int:
+    """Threads of the CPU arm: one per routed expert of a layer, as far as the host has cores."""
+    return max(1, min(TOPK, os.cpu_count() or 1))
+
+
+def time_cpu_token(bank_kind: str):
+    """The CPU arm, used both as `cpu_baseline` and as `--impl reference`: ONE whole token really timed = LAYERS passes
+    of a MoE layer (six routed experts from packed bytes: dequantise, three mat-vecs, SwiGLU, weighted sum) on
+    `cpu_threads()` threads, after one untimed pass.  The passes reuse one layer's packed bytes (generating 240
+    distinct experts on the host would take longer than the measurement; the cost is arithmetic, not memory).
+    Returns (seconds per token, tok/s, threads, description)."""
+    threads = cpu_threads()
     x, w, experts = cpu_layer_inputs(bank_kind)
-    for _ in range(warmup):
-        cpu_layer_pass(bank_kind, x, w, experts, threads)
+    cpu_layer_pass(bank_kind, x, w, experts, threads)
     t0 = time.perf_counter()
-    for _ in range(steps):
+    for _ in range(LAYERS):
         cpu_layer_pass(bank_kind, x, w, experts, threads)
-    dt = (time.perf_counter() - t0) / steps
-    return dt, 1.0 / (dt * LAYERS)
+    dt = time.perf_counter() - t0
+    desc = (f"one token = {LAYERS} timed passes of one MoE layer (6 routed experts from packed bytes, numpy port of the reference's "
+            f"arithmetic), {threads} threads, {dt:.1f} s; one untimed pass first; the passes reuse one layer's packed bytes")
+    return dt, 1.0 / dt, threads, desc
 
 
 def time_cpu_prefill(args):
@@ -221,15 +239,15 @@ def run_reference(args):
         return
     if args.workload == "prefill":
         return run_reference_prefill(args)
-    threads = min(TOPK, os.cpu_count() or 1)
-    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 1))
-    dt, tok_s = time_cpu(args.bank, steps, warmup, threads)
-    sample = f"{steps} timed passes of one MoE layer (6 routed experts from packed bytes), batch 1; a token = {LAYERS} passes"
+    dt, tok_s, threads, desc = time_cpu_token(args.bank)
     line = {
         "impl": "reference", "metric": "moe_decode_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": warmup, "ms_per_step": dt * LAYERS * 1e3, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args, None),
-        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        "steps": 1, "warmup": 0, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, {"parallelism": "cpu", "partial_sum": "none", "cuda_graph": False,
+                                         "steps_note": f"--steps {args.steps} --warmup {args.warmup} asked; one token is timed (a token takes "
+                                                       f"{dt:.0f} s on the host cores)"}),
+        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -254,16 +272,64 @@ def fill_bank(bank, gen):
     bank.fill_random(gen)
 
 
-def _leave(world: int) -> None:
-    """End of a multi-rank run.  The captured CUDA graphs still hold NCCL work; tearing the process group
-    down with them alive blocks, so a rank that has printed (or has nothing to print) leaves at once."""
+def _leave(world: int, closers=()) -> None:
+    """End of a multi-rank run: all ranks stop together with nothing in flight, drop their peer mappings together
+    (`closers`: objects with close()), and only then leave.  The process group is not torn down (captured graphs
+    may still hold NCCL work, and tearing down with them alive blocks): the ranks exit at once after the barrier."""
     if world > 1:
         import torch
+        import torch.distributed as dist
 
         torch.cuda.synchronize()
+        dist.barrier()
+        for c in closers:
+            if c is not None:
+                c.close()
+        torch.cuda.synchronize()
+        dist.barrier()
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)
+
+
+def check_expert_parallel(cb, ep, dist, dev, rank, world, reduce_kind):
+    """A small layer on this rank's shard with the cross-rank sum against the same layer on a whole bank, on every
+    rank: True when every rank agrees within 2e-3 of the largest output and no status bit is set."""
+    import torch
+
+    hidden, inter, n_exp, k = 2048, 2816, 32, TOPK
+    ok = True
+    for kind in ("affine2", "fp4"):
+        fmt = cb.affine_format(hidden, inter) if kind == "affine2" else cb.FP4_FORMAT
+        whole = cb.SlabBank(fmt, hidden, inter, n_exp, layers=1, n_experts=n_exp, device=dev)
+        whole.fill_random(torch.Generator(device=dev).manual_seed(77))
+        lo, hi = ep.local_range(n_exp, rank, world)
+        shard = cb.SlabBank(fmt, hidden, inter, max(hi - lo, 1), layers=1, n_experts=n_exp, device=dev)
+        if hi > lo:
+            shard.slab.copy_(whole.slab[lo:hi])
+        table = ep.local_slot_table(1, n_exp, rank, world).to(dev)
+        peer = ep.PeerLayer(hidden, dev) if reduce_kind == "fused" else None
+        psum = ep.PeerSum(hidden, dev) if reduce_kind == "peer" else None
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        g = torch.Generator().manual_seed(3)
+        for _ in range(4):
+            x = torch.randn(hidden, generator=g).to(torch.bfloat16).to(dev)
+            logits = torch.randn(n_exp, generator=g).to(dev)
+            got = cb.moe_layer_decode(x, logits, shard, table=table, router="sigmoid", peer=peer, status=status)
+            if psum is not None:
+                got = psum(got, status=status)
+            elif peer is None:
+                dist.all_reduce(got)
+            want = cb.moe_layer_decode(x, logits, whole, router="sigmoid")
+            ok = ok and float((got - want).abs().max()) <= 2e-3 * float(want.abs().max())
+        torch.cuda.synchronize(dev)
+        ok = ok and int(status.item()) == 0
+        for c in (peer, psum):
+            if c is not None:
+                c.close()
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(flag.item())
 
 
 def run_ours(args):
@@ -305,38 +371,33 @@ def run_ours(args):
     slots_all = torch.empty((LAYERS, B, K), dtype=torch.int32, device=dev)
     w_all = torch.empty((LAYERS, B, K), dtype=torch.float32, device=dev)
 
-    # cross-rank sum of the partial outputs: the library's peer-memory kernel, checked once against NCCL
-    peer_sum, reduce_kind = None, "none"
+    # cross-rank sum of the partial outputs.  No silent downgrade: what --reduce asks for either works and passes the
+    # check against the unsharded layer, or the run stops with a non-zero exit code.
+    peer_sum, peer_layer, reduce_kind = None, None, "none"
     if world > 1:
-        reduce_kind = "nccl"
-        if args.reduce == "peer":
-            try:
-                peer_sum = ep.PeerSum(B * HIDDEN, dev)
-                probe = torch.randn((B, HIDDEN), generator=torch.Generator().manual_seed(100 + rank)).to(dev)
-                want = probe.clone()
-                dist.all_reduce(want)
-                got = peer_sum(probe.clone().view(-1), status=status).view(B, HIDDEN)
-                torch.cuda.synchronize(dev)
-                if int(status.item()) or not torch.allclose(got, want, rtol=1e-5, atol=1e-5):
-                    raise RuntimeError(f"peer sum differs from the NCCL sum (status {int(status.item())})")
-                reduce_kind = "peer"
-            except Exception as exc:  # no peer access / symmetric memory on this box: the library collective instead
-                if rank == 0:
-                    print(f"peer-memory sum unavailable ({exc}); using NCCL all_reduce", file=sys.stderr, flush=True)
-                peer_sum = None
-                status.zero_()
+        reduce_kind = args.reduce if B == 1 or args.reduce != "fused" else "peer"   # the in-kernel exchange is the one-token kernel's
+        if not check_expert_parallel(cb, ep, dist, dev, rank, world, reduce_kind):
+            if rank == 0:
+                print(f"expert-parallel check failed (--reduce {reduce_kind}): the sharded layer differs from the whole one",
+                      file=sys.stderr, flush=True)
+            torch.cuda.synchronize()
+            os._exit(3)
+        if reduce_kind == "fused":
+            peer_layer = ep.PeerLayer(HIDDEN, dev)
+        elif reduce_kind == "peer":
+            peer_sum = ep.PeerSum(B * HIDDEN, dev)
 
     def token_step():
         for l in range(LAYERS):
             if B == 1:   # routing tail and experts in one launch
                 cb.moe_layer_decode(x[0], logits[l][0], bank, layer=l % NL, topk=K, table=table, router="sigmoid", route_scale=1.0,
-                                    swiglu_limit=SWIGLU_LIMIT, out=out[0], workspace=ws, status=status)
+                                    swiglu_limit=SWIGLU_LIMIT, out=out[0], workspace=ws, status=status, peer=peer_layer)
             else:
                 _, w, slots = cb.route_tail(logits[l], None, table, l % NL, K, 1.0, weights_bf16=False)
                 cb.moe_forward(x, slots, w, bank, swiglu_limit=SWIGLU_LIMIT, out=out, workspace=ws, status=status)
             if peer_sum is not None:
                 peer_sum(out.view(-1), status=status)
-            elif world > 1:
+            elif world > 1 and peer_layer is None:
                 dist.all_reduce(out)
 
     def phase_step(phase):
@@ -401,8 +462,16 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms = timed(run_token, args.steps, feed_device)
-    ms_e2e = timed(run_token, args.steps, feed_host, read_back)
+    def repeated(before, after=None):
+        """The K-step region repeated: at least five times and half a second in total, so that the clock sampler sees
+        the GPU under load.  Returns (median, min, all) in ms per region; identical counts on every rank."""
+        first = timed(run_token, args.steps, before, after)
+        n = args.repeats if args.repeats > 0 else int(min(400, max(5, -(-500.0 // max(first, 1e-3)))))
+        all_ms = sorted([first] + [timed(run_token, args.steps, before, after) for _ in range(n - 1)])
+        return all_ms[len(all_ms) // 2], all_ms[0], all_ms
+
+    ms, ms_min, ms_all = repeated(feed_device)
+    ms_e2e, ms_e2e_min, _ = repeated(feed_host, read_back)
     clocks = sampler.stop() if rank == 0 else None
 
     # per-kernel durations: the same 40 passes with routing done beforehand
@@ -433,7 +502,7 @@ def run_ours(args):
     st = int(status.item())
 
     if rank != 0:
-        _leave(world)
+        _leave(world, (peer_layer, peer_sum))
         return
 
     sizes = bank.tensor_sizes
@@ -454,7 +523,8 @@ def run_ours(args):
         roofline = {"kernel": "fused_decode_kernel (routing tail + W1,W3 dequant-GEMV + SwiGLU + W2 dequant-GEMV + sum over experts, one launch per layer)",
                     "bound": "hbm", "achieved": gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": gbs / peak,
                     "us_per_launch": us_launch, "algorithmic_bytes_per_launch": layer_bytes,
-                    "traffic": NCU_TRAFFIC_BYTES.get((args.bank, B, "fused")),
+                    # the ncu capture is of a one-GPU launch; a rank of an expert-parallel run reads its share only
+                    "traffic": NCU_TRAFFIC_BYTES.get((args.bank, B, "fused")) if world == 1 else None,
                     "us_per_launch_routing_done_beforehand": ms_layer * 1e3}
         launches = LAYERS * args.steps              # routing tail + experts = one launch per layer
     elif fused:
@@ -477,10 +547,11 @@ def run_ours(args):
         launches = 4 * LAYERS * args.steps          # routing tail, row grouping, gate/up, down per layer
 
     if peer_sum is not None:
-        launches += LAYERS * args.steps             # the peer-memory sum, one launch per layer
+        launches += LAYERS * args.steps             # the stand-alone peer-memory sum, one launch per layer
     line = {
         "metric": "moe_decode_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "ms_per_step_min": ms_min / args.steps, "repeats": len(ms_all),
+        "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None,
         "dtype": "int2xbf16->f32" if args.bank == "affine2" else "e2m1xbf16->f32", "data": "synthetic",
         "config": workload_config(args, {"parallelism": f"ep{world}", "partial_sum": reduce_kind, "cuda_graph": use_graph, "numerics_version": cb.NUMERICS_VERSION}),
@@ -494,13 +565,10 @@ def run_ours(args):
         "status_word": st,
     }
     if world == 1 and not args.no_cpu_baseline:
-        threads = 1
-        dt, cpu_tok_s = time_cpu(args.bank, 3, 1, threads)
-        line["cpu_baseline"] = {"value": cpu_tok_s, "unit": "tok/s", "cores": threads, "kind": "port",
-                                "sample": f"3 timed passes of one MoE layer (6 routed experts from packed bytes, numpy), {dt:.2f} s each; "
-                                          f"a token = {LAYERS} passes"}
+        _, cpu_tok_s, threads, desc = time_cpu_token(args.bank)
+        line["cpu_baseline"] = {"value": cpu_tok_s, "unit": "tok/s", "cores": threads, "kind": "port", "sample": desc}
     print(json.dumps(line), flush=True)
-    _leave(world)
+    _leave(world, (peer_layer, peer_sum))
 
 
 # ---- prefill workload --------------------------------------------------------------------------

@@ -54,8 +54,6 @@ class PeerSum:
         import ctypes
 
         import torch.distributed as dist
-        import torch.distributed._symmetric_memory as symm
-
         from ._lib import lib
 
         self.group = group if group is not None else dist.group.WORLD
@@ -63,12 +61,7 @@ class PeerSum:
         inbox = int(lib.cachalot_peer_sum_inbox_bytes(self.world, n))
         flags = int(lib.cachalot_peer_sum_flag_bytes(self.world))
         self._inbox_bytes = (inbox + 255) // 256 * 256
-        self.buf = symm.empty(self._inbox_bytes + flags, dtype=torch.uint8, device=device)
-        self.buf.zero_()
-        self.handle = symm.rendezvous(self.buf, self.group)
-        torch.cuda.synchronize(device)
-        dist.barrier(self.group)   # every inbox is zeroed before anyone writes into it
-        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.buf, self.handle, ptrs = _symmetric_buffer(self._inbox_bytes + flags, device, self.group)
         arr = ctypes.c_void_p * self.world
         self._inbox = arr(*ptrs)
         self._flags = arr(*[p + self._inbox_bytes for p in ptrs])
@@ -84,6 +77,73 @@ class PeerSum:
         check(lib.cachalot_peer_sum(self._inbox, self._flags, self.world, self.rank, partial.data_ptr(), out.data_ptr(), self.n,
                                     self.epoch.data_ptr(), status.data_ptr() if status is not None else None, stream))
         return out
+
+    def close(self):
+        """Drop the mapping together with the peers: call on every rank, with no exchange in flight."""
+        import torch.distributed as dist
+
+        torch.cuda.synchronize(self.buf.device)
+        dist.barrier(self.group)
+        self.handle = None
+        self.buf = None
+
+
+def _symmetric_buffer(nbytes: int, device, group):
+    """A zeroed uint8 buffer every rank of the group can write, and every rank's pointer to it in this process.
+    No multicast object is wanted for it (the kernels use plain peer stores), so the switch that makes
+    torch bind one is turned off before the rendezvous."""
+    import os
+
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm
+
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    buf = symm.empty(nbytes, dtype=torch.uint8, device=device)
+    buf.zero_()
+    handle = symm.rendezvous(buf, group)
+    torch.cuda.synchronize(device)
+    dist.barrier(group)   # every buffer is zeroed before anyone writes into it
+    return buf, handle, [int(p) for p in handle.buffer_ptrs]
+
+
+class PeerLayer:
+    """Peer memory for `moe_layer_decode(..., peer=...)`: the cross-rank sum of an expert-parallel decode layer done
+    in the tail of the expert kernel (`cachalot_moe_layer_decode_peer`).  With `group=None` and no process group it
+    is a one-rank exchange in local memory (the same code path, for single-GPU checks)."""
+
+    def __init__(self, hidden: int, device: torch.device, group=None):
+        import torch.distributed as dist
+
+        from ._lib import PeerCtx, lib
+
+        if dist.is_available() and dist.is_initialized():
+            self.group = group if group is not None else dist.group.WORLD
+            self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        else:
+            self.group, self.world, self.rank = None, 1, 0
+        inbox = (int(lib.cachalot_peer_layer_inbox_bytes(self.world, hidden)) + 255) // 256 * 256
+        flags = int(lib.cachalot_peer_layer_flag_bytes(self.world))
+        if self.world > 1:
+            self.buf, self.handle, ptrs = _symmetric_buffer(inbox + flags, device, self.group)
+        else:
+            self.buf = torch.zeros(inbox + flags, dtype=torch.uint8, device=device)
+            ptrs = [self.buf.data_ptr()]
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=device)
+        ctx = PeerCtx()
+        for r, p in enumerate(ptrs):
+            ctx.inbox[r], ctx.flags[r] = p, p + inbox
+        ctx.epoch, ctx.world, ctx.rank = self.epoch.data_ptr(), self.world, self.rank
+        self.ctx, self.hidden = ctx, hidden
+
+    def close(self):
+        """Drop the mapping together with the peers: call on every rank, with no exchange in flight."""
+        import torch.distributed as dist
+
+        torch.cuda.synchronize(self.buf.device)
+        if self.world > 1:
+            dist.barrier(self.group)
+        self.handle = None
+        self.buf = None
 
 
 def ep_moe_forward(x, slot_ids, gate_weights, bank, *, group=None, **kw) -> torch.Tensor:

@@ -215,12 +215,14 @@ def moe_layer_decode(x: torch.Tensor, logits: torch.Tensor, bank: SlabBank, *, l
                      gate_temp: float = 1.0, route_scale: float = 1.0, norm_topk_prob: bool = True, weights_bf16: bool = False,
                      swiglu_limit: float = 10.0, numerics: str | None = None, out_dtype=torch.float32,
                      out: torch.Tensor | None = None, status: torch.Tensor | None = None,
-                     workspace: torch.Tensor | None = None, want_routing: bool = False):
+                     workspace: torch.Tensor | None = None, want_routing: bool = False, peer=None):
     """Routing tail + routed experts of one decode token as ONE launch: the GPU-side form of the routed half
     of `moe_layer_forward` (model/moe_layer_metal.py:133-405) with slot selection on the device as in
     minimax/gpu_select.py:330-551.  x bf16 [H]; logits float32 [E] (gate output); `table` int32 [layers,E]
     (default: the bank's slot table); router "sigmoid" (route_tail rules) or "sqrt_softplus" (route_topk rules).
-    Returns out [H], or (out, indices int32 [k], weights float32 [k]) with want_routing."""
+    Returns out [H], or (out, indices int32 [k], weights float32 [k]) with want_routing.
+    `peer` (an `ep.PeerLayer`): the bank is this rank's shard of an expert-parallel layer and `out` receives the sum
+    over all ranks, exchanged through peer memory in the tail of the same launch."""
     _need_cuda(x, logits)
     if x.dim() != 1 or x.numel() != bank.hidden:
         raise ValueError(f"x must be 1-D with {bank.hidden} elements, got {tuple(x.shape)}")
@@ -248,6 +250,15 @@ def moe_layer_decode(x: torch.Tensor, logits: torch.Tensor, bank: SlabBank, *, l
     need = lib.cachalot_moe_layer_decode_workspace_bytes(bank.desc_ptr, topk)
     ws = workspace if workspace is not None else _workspace(x.device, need + 256)
     base = (ws.data_ptr() + 255) // 256 * 256
+    if peer is not None:
+        import ctypes as C
+
+        check(lib.cachalot_moe_layer_decode_peer(_ptr(bank.slab), bank.desc_ptr, _ptr(xb), _ptr(lg), _ptr(b), _ptr(table.contiguous()),
+                                                 int(layer), e, int(topk), mode, float(gate_temp), float(route_scale),
+                                                 int(norm_topk_prob), int(weights_bf16), float(swiglu_limit), num, base,
+                                                 ws.numel() - (base - ws.data_ptr()), _ptr(out), odt, _ptr(idx), _ptr(w),
+                                                 C.cast(C.byref(peer.ctx), C.c_void_p), _ptr(status), _stream()))
+        return (out, idx, w) if want_routing else out
     check(lib.cachalot_moe_layer_decode(_ptr(bank.slab), bank.desc_ptr, _ptr(xb), _ptr(lg), _ptr(b), _ptr(table.contiguous()), int(layer),
                                         e, int(topk), mode, float(gate_temp), float(route_scale), int(norm_topk_prob),
                                         int(weights_bf16), float(swiglu_limit), num, base, ws.numel() - (base - ws.data_ptr()),
