@@ -712,13 +712,172 @@ def run_prefill(args):
     _leave(world)
 
 
+# ---- FP8 trunk GEMV workload --------------------------------------------------------------------
+
+FP8_SHAPES = ((12288, 4096), (4096, 8192))
+FP8_BLOCK = 128
+FP8_COPIES = 6      # distinct weight copies of each matrix a step walks through: 503 MB per step, four times L2
+
+
+def fp8_alg_bytes(n, k, batch):
+    return n * k + (n // FP8_BLOCK) * (k // FP8_BLOCK) * 4 + batch * k * 2 + batch * n * 2
+
+
+def time_cpu_fp8(batch):
+    """CPU arm of the FP8 workload: the numpy oracle (act_quant per 1x128 with fp32 scales, block-wise GEMV) over both
+    whole matrices, one token at a time, repeated until about ten seconds have gone.  Returns (GB/s, description)."""
+    import numpy as np
+    from oracle import configs, fp8
+
+    rng = np.random.default_rng(0)
+    work = []
+    for n, k in FP8_SHAPES:
+        w, ws = configs.fp8_matrix(rng, n, k, FP8_BLOCK, "f32")
+        work.append((configs.round_bf16(rng.standard_normal((1, k)).astype(np.float32)), w, ws))
+    fp8.fp8_linear(work[0][0], work[0][1][:128], work[0][2][:1], block_size=FP8_BLOCK, scale_rule="f32")
+    done, tokens, t0 = 0, 0, time.perf_counter()
+    while time.perf_counter() - t0 < 10.0 and tokens < 64:
+        for (n, k), (x, w, ws) in zip(FP8_SHAPES, work):
+            fp8.fp8_linear(x, w, ws, block_size=FP8_BLOCK, scale_rule="f32")
+            done += fp8_alg_bytes(n, k, 1)
+        tokens += 1
+    secs = time.perf_counter() - t0
+    return done / secs / 1e9, f"{tokens} tokens through both whole matrices, one at a time (numpy port, block 128, fp32 scales), {secs:.1f} s"
+
+
+def run_fp8(args):
+    """One step = act_quant + GEMV over FP8_COPIES distinct copies of both trunk matrices ([12288,4096] and [4096,8192],
+    E4M3 weights, fp32 scales per 128x128, activations quantised per 1x128), `--batch` tokens (1 or 32), replayed as
+    one CUDA graph; value = algorithmic GB/s.  One GPU (the trunk GEMV is not sharded)."""
+    import torch
+
+    import cachalot_b200 as cb
+
+    if args.impl == "reference" or int(os.environ.get("WORLD_SIZE", "1")) > 1 and int(os.environ.get("RANK", "0")) != 0:
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        gbs, desc = time_cpu_fp8(args.batch)
+        print(json.dumps({"impl": "reference", "metric": "fp8_trunk_gemv_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": 1,
+                          "warmup": 0, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3",
+                          "data": "synthetic", "config": {"workload": "FP8 E4M3 trunk GEMV with act_quant, block 128, fp32 scales"},
+                          "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port", "sample": desc},
+                          "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+        return
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B = args.batch
+    g = torch.Generator(device=dev).manual_seed(5)
+    finite = torch.tensor([b for b in range(256) if (b & 0x7F) != 0x7F], dtype=torch.uint8, device=dev)
+    mats = []
+    for n, k in FP8_SHAPES:
+        for _ in range(FP8_COPIES):
+            w = finite[torch.randint(0, finite.numel(), (n, k), device=dev, generator=g)]
+            ws = torch.rand((n // FP8_BLOCK, k // FP8_BLOCK), device=dev, generator=g) * 9e-3 + 1e-3
+            mats.append((w, ws))
+    P = 8
+    gi = torch.Generator().manual_seed(3)
+    x_host = [torch.randn((P, B, k), generator=gi).to(torch.bfloat16).pin_memory() for _, k in FP8_SHAPES]
+    x_dev = [t.to(dev) for t in x_host]
+    x = [t[0].clone() for t in x_dev]
+    y = [torch.empty((B, n), dtype=torch.bfloat16, device=dev) for n, _ in FP8_SHAPES]
+    y_host = [torch.empty((B, n), dtype=torch.bfloat16).pin_memory() for n, _ in FP8_SHAPES]
+    codes = [torch.empty((B, k), dtype=torch.uint8, device=dev) for _, k in FP8_SHAPES]
+    scales = [torch.empty((B, k // FP8_BLOCK), dtype=torch.float32, device=dev) for _, k in FP8_SHAPES]
+    from cachalot_b200._lib import check, lib
+    stream = torch.cuda.Stream(device=dev)
+
+    def linear(mi, ci):
+        w, ws = mats[mi * FP8_COPIES + ci]
+        n, k = FP8_SHAPES[mi]
+        check(lib.cachalot_fp8_linear(x[mi].data_ptr(), B, k, FP8_BLOCK, 1, codes[mi].data_ptr(), scales[mi].data_ptr(), w.data_ptr(),
+                                      ws.data_ptr(), n, y[mi].data_ptr(), 1, stream.cuda_stream))
+
+    def graph_of(fn):
+        with torch.cuda.stream(stream):
+            fn()
+            stream.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream):
+                fn()
+        return gr.replay
+
+    step = graph_of(lambda: [linear(mi, ci) for ci in range(FP8_COPIES) for mi in range(2)])
+    only = [graph_of(lambda mi=mi: [linear(mi, ci) for ci in range(FP8_COPIES)]) for mi in range(2)]
+
+    def timed(fn, steps, host=False):
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for i in range(steps):
+                for mi in range(2):
+                    x[mi].copy_((x_host if host else x_dev)[mi][i % P], non_blocking=True)
+                fn()
+                if host:
+                    for mi in range(2):
+                        y_host[mi].copy_(y[mi], non_blocking=True)
+                    stream.synchronize()
+            e1.record(stream)
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1)
+
+    timed(step, max(args.warmup, 3))
+    sampler = ClockSampler(0)
+    sampler.start()
+    first = timed(step, args.steps)
+    n_rep = args.repeats if args.repeats > 0 else int(min(400, max(5, -(-500.0 // max(first, 1e-3)))))
+    all_ms = sorted([first] + [timed(step, args.steps) for _ in range(n_rep - 1)])
+    ms = all_ms[len(all_ms) // 2]
+    ms_e2e = sorted(timed(step, args.steps, True) for _ in range(5))[2]
+    clocks = sampler.stop()
+    per = [sorted(timed(only[mi], args.steps) for _ in range(5))[2] / (args.steps * FP8_COPIES) * 1e3 for mi in range(2)]  # us per linear
+    # parity of what was timed: the last copy of each matrix against the oracle on a few rows
+    import numpy as np
+    from oracle import fp8 as ofp8
+    for mi in range(2):
+        w, ws = mats[mi * FP8_COPIES + FP8_COPIES - 1]
+        rows = slice(0, 256)
+        want = ofp8.fp8_linear(x[mi].float().cpu().numpy(), w[rows].cpu().numpy(), ws[:2].cpu().numpy(), block_size=FP8_BLOCK, scale_rule="f32")
+        got = y[mi][:, rows].float().cpu().numpy()
+        err = float(np.max(np.abs(got - want)) / np.max(np.abs(want)))
+        if not err < 2 ** -7:
+            print(f"fp8 workload: output differs from the oracle ({err:.3e})", file=sys.stderr, flush=True)
+            sys.exit(3)
+    alg = [fp8_alg_bytes(n, k, B) for n, k in FP8_SHAPES]
+    step_bytes = FP8_COPIES * sum(alg)
+    peak, which = measured_peak()
+    gbs = step_bytes * args.steps / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "fp8_trunk_gemv_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "ms_per_step_min": all_ms[0] / args.steps, "repeats": len(all_ms), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
+        "config": {"workload": f"FP8 E4M3 trunk GEMV with act_quant: [12288,4096] and [4096,8192], fp32 scales per 128x128, activations per 1x128, "
+                               f"batch {B}; a step = {FP8_COPIES} distinct copies of both matrices", "batch": B,
+                   "l2": f"inputs larger than L2: a step streams {step_bytes / 1e6:.0f} MB of distinct weights", "cuda_graph": True},
+        "clocks": clocks,
+        "e2e": {"value": step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(sum(B * k * 2 for _, k in FP8_SHAPES)),
+                "d2h_bytes_per_step": int(sum(B * n * 2 for n, _ in FP8_SHAPES))},
+        "gpu_launches": 4 * FP8_COPIES * args.steps,
+        "roofline": {"kernel": "fp8_gemv_stream_kernel (+ act_quant_kernel in front of it)", "bound": "hbm", "achieved": gbs, "peak": peak,
+                     "peak_kind": which, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                     "per_matrix": [{"shape": list(FP8_SHAPES[mi]), "us_per_linear": per[mi], "algorithmic_bytes": alg[mi],
+                                     "achieved": alg[mi] / per[mi] / 1e3, "frac": alg[mi] / per[mi] / 1e3 / peak} for mi in range(2)]},
+    }
+    if not args.no_cpu_baseline:
+        cg, desc = time_cpu_fp8(B)
+        line["cpu_baseline"] = {"value": cg, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port", "sample": desc}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
     if args.watchdog > 0:
         import faulthandler
 
         faulthandler.dump_traceback_later(args.watchdog, exit=True)
-    if args.impl == "reference":
+    if args.workload == "fp8":
+        run_fp8(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif args.workload == "prefill":
         run_prefill(args)

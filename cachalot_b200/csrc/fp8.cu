@@ -1,6 +1,11 @@
 // FP8 E4M3 trunk GEMV with dynamic activation quantisation (act_quant).
 #include <cuda_fp8.h>
 
+#include <cstdlib>
+#include <mutex>
+#include <set>
+#include <utility>
+
 #include "common.cuh"
 
 namespace cachalot {
@@ -17,6 +22,8 @@ __global__ void act_quant_kernel(const __nv_bfloat16* __restrict__ x, int rows, 
                                  uint8_t* __restrict__ codes, float* __restrict__ scales) {
   constexpr int BLOCK = 32 * PER;
   const int nblk = k / BLOCK;
+  // a GEMV launched behind this kernel may start to stream its weights now (it waits for these codes itself)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= (long long)rows * nblk) return;
@@ -49,6 +56,7 @@ __global__ void swiglu_act_quant_kernel(const __nv_bfloat16* __restrict__ gate, 
                                         float* __restrict__ scales) {
   constexpr int BLOCK = 32 * PER;
   const int nblk = k / BLOCK;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= (long long)rows * nblk) return;
@@ -208,6 +216,227 @@ fp8_gemv_mma_kernel(const uint8_t* __restrict__ codes, const float* __restrict__
   }
 }
 
+// ---- streaming GEMV: weight rows through a shared-memory ring --------------------------------------
+// The same arithmetic with the weights brought in by bulk copies instead of per-lane loads: persistent CTAs (one
+// per SM), a tile = 16 output rows over the whole K, cut along K into chunks of KC bytes per row.  Four copy warps
+// (one lane each: the copies of one warp are issued one after the other, and a lane gets through a copy in about
+// 60 ns + bytes / 46 B/ns, so the issuers have to be in different warps and the copies large) bring four rows each:
+// one copy of 4 * K bytes when a stage holds whole rows, else one per row.  Eight MMA warps each take a slice of
+// every stage's K (whole scale blocks) and add their partial sums through shared memory at the end of a tile.
+// Rows 4c..4c+3 of a stage sit 64 bytes (mod 128) from the next four, and MMA row g is tile row
+// (g >> 1) + 4 * (g & 1).  Up to eight tokens have their codes and scales staged in shared memory; more tokens
+// read their codes through L1.  Under programmatic dependent launch the ring starts to fill while the activation
+// quantiser that precedes this kernel is still running: only the staging waits for it.
+constexpr int GS_PROD = 4;   // copy warps
+constexpr int GS_WARPS = 8;  // MMA warps
+constexpr int GS_THREADS = (GS_WARPS + GS_PROD) * 32;
+constexpr int GS_MAX_STAGES = 8;
+constexpr uint32_t GS_WAIT_LIMIT = 1u << 22;
+
+struct GsGeo {
+  int kc;         // bytes of K per stage and row
+  int nkc;        // stages per tile
+  int group_pitch;  // bytes between the four-row groups of a stage: 4 * kc + 64
+  int stage_bytes, n_stage;
+  int tok_pitch;  // bytes between staged tokens
+  int off_ring, off_codes, off_as, off_red, off_bar, total;
+};
+
+__device__ __forceinline__ uint32_t gs_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool gs_wait(uint64_t* b, uint32_t parity) {
+  for (uint32_t i = 0; i < GS_WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(gs_smem(b)), "r"(parity)
+                 : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__host__ __device__ inline int gs_row_off(int r, int kc) { return (r >> 2) * (4 * kc + 64) + (r & 3) * kc; }
+
+template <int NTG, int BLOCK, bool STAGED, typename OutT>
+__global__ void __launch_bounds__(GS_THREADS, 1)
+fp8_gemv_stream_kernel(GsGeo G, const uint8_t* __restrict__ codes, const float* __restrict__ act_scales,
+                       const uint8_t* __restrict__ weight, const void* __restrict__ w_scales, int scale_rule, int rows,
+                       int n_out, int k, OutT* __restrict__ out, long long ldo, const float* __restrict__ addend,
+                       int* __restrict__ status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* ring = smem + G.off_ring;
+  uint8_t* s_codes = smem + G.off_codes;
+  float* s_as = reinterpret_cast<float*>(smem + G.off_as);
+  float* red = reinterpret_cast<float*>(smem + G.off_red);  // [GS_WARPS][NTG][4][32]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + G.off_bar);
+  uint64_t* empty = full + GS_MAX_STAGES;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int tiles = (n_out + 15) / 16;
+  const int tile_lo = (int)((long long)tiles * blockIdx.x / gridDim.x), tile_hi = (int)((long long)tiles * (blockIdx.x + 1) / gridDim.x);
+  const int nkb = k / BLOCK;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GS_MAX_STAGES; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gs_smem(&full[s])), "r"(GS_PROD));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gs_smem(&empty[s])), "r"(GS_WARPS));
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp < GS_PROD) {
+    // ---- copies: warp p brings rows 4p..4p+3 of every stage (the weights do not depend on the previous kernel) ----
+    if (lane == 0) {
+      int s = 0;
+      uint32_t round = 0;
+      bool ok = true;
+      for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
+        const bool whole = G.nkc == 1 && tile * 16 + 16 <= n_out;  // four rows are one contiguous piece
+        for (int c = 0; c < G.nkc; ++c) {
+          if (round > 0 && !gs_wait(&empty[s], (round - 1u) & 1u)) {
+            ok = false;
+            break;
+          }
+          uint8_t* dst = ring + (size_t)s * G.stage_bytes + warp * G.group_pitch;
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(gs_smem(&full[s])), "r"(4u * (uint32_t)G.kc) : "memory");
+          if (whole) {
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(gs_smem(dst)),
+                         "l"(weight + (size_t)(tile * 16 + warp * 4) * k), "r"(4u * (uint32_t)G.kc), "r"(gs_smem(&full[s]))
+                         : "memory");
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int row = min(tile * 16 + warp * 4 + j, n_out - 1);  // rows past the end repeat the last one; never stored
+              asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                               gs_smem(dst + j * G.kc)),
+                           "l"(weight + (size_t)row * k + (size_t)c * G.kc), "r"((uint32_t)G.kc), "r"(gs_smem(&full[s]))
+                           : "memory");
+            }
+          }
+          if (++s == G.n_stage) s = 0, ++round;
+        }
+      }
+      if (!ok && status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
+    }
+    return;
+  }
+  // ---- MMA warps ----
+  const int cw = warp - GS_PROD, tid = threadIdx.x - GS_PROD * 32;
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the codes and scales come from the kernel before this one
+  if (STAGED) {
+    const int per = k / 16;  // 16-byte pieces per token
+    for (int i = tid; i < rows * per; i += GS_WARPS * 32) {
+      const int tok = i / per, p = i - tok * per;
+      *reinterpret_cast<uint4*>(s_codes + (size_t)tok * G.tok_pitch + p * 16) = __ldg(reinterpret_cast<const uint4*>(codes + (size_t)tok * k) + p);
+    }
+    for (int i = tid; i < 8 * nkb; i += GS_WARPS * 32) s_as[i] = i < rows * nkb ? act_scales[i] : 0.f;
+    asm volatile("bar.sync 1, %0;" ::"r"(GS_WARPS * 32) : "memory");
+  }
+  constexpr int MPB = BLOCK / 32;  // MMAs per scale block
+  const int n_u = G.kc / BLOCK;    // scale blocks per stage
+  const int u_lo = n_u * cw / GS_WARPS, u_hi = n_u * (cw + 1) / GS_WARPS;
+  const int wr = (g >> 1) + 4 * (g & 1);  // MMA row g is tile row wr; MMA row g + 8 is tile row wr + 8
+  const int offA = gs_row_off(wr, G.kc) + t * 8, offB = gs_row_off(wr + 8, G.kc) + t * 8;
+  int s = 0;
+  uint32_t round = 0;
+  bool ok = true;
+  for (int tile = tile_lo; tile < tile_hi; ++tile) {
+    float acc[NTG][4];
+#pragma unroll
+    for (int tg = 0; tg < NTG; ++tg) acc[tg][0] = acc[tg][1] = acc[tg][2] = acc[tg][3] = 0.f;
+    const int n0 = tile * 16;
+    const size_t srow = (size_t)(n0 / BLOCK) * nkb;  // the tile's 16 rows share a row of weight scales
+    for (int c = 0; c < G.nkc; ++c) {
+      if (ok && !gs_wait(&full[s], round & 1u)) ok = false;
+      const uint8_t* st = ring + (size_t)s * G.stage_bytes;
+#pragma unroll 2
+      for (int u = u_lo; u < u_hi; ++u) {
+        const int kb = c * n_u + u;
+        float d[NTG][4];
+        // The two NaN codes of E4M3 (0x7F, 0xFF) read as zero.  Masking them out of every weight word would be most of
+        // the loop's instructions, and real weights hold none: the block runs unmasked first, a NaN code shows as a
+        // NaN in the block's sums (NaN times anything, zero included), and only then the block is redone masked.
+        bool masked = false;
+        for (;;) {
+#pragma unroll
+          for (int tg = 0; tg < NTG; ++tg) d[tg][0] = d[tg][1] = d[tg][2] = d[tg][3] = 0.f;
+#pragma unroll
+          for (int m = 0; m < MPB; ++m) {
+            const int ko = u * BLOCK + m * 32;
+            uint2 va = *reinterpret_cast<const uint2*>(st + offA + ko);
+            uint2 vb = *reinterpret_cast<const uint2*>(st + offB + ko);
+            if (masked) {
+              va.x = e4m3x4_nan_to_zero(va.x), va.y = e4m3x4_nan_to_zero(va.y);
+              vb.x = e4m3x4_nan_to_zero(vb.x), vb.y = e4m3x4_nan_to_zero(vb.y);
+            }
+#pragma unroll
+            for (int tg = 0; tg < NTG; ++tg) {
+              uint2 b = make_uint2(0u, 0u);
+              const int tok = tg * 8 + g;
+              if (tok < rows) {
+                if (STAGED) b = *reinterpret_cast<const uint2*>(s_codes + (size_t)tok * G.tok_pitch + c * G.kc + ko + t * 8);
+                else b = __ldg(reinterpret_cast<const uint2*>(codes + (size_t)tok * k + c * G.kc + ko + t * 8));
+              }
+              qmma_e4m3(d[tg], va.x, vb.x, va.y, vb.y, b.x, b.y);
+            }
+          }
+          if (masked) break;
+          float chk = 0.f;
+#pragma unroll
+          for (int tg = 0; tg < NTG; ++tg) chk += (d[tg][0] + d[tg][1]) + (d[tg][2] + d[tg][3]);
+          if (!__any_sync(0xffffffffu, chk != chk)) break;
+          masked = true;
+        }
+        const float ws = scale_rule == CACHALOT_SCALE_E8M0 ? e8m0_to_f32(__ldg(reinterpret_cast<const uint8_t*>(w_scales) + srow + kb))
+                                                            : __ldg(reinterpret_cast<const float*>(w_scales) + srow + kb);
+#pragma unroll
+        for (int tg = 0; tg < NTG; ++tg) {
+          const int t0 = tg * 8 + 2 * t;
+          float s0, s1;
+          if (STAGED) {
+            s0 = s_as[t0 * nkb + kb] * ws, s1 = s_as[(t0 + 1) * nkb + kb] * ws;  // zero for tokens past the end
+          } else {
+            s0 = (t0 < rows ? __ldg(act_scales + (size_t)t0 * nkb + kb) : 0.f) * ws;
+            s1 = (t0 + 1 < rows ? __ldg(act_scales + (size_t)(t0 + 1) * nkb + kb) : 0.f) * ws;
+          }
+          acc[tg][0] = fmaf(d[tg][0], s0, acc[tg][0]);
+          acc[tg][1] = fmaf(d[tg][1], s1, acc[tg][1]);
+          acc[tg][2] = fmaf(d[tg][2], s0, acc[tg][2]);
+          acc[tg][3] = fmaf(d[tg][3], s1, acc[tg][3]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gs_smem(&empty[s])) : "memory");
+      if (++s == G.n_stage) s = 0, ++round;
+    }
+    // add the eight K slices in a fixed order and store.  Two buffers by tile parity: one barrier per tile is enough,
+    // because a warp cannot write the buffer of tile i + 2 before every warp has passed the barrier of tile i + 1,
+    // that is, has read tile i.
+    float* rbuf = red + ((tile - tile_lo) & 1) * (GS_WARPS * NTG * 4 * 32);
+#pragma unroll
+    for (int tg = 0; tg < NTG; ++tg)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) rbuf[((cw * NTG + tg) * 4 + i) * 32 + lane] = acc[tg][i];
+    asm volatile("bar.sync 1, %0;" ::"r"(GS_WARPS * 32) : "memory");
+    // warp w adds and stores accumulator element w & 3 of token group w >> 2
+    for (int job = cw; job < NTG * 4; job += GS_WARPS) {
+      const int tg = job >> 2, i = job & 3;
+      {
+        float v = rbuf[((0 * NTG + tg) * 4 + i) * 32 + lane];
+#pragma unroll
+        for (int w = 1; w < GS_WARPS; ++w) v += rbuf[((w * NTG + tg) * 4 + i) * 32 + lane];
+        const int tok = tg * 8 + 2 * t + (i & 1), row = n0 + wr + (i >> 1) * 8;
+        if (tok < rows && row < n_out) {
+          if (addend) v = bf16_round(v) + addend[(size_t)tok * n_out + row];
+          if constexpr (sizeof(OutT) == 2)
+            out[(size_t)tok * ldo + row] = __float2bfloat16_rn(v);
+          else
+            out[(size_t)tok * ldo + row] = v;
+        }
+      }
+    }
+  }
+  if (!ok && lane == 0 && status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
+}
+
 template <int BLOCK, typename OutT>
 static void launch_gemv_mma(int ntg, cudaStream_t s, const uint8_t* codes, const float* act_scales, const uint8_t* weight,
                             const void* w_scales, int scale_rule, int rows, int n, int k, OutT* out, long long ldo,
@@ -236,6 +465,92 @@ static void launch_gemv_mma(int ntg, cudaStream_t s, const uint8_t* codes, const
 #undef CACHALOT_GEMV
 }
 
+constexpr int GS_SMEM_LIMIT = 227 * 1024 - 256;
+
+// false when the shape is outside what the streaming kernel takes (the per-lane kernel runs then)
+static bool gs_geometry(int rows, int k, int block, int ntg, bool* staged, GsGeo* out) {
+  if (k % block || k % 16) return false;
+  int nkc = 0;
+  for (int n = (k + 4095) / 4096; n <= k / 1024 + 1 && n <= 64; ++n)
+    if (k % n == 0 && (k / n) % block == 0 && (k / n) % 16 == 0) {
+      nkc = n;
+      break;
+    }
+  if (!nkc || k / nkc < 1024) return false;  // short rows: copies of under 1 KB cannot keep HBM busy
+  GsGeo G = {};
+  G.kc = k / nkc, G.nkc = nkc;
+  G.group_pitch = 4 * G.kc + 64;
+  G.stage_bytes = (4 * G.group_pitch + 127) / 128 * 128;
+  G.tok_pitch = k + 32;
+  const int nkb = k / block;
+  int p = 256;  // the barriers
+  G.off_bar = 0;
+  G.off_red = p, p += 2 * GS_WARPS * ntg * 4 * 32 * 4;  // two buffers
+  G.off_as = p, p += (8 * nkb * 4 + 127) / 128 * 128;
+  *staged = rows <= 8 && ntg == 1;
+  G.off_codes = p;
+  if (*staged) p += (rows * G.tok_pitch + 127) / 128 * 128;
+  G.off_ring = p;
+  G.n_stage = (GS_SMEM_LIMIT - p) / G.stage_bytes;
+  if (G.n_stage > GS_MAX_STAGES) G.n_stage = GS_MAX_STAGES;
+  if (G.n_stage < 3) {  // too little room next to the staged tokens: read them through L1 instead
+    if (!*staged) return false;
+    *staged = false;
+    p = G.off_codes, G.off_ring = p;
+    G.n_stage = (GS_SMEM_LIMIT - p) / G.stage_bytes;
+    if (G.n_stage > GS_MAX_STAGES) G.n_stage = GS_MAX_STAGES;
+    if (G.n_stage < 3) return false;
+  }
+  G.total = p + G.n_stage * G.stage_bytes;
+  *out = G;
+  return true;
+}
+
+template <int BLOCK, typename OutT>
+static cudaError_t launch_gemv_stream(const GsGeo& G, bool staged, bool pdl, int ntg, cudaStream_t s, const uint8_t* codes,
+                                      const float* act_scales, const uint8_t* weight, const void* w_scales, int scale_rule,
+                                      int rows, int n, int k, OutT* out, long long ldo, const float* addend, int* status) {
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return e;
+  const int tiles = (n + 15) / 16;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(tiles < sms ? tiles : sms));
+  cfg.blockDim = dim3(GS_THREADS);
+  cfg.dynamicSmemBytes = (size_t)G.total;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl ? 1 : 0;
+  auto go = [&](auto kern) {
+    static std::mutex mu;
+    static std::set<std::pair<const void*, int>> done;  // the shared-memory opt-in is per kernel and device
+    {
+      std::lock_guard<std::mutex> lock(mu);
+      if (!done.count({(const void*)kern, dev})) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GS_SMEM_LIMIT);
+        if (e != cudaSuccess) return;
+        done.insert({(const void*)kern, dev});
+      }
+    }
+    e = cudaLaunchKernelEx(&cfg, kern, G, codes, act_scales, weight, w_scales, scale_rule, rows, n, k, out, ldo, addend, status);
+  };
+  if (ntg == 1) {
+    if (staged) go(fp8_gemv_stream_kernel<1, BLOCK, true, OutT>);
+    else go(fp8_gemv_stream_kernel<1, BLOCK, false, OutT>);
+  } else if (ntg == 2) {
+    go(fp8_gemv_stream_kernel<2, BLOCK, false, OutT>);
+  } else if (ntg <= 4) {
+    go(fp8_gemv_stream_kernel<4, BLOCK, false, OutT>);
+  } else {
+    go(fp8_gemv_stream_kernel<8, BLOCK, false, OutT>);
+  }
+  return e;
+}
+
 }  // namespace cachalot
 
 using namespace cachalot;
@@ -257,9 +572,11 @@ extern "C" int cachalot_fp8_act_quant(const void* x_bf16, int rows, int k, int b
   return check_launch("fp8_act_quant");
 }
 
+// pdl: the kernel directly before this call in the stream is one of this file's quantisers (it writes the codes and
+// scales only), so the GEMV may start streaming weights while it runs
 static int gemv_checked(const char* who, const uint8_t* codes, const float* act_scales, const uint8_t* weight, const void* w_scales,
                         int scale_rule, int block, int rows, int n, int k, void* out, int out_dtype, long long ldo,
-                        const float* addend, cudaStream_t s) {
+                        const float* addend, cudaStream_t s, bool pdl = false, int* status = nullptr) {
   if (!codes || !act_scales || !weight || !w_scales || !out) return fail(CACHALOT_EINVAL, "%s: null pointer", who);
   if (block != 32 && block != 128) return fail(CACHALOT_EUNSUPPORTED, "%s: block=%d (32 or 128)", who, block);
   if (rows < 0 || n <= 0 || k <= 0 || k % block) return fail(CACHALOT_EINVAL, "K=%d is not divisible by %d", k, block);
@@ -275,6 +592,26 @@ static int gemv_checked(const char* who, const uint8_t* codes, const float* act_
     const uint8_t* c = codes + (size_t)r0 * k;
     const float* as = act_scales + (size_t)r0 * (k / block);
     const float* ad = addend ? addend + (size_t)r0 * n : nullptr;
+    static const bool no_stream = [] { const char* e = std::getenv("CACHALOT_FP8_PER_LANE"); return e && e[0] == '1'; }();
+    GsGeo G;
+    bool staged = false;
+    // up to eight tokens; beyond that the activation fragments outweigh the weights and the per-lane kernel, which
+    // shares them between two row tiles, is the faster one (measured at 32 tokens)
+    if (!no_stream && ntg == 1 && gs_geometry(nr, k, block, 1, &staged, &G)) {
+      cudaError_t e;
+      if (out_dtype == CACHALOT_BF16) {
+        __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)r0 * ldo;
+        e = block == 32 ? launch_gemv_stream<32>(G, staged, pdl, ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o, ldo, ad, status)
+                        : launch_gemv_stream<128>(G, staged, pdl, ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o, ldo, ad, status);
+      } else {
+        float* o = (float*)out + (size_t)r0 * ldo;
+        e = block == 32 ? launch_gemv_stream<32>(G, staged, pdl, ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o, ldo, ad, status)
+                        : launch_gemv_stream<128>(G, staged, pdl, ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o, ldo, ad, status);
+      }
+      if (e != cudaSuccess) return fail(CACHALOT_ECUDA, "%s: %s", who, cudaGetErrorString(e));
+      pdl = false;  // a further launch of this call follows a GEMV, not the quantiser
+      continue;
+    }
     if (out_dtype == CACHALOT_BF16) {
       __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)r0 * ldo;
       if (block == 32) launch_gemv_mma<32>(ntg, s, c, as, weight, w_scales, scale_rule, nr, n, k, o, ldo, ad);
@@ -293,6 +630,15 @@ extern "C" int cachalot_fp8_gemv(const uint8_t* codes, const float* act_scales, 
                                  int out_dtype, cachalot_stream_t stream) {
   return gemv_checked("fp8_gemv", codes, act_scales, weight, w_scales, scale_rule, block, rows, n, k, out, out_dtype, n, nullptr,
                       (cudaStream_t)stream);
+}
+
+extern "C" int cachalot_fp8_linear(const void* x_bf16, int rows, int k, int block, int scale_rule, uint8_t* codes, float* scales,
+                                   const uint8_t* weight, const void* w_scales, int n, void* out, int out_dtype,
+                                   cachalot_stream_t stream) {
+  int rc = cachalot_fp8_act_quant(x_bf16, rows, k, block, scale_rule, codes, scales, stream);
+  if (rc) return rc;
+  return gemv_checked("fp8_linear", codes, scales, weight, w_scales, scale_rule, block, rows, n, k, out, out_dtype, n, nullptr,
+                      (cudaStream_t)stream, true);
 }
 
 static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
@@ -329,11 +675,11 @@ extern "C" int cachalot_shared_expert(const void* x_bf16, int rows, int hidden, 
   if (rc) return rc;
   const long long ld = 2LL * inter;
   if (w3) {
-    rc = gemv_checked("shared_expert w1", codes, scales, w1, w1_scales, scale_rule, block, rows, inter, hidden, gu, CACHALOT_BF16, ld, nullptr, s);
+    rc = gemv_checked("shared_expert w1", codes, scales, w1, w1_scales, scale_rule, block, rows, inter, hidden, gu, CACHALOT_BF16, ld, nullptr, s, true);
     if (rc) return rc;
     rc = gemv_checked("shared_expert w3", codes, scales, w3, w3_scales, scale_rule, block, rows, inter, hidden, gu + inter, CACHALOT_BF16, ld, nullptr, s);
   } else {  // w1 holds [2*inter, hidden] = w1 rows, then w3 rows
-    rc = gemv_checked("shared_expert w13", codes, scales, w1, w1_scales, scale_rule, block, rows, 2 * inter, hidden, gu, CACHALOT_BF16, ld, nullptr, s);
+    rc = gemv_checked("shared_expert w13", codes, scales, w1, w1_scales, scale_rule, block, rows, 2 * inter, hidden, gu, CACHALOT_BF16, ld, nullptr, s, true);
   }
   if (rc) return rc;
   {
@@ -343,5 +689,5 @@ extern "C" int cachalot_shared_expert(const void* x_bf16, int rows, int hidden, 
     else swiglu_act_quant_kernel<4><<<blocks, 256, 0, s>>>(gu, gu + inter, ld, rows, inter, scale_rule, swiglu_limit, codes, scales);
     if ((rc = check_launch("shared_expert swiglu"))) return rc;
   }
-  return gemv_checked("shared_expert w2", codes, scales, w2, w2_scales, scale_rule, block, rows, hidden, inter, out_bf16, CACHALOT_BF16, hidden, addend, s);
+  return gemv_checked("shared_expert w2", codes, scales, w2, w2_scales, scale_rule, block, rows, hidden, inter, out_bf16, CACHALOT_BF16, hidden, addend, s, true);
 }

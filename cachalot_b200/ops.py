@@ -385,7 +385,29 @@ def fp8_linear(x: torch.Tensor, weight: torch.Tensor, weight_scales: torch.Tenso
         block, rule = 32, "e8m0"
     else:
         block, rule = weight.shape[1] // weight_scales.shape[1], "f32"
-    return fp8_linear_quantized(quantize_fp8_activation(x, block, rule), weight, weight_scales, out_dtype=out_dtype)
+    _need_cuda(x, weight, weight_scales)
+    if x.dim() not in (1, 2):
+        raise ValueError(f"Decode FP8 activation must be 1D, got {tuple(x.shape)}")
+    if weight.dim() != 2:
+        raise ValueError(f"weight must be 2D, got {tuple(weight.shape)}")
+    n, k = weight.shape
+    if x.shape[-1] != k:
+        raise ValueError(f"weight expects {k} inputs, activation has {x.shape[-1]}")
+    if k % block:
+        raise ValueError(f"K={k} must be divisible by block_size={block}")
+    expected = (-(-n // block), k // block)
+    if tuple(weight_scales.shape) != expected:
+        raise ValueError(f"scale shape {tuple(weight_scales.shape)} != {expected}")
+    x2 = x.reshape(-1, k).to(torch.bfloat16).contiguous()
+    rows = x2.shape[0]
+    codes = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((rows, k // block), dtype=torch.float32, device=x.device)
+    out = torch.empty((rows, n), dtype=out_dtype, device=x.device)
+    odt = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}[out_dtype]
+    if rows:
+        check(lib.cachalot_fp8_linear(_ptr(x2), rows, k, block, _RULE[rule], _ptr(codes), _ptr(scales), _ptr(weight.contiguous()),
+                                      _ptr(weight_scales.contiguous()), n, _ptr(out), odt, _stream()))
+    return out[0] if x.dim() == 1 else out
 
 
 # ---- prefill ----------------------------------------------------------------------------------

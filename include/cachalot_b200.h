@@ -205,6 +205,15 @@ CACHALOT_API int cachalot_fp8_gemv(const uint8_t* codes, const float* act_scales
                       int scale_rule, int block, int rows, int n, int k, void* out, int out_dtype,
                       cachalot_stream_t stream);
 
+/* Replaces model/fp8_linear_metal.py:92-107 fp8_linear: the two calls above as one (act_quant, then the GEMV, which
+ * starts to stream its weights while the quantiser still runs).  codes u8 [rows,K] and scales f32 [rows,K/block]
+ * are the caller's buffers and hold the quantised activation afterwards (another projection of the same
+ * activation can go on with cachalot_fp8_gemv).  The weights must not be written by the kernel that directly
+ * precedes this call in the stream. */
+CACHALOT_API int cachalot_fp8_linear(const void* x_bf16, int rows, int k, int block, int scale_rule, uint8_t* codes, float* scales,
+                        const uint8_t* weight, const void* w_scales, int n, void* out, int out_dtype,
+                        cachalot_stream_t stream);
+
 /* Replaces model/shared_expert_metal.py:45-188 shared_expert_forward / shared_expert_forward_fused (decode, rows = 1)
  * and model/moe_prefill_batched.py:100-125 shared_expert_forward_batched (rows = M): the resident FP8 expert
  *   qx = act_quant(x);  gate = bf16(w1 qx), up = bf16(w3 qx)  (one act_quant for both);

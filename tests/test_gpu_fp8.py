@@ -107,3 +107,25 @@ def test_fp8_errors():
         cb.fp8_linear_quantized(q, torch.zeros((32, 96), dtype=torch.uint8, device="cuda"), torch.zeros((2, 3), dtype=torch.uint8, device="cuda"))
     with pytest.raises(ValueError, match="must be 2D"):
         cb.fp8_linear_quantized(q, torch.zeros(96, dtype=torch.uint8, device="cuda"), torch.zeros((1, 3), dtype=torch.uint8, device="cuda"))
+
+
+@pytest.mark.parametrize("n,k,block,rule,rows", [(64, 4096, 128, "f32", 1), (200, 8192, 128, "f32", 3), (96, 2880, 32, "e8m0", 8),
+                                                 (40, 5120, 32, "e8m0", 1)])
+def test_streaming_gemv_shapes_and_nan_codes(n, k, block, rule, rows):
+    """The ring-fed GEMV (up to eight tokens, rows of at least 1 KB): a partial last tile, K cut into several stages,
+    a K that is not a multiple of 128 bytes, and NaN codes (0x7F / 0xFF) scattered over the weights, which read as
+    zero -- against the oracle on the same bytes with those codes replaced by zero."""
+    import cachalot_b200 as cb
+    rng = np.random.default_rng(n + k)
+    w, ws = configs.fp8_matrix(rng, n, k, block, rule)
+    w = w.copy()
+    hit = rng.integers(0, n * k, 50)
+    w.reshape(-1)[hit] = np.where(rng.integers(0, 2, 50) == 0, 0x7F, 0xFF).astype(np.uint8)
+    clean = np.where((w & 0x7F) == 0x7F, 0, w).astype(np.uint8)
+    x = round_bf16(rng.standard_normal((rows, k)).astype(np.float32))
+    got = cb.fp8_linear(bf16_tensor(x), _cuda(w), _cuda(ws), out_dtype=torch.float32).cpu().numpy()
+    want = fp8.fp8_linear(x, clean, ws, block_size=block, scale_rule=rule)
+    assert np.isfinite(got).all() and max_rel(got, want) < TOL
+    q = cb.quantize_fp8_activation(bf16_tensor(x), block, rule)
+    two = cb.fp8_linear_quantized(q, _cuda(w), _cuda(ws), out_dtype=torch.float32).cpu().numpy()
+    assert np.array_equal(two, got)
