@@ -527,6 +527,16 @@ def run_ours(args):
                     "traffic": NCU_TRAFFIC_BYTES.get((args.bank, B, "fused")) if world == 1 else None,
                     "us_per_launch_routing_done_beforehand": ms_layer * 1e3}
         launches = LAYERS * args.steps              # routing tail + experts = one launch per layer
+    elif fused and args.bank == "fp4" and B >= int(os.environ.get("CACHALOT_GROUPED_MIN_ROWS", "8")):
+        # FP4 bank from eight tokens up: rows grouped by expert, every distinct expert streamed once by the two grouped
+        # block-scaled GEMMs (planning, residual quantiser, gate/up, down, combine: six launches after the routing one)
+        us_layer = ms_layer * 1e3
+        gbs = layer_bytes / (us_layer * 1e-6) / 1e9
+        roofline = {"kernel": "grouped_mxf4_kernel x2 (gate/up, down) + planning, residual quantiser, combine; one layer, routing done beforehand",
+                    "bound": "hbm", "achieved": gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": gbs / peak,
+                    "us_per_launch": us_layer, "algorithmic_bytes_per_launch": layer_bytes, "distinct_experts_per_layer": u_per_layer,
+                    "traffic": None}
+        launches = 7 * LAYERS * args.steps
     elif fused:
         # a few tokens: per layer one routing launch and B launches of the single-token kernel (k experts each)
         launch_bytes = K * (up_bytes + dn_bytes) / max(world, 1) + HIDDEN * 2 + HIDDEN * 4

@@ -89,5 +89,10 @@ int launch_prefill_rows(const BankView& v, const uint8_t* x_codes, const uint8_t
 size_t prefill_rows_workspace_bytes(int inter, long long rows, int n_seg);
 int launch_combine_rows(const __nv_bfloat16* y, const int32_t* inv, int tokens, int k, int hidden, float* out, cudaStream_t stream);
 bool prefill_tc_supported(const BankView& v);
+// decode batches through the same grouped kernels (FP4 bank, fp32 numerics), every distinct expert streamed once
+int launch_decode_tc(const BankView& v, const void* x_bf16, const int32_t* slots, const float* gate_w, int rows, int k, float limit,
+                     void* workspace, void* out, int out_dtype, int* status, cudaStream_t stream);
+size_t decode_tc_workspace_bytes(int hidden, int inter, int rows, int k);
+bool decode_tc_supported(const BankView& v, int rows, int k);
 
 }  // namespace cachalot

@@ -5,6 +5,7 @@
 // Weights are read as 16-byte chunks straight from the slot record (FP4: 32 codes + one E8M0
 // byte; 2-bit affine: 64 codes, scale/bias per group), activations sit in shared memory in a
 // chunk-transposed order so that a warp's lanes hit distinct banks.
+#include <cstdlib>
 #include <mutex>
 
 #include "kernels.cuh"
@@ -271,11 +272,30 @@ using namespace cachalot;
 #endif
 static constexpr int FUSED_PER_TOKEN_MAX_ROWS = CB_FUSED_PER_TOKEN_MAX_ROWS;
 
+// FP4 bank, fp32 numerics, from this many tokens: rows grouped by expert on the block-scaled tensor cores, every distinct
+// expert streamed once (below it, one single-launch kernel per token is faster)
+#ifndef CB_GROUPED_TC_MIN_ROWS
+#define CB_GROUPED_TC_MIN_ROWS 8
+#endif
+static int grouped_tc_min_rows() {  // CACHALOT_GROUPED_MIN_ROWS overrides the built-in threshold (for measurements)
+  static const int v = [] {
+    const char* e = std::getenv("CACHALOT_GROUPED_MIN_ROWS");
+    const int n = e ? std::atoi(e) : 0;
+    return n > 0 ? n : CB_GROUPED_TC_MIN_ROWS;
+  }();
+  return v;
+}
+#define GROUPED_TC_MIN_ROWS grouped_tc_min_rows()
+
 extern "C" size_t cachalot_moe_decode_workspace_bytes(const cachalot_bank_desc* desc, int rows, int k) {
   if (!desc || rows <= 0 || k <= 0) return 0;
   const size_t a = decode_mma_workspace_bytes(desc->hidden, desc->inter, rows, k);  // >= the simple kernels' rows*k*inter floats
   const size_t b = decode_fused_workspace_bytes(desc->hidden, desc->inter, rows, k);
-  return a > b ? a : b;
+  size_t c = 0;
+  if (desc->format == CACHALOT_BANK_FP4 && rows >= GROUPED_TC_MIN_ROWS && (long long)rows * k <= 1024)
+    c = decode_tc_workspace_bytes(desc->hidden, desc->inter, rows, k);
+  const size_t m = a > b ? a : b;
+  return m > c ? m : c;
 }
 
 extern "C" int cachalot_moe_decode(const void* bank, const cachalot_bank_desc* desc, const void* x_bf16,
@@ -298,6 +318,9 @@ extern "C" int cachalot_moe_decode(const void* bank, const cachalot_bank_desc* d
   const bool fused_ok = !(numerics & (CACHALOT_DECODE_SIMPLE | CACHALOT_DECODE_UNFUSED | CACHALOT_DECODE_ONLY_GATE_UP | CACHALOT_DECODE_ONLY_DOWN));
   if (fused_ok && decode_fused_supported(v, rows, k))
     return launch_decode_fused(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, numerics, workspace, out, out_dtype, status, (cudaStream_t)stream);
+  if (fused_ok && rows >= GROUPED_TC_MIN_ROWS && (numerics & 0xff) == CACHALOT_NUMERICS_F32 && v.format == CACHALOT_BANK_FP4 &&
+      decode_tc_supported(v, rows, k))
+    return launch_decode_tc(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, workspace, out, out_dtype, status, (cudaStream_t)stream);
   // Up to 64 tokens: one single-launch kernel per token, back to back.  Tokens share few experts at these sizes (384
   // routed rows touch about 244 of 384 experts), so grouping rows by expert saves less than the per-token kernel
   // gains by streaming its experts about twice as fast as the grouped kernels (measured: FP4 bank, 8 tokens 0.29 ms

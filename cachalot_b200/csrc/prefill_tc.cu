@@ -157,6 +157,7 @@ struct GemmArgs {
   uint8_t* h_scales;          // u8 [R, N/32]
   // down epilogue
   __nv_bfloat16* y;           // bf16 [R, N]
+  float* y32;                 // TERMS > 1: f32 [R / TERMS, N], one row per routed row
   int* status;
 };
 
@@ -205,7 +206,12 @@ __device__ __forceinline__ uint4 load_sf16(const uint8_t* row, int kb0, int nkb,
 // RAW: the scale bytes of an item (contiguous in the bank: 128 rows of K/32 bytes per matrix, and the unit's
 // rows of the activation scales) are bulk-copied into shared memory one item ahead and the loader warps read
 // them from there; otherwise the loader warps read their rows from global memory (one row per lane).
-template <int NA, int NSTAGE, int KSUB, bool RAW>
+// TERMS = 1: prefill numerics (activations are MXFP4 by definition; g, u rounded to bf16; outputs bf16).
+// TERMS = 4: decode numerics.  Every routed row arrives as four consecutive MXFP4 rows whose sum is the row to
+// within 6**-4 of its block maxima (each row quantises what the rows before it left over, with its own block
+// scales), so the MMAs see the bf16 / fp32 activation almost exactly; the drain adds the four columns, keeps fp32
+// throughout and writes the hidden activation as four residual rows again, the output as one fp32 row.
+template <int NA, int NSTAGE, int KSUB, bool RAW, int TERMS = 1>
 __global__ void __launch_bounds__(NTHREADS, 1)
 grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
                     const __grid_constant__ CUtensorMap map_b, GemmArgs A) {
@@ -531,9 +537,45 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
         tc_ld16(lane_base + buf * ACC_COLS + j0, g);
         if (NA == 2) tc_ld16(lane_base + buf * ACC_COLS + NTMAX + j0, up);
         float wv = 0.f;
-        if (NA == 2 && lane < 16 && j0 + lane < u.ntok) wv = A.row_w[u.row_start + j0 + lane];
+        if (TERMS == 1) {
+          if (NA == 2 && lane < 16 && j0 + lane < u.ntok) wv = A.row_w[u.row_start + j0 + lane];
+        } else {
+          if (NA == 2 && lane < 16 / TERMS && j0 + lane * TERMS < u.ntok) wv = A.row_w[(u.row_start + j0) / TERMS + lane];
+        }
         tc_ld_wait();
         if (!rows_ok) continue;
+        if constexpr (TERMS > 1) {
+#pragma unroll
+          for (int r = 0; r < 16 / TERMS; ++r) {
+            if (j0 + r * TERMS >= u.ntok) break;
+            const size_t rr = (size_t)(u.row_start + j0) / TERMS + r;  // routed row
+            float gs = 0.f, us = 0.f;
+#pragma unroll
+            for (int tt = 0; tt < TERMS; ++tt) {
+              gs += __uint_as_float(g[r * TERMS + tt]);
+              if (NA == 2) us += __uint_as_float(up[r * TERMS + tt]);
+            }
+            if (NA == 2) {
+              float res = swiglu(gs, us, A.limit) * __shfl_sync(0xffffffffu, wv, r);
+#pragma unroll
+              for (int tt = 0; tt < TERMS; ++tt) {
+                const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(res))));
+                const int e = mxfp4_exponent(amax);
+                const float qv = res * pow2f(-e);
+                const float qn = __shfl_down_sync(0xffffffffu, qv, 1);
+                const uint32_t byte = e2m1x2_byte(qv, qn);
+                const uint32_t pair = __shfl_sync(0xffffffffu, byte, lane & ~1);
+                const uint32_t code = (lane & 1) ? pair >> 4 : pair & 15u;
+                res -= e2m1_to_f32(code) * pow2f(e);
+                const size_t row = rr * TERMS + tt;
+                if ((lane & 1) == 0) A.h_codes[row * (size_t)(A.n_rows / 2) + (n >> 1)] = (uint8_t)byte;
+                if (lane == 0) A.h_scales[row * (size_t)(A.n_rows / 32) + (n >> 5)] = (uint8_t)(e + 127);
+              }
+            } else {
+              A.y32[rr * (size_t)A.n_rows + n] = gs;
+            }
+          }
+        } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           if (j0 + j >= u.ntok) break;
@@ -555,6 +597,7 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
           } else {
             A.y[row * (size_t)A.n_rows + n] = __float2bfloat16_rn(__uint_as_float(g[j]));
           }
+        }
         }
       }
       tc_fence_before();
@@ -763,7 +806,212 @@ Scratch carve(uint8_t* base, int hidden, int inter, size_t rows, int n_experts) 
   return s;
 }
 
+// ---- decode batches on the same grouped kernels ------------------------------------------------------
+
+constexpr int DTERMS = 4;  // MXFP4 rows per routed row
+
+// single CTA: routed rows (token * k + route slot) ordered by bank slot, stable; runs of one slot become segments of
+// DTERMS rows per routed row.  seg_off i32 [R + 1] (in MXFP4 rows), seg_slot i32 [R] (-1 behind the last segment and
+// for rows whose slot is absent or out of range), inv i32 [R] (position of a routed row in the order, -1 if absent),
+// src_token i32 [R] and row_w f32 [R] in the order.
+__global__ void decode_plan_kernel(const int32_t* __restrict__ slots, const float* __restrict__ gate_w, int R, int k, int n_slots,
+                                   int32_t* __restrict__ seg_off, int32_t* __restrict__ seg_slot, int32_t* __restrict__ inv,
+                                   int32_t* __restrict__ src_token, float* __restrict__ row_w, int* __restrict__ status) {
+  extern __shared__ int32_t sh[];  // [R] slot of every row, [R] slot by position
+  int32_t* s_in = sh;
+  int32_t* s_sorted = sh + R;
+  bool oob = false;
+  for (int i = threadIdx.x; i < R; i += blockDim.x) {
+    int v = slots[i];
+    if (v >= n_slots) oob = true, v = -1;
+    s_in[i] = v < 0 ? -1 : v;
+  }
+  if (oob && status) atomicOr(status, CACHALOT_STATUS_SLOT_RANGE);
+  __syncthreads();
+  for (int i = threadIdx.x; i < R; i += blockDim.x) {
+    const int v = s_in[i];
+    int rank = 0;
+    for (int j = 0; j < R; ++j) {
+      const int o = s_in[j];
+      rank += (o < v || (o == v && j < i)) ? 1 : 0;
+    }
+    s_sorted[rank] = v;
+    inv[i] = v < 0 ? -1 : rank;
+    src_token[rank] = i / k;
+    row_w[rank] = gate_w[i];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int ng = 0;
+    for (int i = 0; i < R; ++i)
+      if (i == 0 || s_sorted[i] != s_sorted[i - 1]) {
+        seg_off[ng] = i * DTERMS;
+        seg_slot[ng] = s_sorted[i];
+        ++ng;
+      }
+    for (int gidx = ng; gidx <= R; ++gidx) {
+      seg_off[gidx] = R * DTERMS;
+      if (gidx < R) seg_slot[gidx] = -1;
+    }
+  }
+}
+
+// One warp per (routed row, block of 32): the block as DTERMS MXFP4 blocks, each the quantisation (reference rule:
+// model/fp4_act_mlx.py:101-250) of what the ones before it left over.  x bf16 [tokens, K]; row p reads token src[p].
+__global__ void mxfp4_residual_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ src, int rows, int k,
+                                            uint8_t* __restrict__ codes, uint8_t* __restrict__ scales) {
+  const int nblk = k / 32;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= (long long)rows * nblk) return;
+  const long long p = warp / nblk;
+  const int b = (int)(warp - p * nblk);
+  float res = __bfloat162float(x[(size_t)src[p] * k + b * 32 + lane]);
+#pragma unroll
+  for (int tt = 0; tt < DTERMS; ++tt) {
+    const float amax = warp_max(fabsf(res));
+    const int e = mxfp4_exponent(amax);
+    const float qv = res * pow2f(-e);
+    const float qn = __shfl_down_sync(0xffffffffu, qv, 1);
+    const uint32_t byte = e2m1x2_byte(qv, qn);
+    const uint32_t pair = __shfl_sync(0xffffffffu, byte, lane & ~1);
+    const uint32_t code = (lane & 1) ? pair >> 4 : pair & 15u;
+    res -= e2m1_to_f32(code) * pow2f(e);
+    const size_t row = (size_t)p * DTERMS + tt;
+    if ((lane & 1) == 0) codes[row * (size_t)(k / 2) + b * 16 + (lane >> 1)] = (uint8_t)byte;
+    if (lane == 0) scales[row * (size_t)nblk + b] = (uint8_t)(e + 127);
+  }
+}
+
+// out[t, :] = sum over the token's route slots j = 0..k-1 (in that order) of its fp32 row
+template <typename OutT>
+__global__ void decode_combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ inv, int k, int hidden, OutT* __restrict__ out) {
+  const int t = blockIdx.x;
+  for (int n = threadIdx.x; n < hidden; n += blockDim.x) {
+    float a = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const int p = inv[t * k + j];
+      if (p >= 0) a += y[(size_t)p * hidden + n];
+    }
+    if constexpr (sizeof(OutT) == 2)
+      out[(size_t)t * hidden + n] = __float2bfloat16_rn(a);
+    else
+      out[(size_t)t * hidden + n] = a;
+  }
+}
+
+struct DecodeScratch {
+  int32_t *seg_off, *seg_slot, *inv, *src_token, *n_units;
+  float *row_w, *y32;
+  uint8_t *x_codes, *x_scales, *h_codes, *h_scales;
+  Unit* units;
+  size_t total;
+};
+DecodeScratch carve_decode(uint8_t* base, int hidden, int inter, size_t R) {
+  DecodeScratch s;
+  size_t at = 0;
+  auto take = [&](size_t bytes) {
+    uint8_t* p = base ? base + at : nullptr;
+    at += align_up(bytes, 256);
+    return p;
+  };
+  const size_t Q = R * DTERMS;
+  s.seg_off = reinterpret_cast<int32_t*>(take((R + 1) * 4));
+  s.seg_slot = reinterpret_cast<int32_t*>(take(R * 4));
+  s.inv = reinterpret_cast<int32_t*>(take(R * 4));
+  s.src_token = reinterpret_cast<int32_t*>(take(R * 4));
+  s.row_w = reinterpret_cast<float*>(take(R * 4));
+  s.n_units = reinterpret_cast<int32_t*>(take(256));
+  s.units = reinterpret_cast<Unit*>(take((Q / NTMAX + R + 1) * sizeof(Unit)));
+  s.x_codes = take(Q * (hidden / 2));
+  s.x_scales = take(Q * (hidden / 32) + 32);
+  s.h_codes = take(Q * (inter / 2));
+  s.h_scales = take(Q * (inter / 32) + 32);
+  s.y32 = reinterpret_cast<float*>(take(R * (size_t)hidden * 4));
+  s.total = at;
+  return s;
+}
+
 }  // namespace
+
+bool decode_tc_supported(const BankView& v, int rows, int k) {
+  return prefill_tc_supported(v) && rows >= 1 && (long long)rows * k <= 1024;
+}
+size_t decode_tc_workspace_bytes(int hidden, int inter, int rows, int k) { return carve_decode(nullptr, hidden, inter, (size_t)rows * k).total; }
+
+// Routed experts of a decode batch with every distinct expert streamed once: rows grouped by bank slot, activations as
+// DTERMS residual MXFP4 rows, the two grouped block-scaled GEMMs, slot-ordered fp32 sum.  fp32 numerics (the FP4 decode op).
+int launch_decode_tc(const BankView& v, const void* x_bf16, const int32_t* slots, const float* gate_w, int rows, int k, float limit,
+                     void* workspace, void* out, int out_dtype, int* status, cudaStream_t stream) {
+  if (!decode_tc_supported(v, rows, k)) return CACHALOT_EUNSUPPORTED;
+  const int H = v.hidden, I = v.inter, R = rows * k;
+  const long long Q = (long long)R * DTERMS;
+  const DecodeScratch s = carve_decode(static_cast<uint8_t*>(workspace), H, I, (size_t)R);
+  const int threads = R < 1024 ? ((R + 31) / 32) * 32 : 1024;
+  decode_plan_kernel<<<1, threads, 2 * R * sizeof(int32_t), stream>>>(slots, gate_w, R, k, v.n_slots, s.seg_off, s.seg_slot, s.inv, s.src_token,
+                                                                    s.row_w, status);
+  {
+    const long long warps = (long long)R * (H / 32);
+    mxfp4_residual_quant_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x_bf16, s.src_token, R, H,
+                                                                                      s.x_codes, s.x_scales);
+  }
+  plan_units_kernel<<<1, 256, 256 * sizeof(int32_t), stream>>>(s.seg_off, s.seg_slot, R, v.n_slots, s.units, s.n_units);
+  int rc;
+  if ((rc = check_launch("moe_decode (grouped) plan"))) return rc;
+  CUtensorMap m_w1, m_w3, m_w2, m_x, m_h;
+  if ((rc = make_map(&m_w1, v.base + v.off[0], H / 2, H / 2, I, v.record_bytes, v.n_slots, BM))) return rc;
+  if ((rc = make_map(&m_w3, v.base + v.off[4], H / 2, H / 2, I, v.record_bytes, v.n_slots, BM))) return rc;
+  if ((rc = make_map(&m_w2, v.base + v.off[2], I / 2, I / 2, H, v.record_bytes, v.n_slots, BM))) return rc;
+  if ((rc = make_map(&m_x, s.x_codes, H / 2, H / 2, (int)Q, 0, 0, NTMAX))) return rc;
+  if ((rc = make_map(&m_h, s.h_codes, I / 2, I / 2, (int)Q, 0, 0, NTMAX))) return rc;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  auto launch = [&](auto kern, int na, int nstage, bool raw, const CUtensorMap& ma0, const CUtensorMap& ma1, const CUtensorMap& mb,
+                    const GemmArgs& ga) {
+    const size_t sm = smem_bytes(na, nstage, ga.k_codes / 32, raw);
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    kern<<<sms, NTHREADS, sm, stream>>>(ma0, ma1, mb, ga);
+  };
+  GemmArgs a = {};
+  a.bank = v.base;
+  a.record_bytes = v.record_bytes;
+  a.units = s.units;
+  a.n_units = s.n_units;
+  a.total_rows = (int)Q;
+  a.row_w = s.row_w;
+  a.limit = limit;
+  a.h_codes = s.h_codes;
+  a.h_scales = s.h_scales;
+  a.y = nullptr;
+  a.y32 = s.y32;
+  a.status = status;
+  a.off_sc[0] = v.off[1];
+  a.off_sc[1] = v.off[5];
+  a.act_scales = s.x_scales;
+  a.n_rows = I;
+  a.k_codes = H;
+  if (smem_bytes(2, STAGES_GU, H / 32, true) <= SMEM_LIMIT)
+    launch(grouped_mxf4_kernel<2, STAGES_GU, KSUB, true, DTERMS>, 2, STAGES_GU, true, m_w1, m_w3, m_x, a);
+  else
+    launch(grouped_mxf4_kernel<2, STAGES_GU, KSUB, false, DTERMS>, 2, STAGES_GU, false, m_w1, m_w3, m_x, a);
+  if ((rc = check_launch("moe_decode (grouped) gate/up"))) return rc;
+  a.off_sc[0] = v.off[3];
+  a.off_sc[1] = v.off[3];
+  a.act_scales = s.h_scales;
+  a.n_rows = H;
+  a.k_codes = I;
+  if (smem_bytes(1, STAGES_DN, I / 32, true) <= SMEM_LIMIT)
+    launch(grouped_mxf4_kernel<1, STAGES_DN, KSUB, true, DTERMS>, 1, STAGES_DN, true, m_w2, m_w2, m_h, a);
+  else
+    launch(grouped_mxf4_kernel<1, STAGES_DN, KSUB, false, DTERMS>, 1, STAGES_DN, false, m_w2, m_w2, m_h, a);
+  if ((rc = check_launch("moe_decode (grouped) down"))) return rc;
+  if (out_dtype == CACHALOT_BF16)
+    decode_combine_kernel<<<rows, 256, 0, stream>>>(s.y32, s.inv, k, H, static_cast<__nv_bfloat16*>(out));
+  else
+    decode_combine_kernel<<<rows, 256, 0, stream>>>(s.y32, s.inv, k, H, static_cast<float*>(out));
+  return check_launch("moe_decode (grouped) combine");
+}
 
 bool prefill_tc_supported(const BankView& v) {
   // inter a multiple of 64: rows of scale bytes start on even addresses (the loaders read them in 2-byte units)
