@@ -15,9 +15,10 @@ _OPS = (
     "quantize_fp8_activation", "quantize_mxfp4", "route_tail", "route_topk", "route_topk_fused", "route_topk_rows",
     "routed_expert_forward", "router_logits", "routed_expert_forward_batched", "routed_expert_forward_sgmm",
     "affine_expert_forward_batched", "SlabExperts", "shared_expert_forward", "shared_expert_forward_fused",
-    "shared_expert_forward_batched", "fp8_linear_rows", "fused_qr_kv_linear", "moe_layer_forward",
+    "shared_expert_forward_batched", "fp8_linear_rows", "fused_qr_kv_linear", "moe_layer_forward", "validate_routing", "self_check",
 )
-__all__ = [*_BANK, *_OPS, "NUMERICS_VERSION"]
+_LOADER = ("load_bank", "detect_expert_bank", "build_expert_index", "build_stacked_expert_index")
+__all__ = [*_BANK, *_OPS, *_LOADER, "NUMERICS_VERSION"]
 
 
 def __getattr__(name):
@@ -27,4 +28,6 @@ def __getattr__(name):
         return getattr(importlib.import_module(".bank", __name__), name)
     if name in _OPS:
         return getattr(importlib.import_module(".ops", __name__), name)
+    if name in _LOADER:
+        return getattr(importlib.import_module(".loader", __name__), name)
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -19,7 +19,7 @@ NUMERICS_F32, NUMERICS_BF16, NUMERICS_BF16_H32 = 0, 1, 2
 DECODE_ONLY_GATE_UP, DECODE_ONLY_DOWN, DECODE_SIMPLE, DECODE_UNFUSED = 0x100, 0x200, 0x400, 0x800
 ROUTER_SQRT_SOFTPLUS, ROUTER_SIGMOID = 0, 1
 SCALE_E8M0, SCALE_F32 = 0, 1
-STATUS_SLOT_RANGE, STATUS_ID_RANGE, STATUS_SCALE_RANGE, STATUS_WAIT_EXPIRED = 1, 2, 4, 8
+STATUS_SLOT_RANGE, STATUS_ID_RANGE, STATUS_SCALE_RANGE, STATUS_WAIT_EXPIRED, STATUS_BAD_WEIGHT = 1, 2, 4, 8, 16
 
 
 class BankDesc(C.Structure):

@@ -559,6 +559,8 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
     }
     const bool oob = lane < k && my_slot >= bank.n_slots;
     if (__any_sync(0xffffffffu, oob) && lane == 0 && blockIdx.x == 0 && status) atomicOr(status, CACHALOT_STATUS_SLOT_RANGE);
+    const bool bad_w = lane < k && !(fabsf(my_w) <= 3.0e38f);  // NaN or infinite
+    if (__any_sync(0xffffffffu, bad_w) && lane == 0 && blockIdx.x == 0 && status) atomicOr(status, CACHALOT_STATUS_BAD_WEIGHT);
     if (lane == 0) s_np = __popc(pmask);
   }
   __syncthreads();

@@ -838,7 +838,9 @@ __global__ void decode_plan_kernel(const int32_t* __restrict__ slots, const floa
     s_sorted[rank] = v;
     inv[i] = v < 0 ? -1 : rank;
     src_token[rank] = i / k;
-    row_w[rank] = gate_w[i];
+    const float w = gate_w[i];
+    if (!(fabsf(w) <= 3.0e38f) && status) atomicOr(status, CACHALOT_STATUS_BAD_WEIGHT);
+    row_w[rank] = w;
   }
   __syncthreads();
   if (threadIdx.x == 0) {

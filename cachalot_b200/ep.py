@@ -153,12 +153,20 @@ def ep_moe_forward(x, slot_ids, gate_weights, bank, *, group=None, **kw) -> torc
     return reduce_partials(moe_forward(x, slot_ids, gate_weights, bank, **kw), group)
 
 
+class ExchangeError(RuntimeError):
+    """A collective of the expert-parallel exchange did not complete (a peer left, or the group's timeout ran out).
+    The ranks that are still there get this instead of a result; nothing of the step's output is valid."""
+
+
 def _all_to_all_rows(send: torch.Tensor, send_rows: list[int], recv_rows: list[int], group) -> torch.Tensor:
     """Variable all-to-all over the leading dimension: block d of `send` (send_rows[d] rows) goes to rank d."""
     import torch.distributed as dist
 
     recv = torch.empty((sum(recv_rows), *send.shape[1:]), dtype=send.dtype, device=send.device)
-    dist.all_to_all_single(recv, send.contiguous(), output_split_sizes=recv_rows, input_split_sizes=send_rows, group=group)
+    try:
+        dist.all_to_all_single(recv, send.contiguous(), output_split_sizes=recv_rows, input_split_sizes=send_rows, group=group)
+    except Exception as exc:  # torch raises backend-specific types (DistBackendError, RuntimeError, ...)
+        raise ExchangeError(f"expert-parallel exchange failed: {type(exc).__name__}: {exc}") from exc
     return recv
 
 
@@ -169,7 +177,8 @@ def ep_moe_prefill(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Ten
     a local slot (-1 for experts of other ranks).  Returns float32 [T_local,H].
 
     Rows are grouped by global expert, quantised to MXFP4 (codes + scale bytes: 0.53 bytes per element cross
-    NVLink instead of 2), dispatched to the owners of their experts with a variable all-to-all, run through
+    NVLink instead of 2), dispatched to the owners of their experts with one variable all-to-all of packed records
+    (codes, scale bytes and the row's router weight), run through
     the grouped FP4 GEMMs there, sent back as bf16 rows and summed per token in route-slot order -- the same
     arithmetic and the same order as `moe_prefill_grouped(mxfp4_act=1)` on one GPU.
 
@@ -195,14 +204,24 @@ def ep_moe_prefill(x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Ten
     counts[:n_experts] = (offsets[1:] - offsets[:-1]).to(torch.int64)
     send_counts = counts.view(world, per)
     recv_counts = torch.empty_like(send_counts)
-    dist.all_to_all_single(recv_counts, send_counts.contiguous(), group=group)
+    try:
+        dist.all_to_all_single(recv_counts, send_counts.contiguous(), group=group)
+    except Exception as exc:
+        raise ExchangeError(f"expert-parallel exchange failed: {type(exc).__name__}: {exc}") from exc
     send_rows = send_counts.sum(1).tolist()   # host sync: the collective needs the split sizes
     recv_rows = recv_counts.sum(1).tolist()
     kept = sum(send_rows)                      # rows with an expert id in range (the others were dropped by the grouping)
 
-    r_codes = _all_to_all_rows(codes[:kept], send_rows, recv_rows, group)
-    r_scales = _all_to_all_rows(scales[:kept], send_rows, recv_rows, group)
-    r_w = _all_to_all_rows(row_w[:kept], send_rows, recv_rows, group)
+    # one record per row -- codes, scale bytes, router weight -- so that one collective carries the dispatch
+    nc, ns = codes.shape[1], scales.shape[1]
+    record = torch.empty((kept, nc + ns + 4), dtype=torch.uint8, device=dev)
+    record[:, :nc] = codes[:kept]
+    record[:, nc:nc + ns] = scales[:kept]
+    record[:, nc + ns:] = row_w[:kept].contiguous().view(torch.uint8).reshape(kept, 4)
+    arrived = _all_to_all_rows(record, send_rows, recv_rows, group)
+    r_codes = arrived[:, :nc].contiguous()
+    r_scales = arrived[:, nc:nc + ns].contiguous()
+    r_w = arrived[:, nc + ns:].contiguous().view(torch.float32).reshape(-1)
 
     # what arrived is ordered by source rank, then by local expert: one segment per (source, expert)
     seg_offsets = torch.zeros(world * per + 1, dtype=torch.int32, device=dev)

@@ -191,7 +191,7 @@ def moe_forward(x: torch.Tensor, slot_ids: torch.Tensor, gate_weights: torch.Ten
         numerics = "f32" if bank.fmt.kind == "fp4" else "bf16"
     num = {"f32": _lib.NUMERICS_F32, "bf16": _lib.NUMERICS_BF16, "bf16_h32": _lib.NUMERICS_BF16_H32}[numerics]
     num |= {None: 0, "gate_up": _lib.DECODE_ONLY_GATE_UP, "down": _lib.DECODE_ONLY_DOWN}[phase]
-    if simple:
+    if simple or FORCE_SIMPLE_KERNELS:
         num |= _lib.DECODE_SIMPLE
     if unfused:
         num |= _lib.DECODE_UNFUSED
@@ -674,3 +674,69 @@ def moe_layer_forward(x: torch.Tensor, *, layer_id: int, gate_weight: torch.Tens
     out = _shared(x[None], shared_w1, shared_w1_scales, shared_w3, shared_w3_scales, shared_w2, shared_w2_scales, swiglu_limit,
                   routed[None])[0]
     return out, RouterResult(indices=idx, weights=w, scores=sc)
+
+
+# ---- checks --------------------------------------------------------------------------------------
+
+def validate_routing(expert_ids: torch.Tensor, weights: torch.Tensor, n_experts: int, *, allow_absent: bool = False) -> None:
+    """Host-side check of a routing result before it is handed to the expert operators (it reads the tensors, so on
+    CUDA tensors it waits for the device: a debugging aid, not part of the hot path).  Raises ValueError for an expert
+    id outside [0, n_experts) (-1 passes with `allow_absent`), for an expert chosen twice by one token, for a weight
+    that is NaN or infinite, and for shapes that do not match.  The kernels themselves never trap on such input: an id
+    out of range is dropped (CACHALOT_STATUS_ID_RANGE / SLOT_RANGE), a bad weight is used as it is
+    (CACHALOT_STATUS_BAD_WEIGHT)."""
+    if expert_ids.dim() != 2 or tuple(weights.shape) != tuple(expert_ids.shape):
+        raise ValueError(f"expert_ids {tuple(expert_ids.shape)} and weights {tuple(weights.shape)} must both be [tokens, k]")
+    ids = expert_ids.detach().to("cpu", torch.int64)
+    w = weights.detach().to("cpu", torch.float32)
+    low = -1 if allow_absent else 0
+    bad = (ids < low) | (ids >= n_experts)
+    if bool(bad.any()):
+        t, j = (int(v) for v in bad.nonzero()[0])
+        raise ValueError(f"expert id {int(ids[t, j])} of token {t}, slot {j} is outside [0, {n_experts})")
+    srt, _ = torch.sort(ids, dim=1)
+    dup = (srt[:, 1:] == srt[:, :-1]) & (srt[:, 1:] >= 0)
+    if bool(dup.any()):
+        t = int(dup.nonzero()[0][0])
+        raise ValueError(f"token {t} routes to one expert twice: {ids[t].tolist()}")
+    if not bool(torch.isfinite(w).all()):
+        t, j = (int(v) for v in (~torch.isfinite(w)).nonzero()[0])
+        raise ValueError(f"router weight of token {t}, slot {j} is {float(w[t, j])}")
+
+
+_self_check_done: dict = {}
+FORCE_SIMPLE_KERNELS = False   # set by a failed self_check: moe_forward then takes the one-warp-per-output kernels
+
+
+def self_check(device=None, *, tol: float = 2e-3, _run=None) -> bool:
+    """Load-time check in the manner of the reference's kernel self-check (minimax/codes_qmv.py:8-15, 475-477: a
+    custom kernel that stops matching the library path is switched off): one tiny decode through the single-launch
+    kernel against the one-warp-per-output kernels for both bank formats.  Returns True when they agree; on a
+    mismatch it sets FORCE_SIMPLE_KERNELS, so `moe_forward` keeps to the simple kernels, and returns False.  Once per
+    device.  `_run(kind) -> (fast, slow)` replaces the device work (tests)."""
+    global FORCE_SIMPLE_KERNELS
+    key = str(device)
+    if key in _self_check_done:
+        return _self_check_done[key]
+
+    def run(kind):
+        from .bank import affine_format
+        dev = torch.device("cuda") if device is None else torch.device(device)
+        hidden, inter, k = 256, 192, 3
+        fmt = FP4_FORMAT if kind == "fp4" else affine_format(hidden, inter)
+        bank = SlabBank(fmt, hidden, inter, 4, device=dev)
+        gen = torch.Generator(device=dev).manual_seed(0)
+        bank.fill_random(gen)
+        x = torch.randn((1, hidden), device=dev, generator=gen).to(torch.bfloat16)
+        slots = torch.tensor([[2, 0, 3]], dtype=torch.int32, device=dev)
+        w = torch.tensor([[0.5, 0.3, 0.2]], dtype=torch.float32, device=dev)
+        return moe_forward(x, slots, w, bank, numerics="f32"), moe_forward(x, slots, w, bank, numerics="f32", simple=True)
+
+    ok = True
+    for kind in ("fp4", "affine"):
+        fast, slow = (_run or run)(kind)
+        ok = ok and bool(torch.isfinite(fast).all()) and float((fast - slow).abs().max()) <= tol * max(float(slow.abs().max()), 1e-30)
+    if not ok:
+        FORCE_SIMPLE_KERNELS = True
+    _self_check_done[key] = ok
+    return ok

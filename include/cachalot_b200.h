@@ -43,7 +43,8 @@ enum {
   CACHALOT_STATUS_SLOT_RANGE = 1, /* a slot id >= n_slots was seen and treated as absent */
   CACHALOT_STATUS_ID_RANGE = 2,   /* an expert id outside [0, E) was seen and dropped */
   CACHALOT_STATUS_SCALE_RANGE = 4, /* an FP4 block scale outside the window around fp4_scale_centre was clamped */
-  CACHALOT_STATUS_WAIT_EXPIRED = 8 /* a bounded device-side wait ran out (the result of that call is not valid) */
+  CACHALOT_STATUS_WAIT_EXPIRED = 8, /* a bounded device-side wait ran out (the result of that call is not valid) */
+  CACHALOT_STATUS_BAD_WEIGHT = 16 /* a router weight was NaN or infinite (it was used as it is) */
 };
 
 enum { CACHALOT_BANK_FP4 = 0, CACHALOT_BANK_AFFINE = 1 };

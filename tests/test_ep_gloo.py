@@ -178,3 +178,53 @@ def test_two_rank_prefill_exchange_equals_unsharded():
         assert p.exitcode == 0
     assert sorted(r for r, _ in res) == [0, 1]
     assert all(isinstance(err, float) and err < 2e-3 for _, err in res), res
+
+
+def _report_and_exit(q, item):
+    q.put(item)
+    q.close()
+    q.join_thread()      # the message is on its way before the process goes
+    os._exit(0)
+
+
+def _leaver_worker(rank, world, port, q):
+    """Both ranks do one exchange; then rank 1 leaves between the steps and rank 0 tries the next one."""
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from oracle import configs
+
+    hidden, inter, n_exp, k, tokens = 64, 64, 4, 2, 8
+    x, ids, w, experts = configs.config3(seed=6, tokens=tokens, hidden=hidden, inter=inter, n_experts=n_exp, k=k, materialise=range(n_exp))
+    experts = [experts[e] for e in range(n_exp)]
+    mine = slice(rank * tokens // world, (rank + 1) * tokens // world)
+    args = (torch.from_numpy(x[mine]).to(torch.bfloat16), torch.from_numpy(ids[mine]), torch.from_numpy(w[mine]), _Shard(experts, rank, world))
+    kw = dict(n_experts=n_exp, backend=_OracleBackend(experts, hidden))
+    first = ep.ep_moe_prefill(*args, **kw)
+    dist.barrier()                      # the step is over on both ranks: nothing is in flight
+    if rank == 1:
+        _report_and_exit(q, (1, "left"))  # a rank that is gone: no goodbye, no destroy_process_group
+    try:
+        ep.ep_moe_prefill(*args, **kw)
+        msg = "no error"
+    except ep.ExchangeError as exc:
+        msg = f"ExchangeError {tuple(first.shape)} {str(exc)[:60]}"
+    except Exception as exc:          # anything else is a finding too
+        msg = f"other {type(exc).__name__}"
+    _report_and_exit(q, (0, msg))
+
+
+@pytest.mark.timeout(120)
+def test_a_rank_that_leaves_between_steps_gives_the_survivor_an_error_not_a_hang():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_leaver_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=90) for _ in procs)
+    for p in procs:
+        p.join(timeout=30)
+    assert res[1] == "left"
+    assert res[0].startswith("ExchangeError"), res

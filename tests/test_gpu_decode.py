@@ -393,3 +393,52 @@ def test_config2_batches_at_full_dims_meet_the_oracle(kind, rows):
             print(f"{kind} rows={rows} token {t} {name}: {outside} of {hidden} elements moved across a bf16 boundary, max {err.max():.2e}")
             assert err.max() < 2 ** -7 and outside <= hidden // 64, (name, t, outside)
             assert max_rel(exact[name][t].cpu().numpy(), plain) < TOL, (name, t)
+
+
+def test_self_check_passes_and_a_nan_weight_sets_its_status_bit():
+    import cachalot_b200 as cb
+    from cachalot_b200 import _lib
+    assert cb.self_check() is True and cb.ops.FORCE_SIMPLE_KERNELS is False
+    hidden, inter, n_slots, k = 4096, 2880, 8, 6
+    bank = cb.SlabBank(cb.FP4_FORMAT, hidden, inter, n_slots)
+    bank.fill_random(torch.Generator(device="cuda").manual_seed(1))
+    for rows in (1, 8):          # the single-launch kernel, and the grouped tensor-core path
+        x = torch.randn((rows, hidden), device="cuda").to(torch.bfloat16)
+        slots = torch.arange(k, dtype=torch.int32, device="cuda").repeat(rows, 1)
+        w = torch.full((rows, k), 0.2, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        cb.moe_forward(x, slots, w, bank, status=status)
+        assert int(status.item()) == 0
+        w[rows - 1, 2] = float("nan")
+        cb.moe_forward(x, slots, w, bank, status=status)
+        assert int(status.item()) & _lib.STATUS_BAD_WEIGHT
+
+
+def test_two_streams_decode_small_banks_concurrently():
+    """Small banks leave most of an SM's shared memory unused, yet the single-launch kernel always takes a whole SM per
+    CTA: launches from two streams cannot be at the grid barrier together, and both streams get the right answers."""
+    import cachalot_b200 as cb
+    hidden, inter, n_slots, k = 512, 384, 12, 6
+    bank = cb.SlabBank(cb.affine_format(hidden, inter), hidden, inter, n_slots)
+    bank.fill_random(torch.Generator(device="cuda").manual_seed(4))
+    g = torch.Generator(device="cuda").manual_seed(5)
+    xs = [torch.randn((1, hidden), device="cuda", generator=g).to(torch.bfloat16) for _ in range(2)]
+    slots = [torch.randperm(n_slots, device="cuda", generator=g)[:k].to(torch.int32)[None] for _ in range(2)]
+    w = torch.full((1, k), 0.15, device="cuda")
+    want = [cb.moe_forward(xs[i], slots[i], w, bank, simple=True) for i in range(2)]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    ws = [torch.empty(1 << 20, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    outs = [[], []]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for it in range(30):
+        for i, st in enumerate(streams):
+            with torch.cuda.stream(st):
+                outs[i].append(cb.moe_forward(xs[i], slots[i], w, bank, workspace=ws[i], status=status))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for i in range(2):
+        scale = float(want[i].abs().max())
+        for o in outs[i]:
+            assert torch.equal(o, outs[i][0])
+            assert float((o - want[i]).abs().max()) <= 2 ** -7 * scale

@@ -283,3 +283,28 @@ def test_prefill_tensor_core_path_edges(case):
     assert float(err.max()) < 5e-2
     y, perm, offsets, inv = check_prefill_rows(bank, lambda e: experts[e], xt, it, wt, n_experts=n_exp, k=k, tol=TOL, max_exempt=0.5)
     assert torch.equal(tc, cb.combine_rows(y, inv, tokens, k))
+
+
+def test_prefill_over_a_two_bit_bank_matches_oracle():
+    """model/expert_affine.py:84-99 through the grouped prefill entry: a 2-bit g128 bank, the affine op's rounding points
+    (g, u, h and each expert's output through bf16), results summed in slot order."""
+    import cachalot_b200 as cb
+    from oracle import affine
+    tokens, hidden, inter, n_exp, k = 20, 256, 384, 6, 3
+    rng = np.random.default_rng(41)
+    experts = [configs.affine_expert(rng, hidden, inter) for _ in range(n_exp)]
+    bank = make_bank(experts, cb.affine_format(hidden, inter), hidden, inter)
+    bank.slot_table[0, 4] = -1
+    x = round_bf16(rng.standard_normal((tokens, hidden)).astype(np.float32))
+    ids = np.stack([rng.permutation(n_exp)[:k] for _ in range(tokens)]).astype(np.int32)
+    w = rng.uniform(0.1, 0.5, (tokens, k)).astype(np.float32)
+    got = cb.moe_prefill_grouped(bf16_tensor(x), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), bank).cpu().numpy()
+    want = np.zeros((tokens, hidden), np.float32)
+    for t in range(tokens):
+        for j in range(k):
+            if ids[t, j] == 4:
+                continue
+            want[t] += affine.affine_expert_forward(x[t], experts[ids[t, j]], bits=2, group_size=128, weight=w[t, j], swiglu_limit=10.0,
+                                                    acc=np.float64)
+    err = np.abs(got - want) / np.max(np.abs(want))
+    assert err.max() < 2 ** -7 and np.count_nonzero(err >= TOL) <= max(2, err.size // 64)
