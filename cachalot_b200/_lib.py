@@ -54,6 +54,7 @@ SIGNATURES = {
     "cachalot_version": (_i, []),
     "cachalot_fp4_dequant": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
     "cachalot_affine_dequant": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
+    "cachalot_requant_fp4_to_affine": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "cachalot_router_logits": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "cachalot_route_topk": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "cachalot_moe_decode_workspace_bytes": (_sz, [_desc, _i, _i]),

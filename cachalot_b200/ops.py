@@ -65,6 +65,47 @@ def dequantize_affine(words: torch.Tensor, scales: torch.Tensor, biases: torch.T
     return out
 
 
+def requantize_fp4_to_affine(packed: torch.Tensor, scales: torch.Tensor, *, bits: int = 2, group_size: int = 128,
+                             scale_dtype=torch.float16, lsq_iters: int = 4):
+    """FP4 matrix (packed uint8 [N,K/2], E8M0 uint8 [N,K/32]) -> (words int32 [N, K*bits/32], scales, biases
+    [N*K/group_size] in `scale_dtype`): the searched affine fit with least-squares refinement that builds a 2-bit
+    bank from the FP4 checkpoint (benchmarks/quant_affine.py:138-329, fit_search_lsq + quantize_affine)."""
+    _need_cuda(packed, scales)
+    n, k = packed.shape[0], packed.shape[1] * 2
+    if tuple(scales.shape) != (n, k // 32):
+        raise ValueError(f"Scale shape {tuple(scales.shape)} does not match expected {(n, k // 32)}")
+    if scale_dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("scales and biases are stored as float16 or bfloat16")
+    words = torch.empty((n, k * bits // 32), dtype=torch.int32, device=packed.device)
+    s = torch.empty(n * k // group_size, dtype=scale_dtype, device=packed.device)
+    b = torch.empty_like(s)
+    sdt = _lib.BF16 if scale_dtype == torch.bfloat16 else _lib.F16
+    check(lib.cachalot_requant_fp4_to_affine(_ptr(packed.contiguous()), _ptr(scales.contiguous()), n, k, bits, group_size, sdt,
+                                             int(lsq_iters), _ptr(words), _ptr(s), _ptr(b), _stream()))
+    return words, s, b
+
+
+def requantize_bank(bank: SlabBank, *, bits: int = 2, group_size: int = 128, scale_dtype=torch.float16, lsq_iters: int = 4) -> SlabBank:
+    """An affine bank with the same slots and slot table as the FP4 `bank`, every expert re-quantised on the GPU
+    (what benchmarks/build_affine_bank.py does offline for the 2-bit bank)."""
+    from .bank import affine_format
+
+    if bank.fmt.kind != "fp4":
+        raise ValueError("requantize_bank takes an FP4 bank")
+    name = "bfloat16" if scale_dtype == torch.bfloat16 else "float16"
+    out = SlabBank(affine_format(bank.hidden, bank.inter, bits, group_size, name), bank.hidden, bank.inter, bank.n_slots,
+                   layers=bank.layers, n_experts=bank.n_experts, device=bank.slab.device)
+    out.slot_table_host, out.slot_table = bank.slot_table_host.clone(), bank.slot_table.clone()
+    for slot in range(bank.n_slots):
+        t = {}
+        for proj in ("w1", "w2", "w3"):
+            w, s, b = requantize_fp4_to_affine(bank.typed_view(slot, f"{proj}.weight"), bank.typed_view(slot, f"{proj}.scale"), bits=bits,
+                                               group_size=group_size, scale_dtype=scale_dtype, lsq_iters=lsq_iters)
+            t[f"{proj}.weight"], t[f"{proj}.scales"], t[f"{proj}.biases"] = w, s, b
+        out.write_expert(slot, t)
+    return out
+
+
 # ---- routing ----------------------------------------------------------------------------------
 
 @dataclass(frozen=True)

@@ -110,6 +110,17 @@ CACHALOT_API int cachalot_fp4_dequant(const uint8_t* packed, const uint8_t* scal
 CACHALOT_API int cachalot_affine_dequant(const uint32_t* words, const void* scales, const void* biases, int n, int k,
                             int bits, int group, int scale_dtype, float* out, cachalot_stream_t stream);
 
+/* Replaces benchmarks/quant_affine.py:138-329 (fit_search + refine_lsq + quantize_affine), the step that builds a
+ * 2-bit affine bank from FP4 weights (benchmarks/build_affine_bank.py:72-187): per group of `group` (64 or 128)
+ * consecutive elements of the flattened [N*K] matrix a min/max fit, the 5 x 5 grid search over shrunk ranges, then
+ * `lsq_iters` rounds of least-squares refinement with scale and bias rounded to the storage dtype every round;
+ * levels are taken against the rounded scale and bias.  packed u8 [N,K/2], scales u8 [N,K/32] (FP4 as above) ->
+ * out_words u32 [N*K*bits/32] (little-endian bit stream), out_scales / out_biases [N*K/group] in scale_dtype.
+ * bits 2 or 4. */
+CACHALOT_API int cachalot_requant_fp4_to_affine(const uint8_t* packed, const uint8_t* scales, int n, int k, int bits, int group,
+                                   int scale_dtype, int lsq_iters, uint32_t* out_words, void* out_scales,
+                                   void* out_biases, cachalot_stream_t stream);
+
 /* ---- routing ------------------------------------------------------------------------------ */
 
 /* Replaces the score half of model/router_fused_metal.py:33-58 (router_scores): for each of
