@@ -109,6 +109,15 @@ class SlabBank:
         d.scale_dtype = _lib.BF16 if sdt == "bfloat16" else _lib.F16
         d.fp4_scale_centre = 0
         self.desc = d
+        self._scale_lo, self._scale_hi = 255, 0      # E8M0 bytes seen so far (FP4 banks; byte 0 is not counted)
+
+    def _note_scale_bytes(self, lo: int, hi: int) -> None:
+        """Widens the range of E8M0 bytes the bank is known to hold and re-centres the descriptor on it."""
+        self._scale_lo, self._scale_hi = min(self._scale_lo, lo), max(self._scale_hi, hi)
+        if self._scale_hi - self._scale_lo > 27:
+            raise NotImplementedError(f"FP4 block scales span 2**{self._scale_lo - 127}..2**{self._scale_hi - 127}: "
+                                      "wider than the 28 binades the grouped kernels hold in f16")
+        self.desc.fp4_scale_centre = max(1, min(254, (self._scale_lo + self._scale_hi + 1) // 2))
 
     def calibrate_scale_centre(self) -> int:
         """FP4 banks: set the descriptor's scale centre to the middle of the E8M0 bytes actually
@@ -116,14 +125,13 @@ class SlabBank:
         centre-14 .. centre+13).  Call once after the bank is filled; returns the centre."""
         if self.fmt.kind != "fp4":
             return 0
-        lo, hi = 255, 0
+        self._scale_lo, self._scale_hi = 255, 0
         for name in ("w1.scale", "w2.scale", "w3.scale"):
             o, n = self.offsets[name], self.tensor_sizes[name]
             region = self.slab[:, o:o + n]
-            lo, hi = min(lo, int(region.min())), max(hi, int(region.max()))
-        if hi - lo > 27:
-            raise NotImplementedError(f"FP4 block scales span 2**{lo - 127}..2**{hi - 127}: wider than the 28 binades supported")
-        self.desc.fp4_scale_centre = max(1, min(254, (lo + hi + 1) // 2 + 0))
+            # byte 0 (2**-127) marks a block that is zero whatever its codes are; it does not widen the range
+            nz = torch.where(region == 0, torch.full_like(region, 255), region)
+            self._note_scale_bytes(int(nz.min()), int(region.max()))
         return int(self.desc.fp4_scale_centre)
 
     @property
@@ -165,6 +173,13 @@ class SlabBank:
                 src = src.contiguous().view(torch.uint8).reshape(-1)
             if src.numel() != self.tensor_sizes[name]:
                 raise ValueError(f"{name}: {src.numel()} bytes, slot expects {self.tensor_sizes[name]}")
+            if self.fmt.kind == "fp4" and name.endswith(".scale") and src.numel():
+                # keep the descriptor's scale centre on the bytes the bank holds (the grouped FP4 kernels clamp
+                # scales outside centre-14 .. centre+13); byte 0 = a zero block, not counted
+                nz = torch.where(src == 0, torch.full_like(src, 255), src)
+                lo, hi = int(nz.min()), int(src.max())
+                if lo <= hi:
+                    self._note_scale_bytes(lo, hi)
             self.view(slot, name).copy_(src)
 
     def fill_random(self, gen: torch.Generator | None = None, step: int = 64) -> None:
@@ -186,6 +201,8 @@ class SlabBank:
                 else:
                     v = torch.randn((s1 - s0, n // 2), device=dev, generator=gen) * 0.01
                     region.view(torch.float16).copy_(v.to(torch.float16))
+        if self.fmt.kind == "fp4":
+            self._note_scale_bytes(118, 123)
 
     def expert(self, layer: int, expert: int) -> "ResidentExpert":
         in_range = 0 <= layer < self.layers and 0 <= expert < self.n_experts

@@ -241,4 +241,5 @@ def load_bank(model_path, device="cuda", *, layers=None, n_experts: int | None =
             os.close(fd)
     bank.slot_table_host = table
     bank.slot_table = table.to(bank.slab.device)
+    bank.calibrate_scale_centre()      # FP4: centre the grouped kernels' scale window on the bytes just loaded
     return bank

@@ -214,6 +214,10 @@ def moe_forward(x: torch.Tensor, slot_ids: torch.Tensor, gate_weights: torch.Ten
     """Routed experts for `rows` tokens: x bf16 [rows,H], slot_ids int32 [rows,k] (bank slots, -1 =
     absent -> zero contribution), gate_weights float32 [rows,k] -> [rows,H].
 
+    x of another float dtype is ROUNDED TO BF16 first: the kernels take bf16 activations only.  The reference's
+    runtime passes bf16 hidden states, for which this is the identity; its op would read a float32 x unrounded
+    (model/moe_fused_metal.py:200,208), so a float32 caller sees up to 2**-9 relative input rounding here.
+
     numerics "f32" keeps fp32 between the projections (the FP4 decode op,
     model/moe_fused_metal.py:189-233); "bf16" rounds g, u, h and each expert's output to bf16 (the
     affine op, model/expert_affine.py:65-81).  Default: by bank format.  `phase` ("gate_up" or
@@ -320,8 +324,8 @@ def _slots_of(experts) -> tuple[SlabBank, torch.Tensor]:
 def fused_routed_experts(x: torch.Tensor, experts, router_weights: torch.Tensor, *, hidden_size: int = 5120,
                          intermediate: int = 2304, swiglu_limit: float = 10.0) -> torch.Tensor:
     """Top-k routed experts of one decode token over an FP4 bank (model/moe_fused_metal.py:189-233):
-    x [hidden_size] any float dtype, experts = ResidentExpert objects, router_weights float32 [k]
-    -> float32 [hidden_size]."""
+    x [hidden_size] bf16 (another float dtype is rounded to bf16, see `moe_forward`), experts = ResidentExpert
+    objects, router_weights float32 [k] -> float32 [hidden_size]."""
     bank, slots = _slots_of(experts)
     if bank.fmt.kind != "fp4":
         raise ValueError("fused_routed_experts needs an FP4 bank; use affine_routed_experts")

@@ -317,8 +317,9 @@ def test_layer_decode_one_launch_equals_route_then_experts(kind, router_mode):
 
 def test_fp4_scale_window_and_calibration():
     """Block scales far from the default centre: the grouped (two-launch) kernels hold scales relative to
-    a centre in f16 and need the bank calibrated; the single-launch kernel applies every E8M0 scale in
-    fp32 and needs no calibration."""
+    a centre in f16; `SlabBank.write_expert` keeps the centre on the bytes the bank holds, and a descriptor whose
+    centre is off raises the status bit.  The single-launch kernel applies every E8M0 scale in fp32 and does not
+    depend on the centre."""
     import cachalot_b200 as cb
     rng = np.random.default_rng(9)
     hidden, inter = 256, 192
@@ -333,8 +334,10 @@ def test_fp4_scale_window_and_calibration():
     want = _fp4_expert_out(x, e, None, 0.0)
     got = cb.moe_forward(bf16_tensor(x), slots, w, bank, swiglu_limit=0.0, status=status).cpu().numpy()
     assert int(status.item()) == 0 and max_rel(got, want) < TOL               # single launch: any scale
+    assert 90 <= bank.desc.fp4_scale_centre <= 100                             # set while the expert was written
+    bank.desc.fp4_scale_centre = 121                                          # a host that passes the default
     cb.moe_forward(bf16_tensor(x), slots, w, bank, swiglu_limit=0.0, status=status, unfused=True)
-    assert int(status.item()) & 4                                             # default centre 121 does not cover them
+    assert int(status.item()) & 4                                             # centre 121 does not cover them
     assert 90 <= bank.calibrate_scale_centre() <= 100
     status.zero_()
     got = cb.moe_forward(bf16_tensor(x), slots, w, bank, swiglu_limit=0.0, status=status, unfused=True).cpu().numpy()
@@ -442,3 +445,18 @@ def test_two_streams_decode_small_banks_concurrently():
         for o in outs[i]:
             assert torch.equal(o, outs[i][0])
             assert float((o - want[i]).abs().max()) <= 2 ** -7 * scale
+
+
+def test_float32_activations_are_rounded_to_bf16():
+    """The kernels take bf16 activations: a float32 x gives exactly what its bf16 rounding gives (documented on
+    `moe_forward`; the reference's op would read the float32 values unrounded)."""
+    import cachalot_b200 as cb
+    rng = np.random.default_rng(21)
+    hidden, inter = 256, 192
+    bank = make_bank([configs.fp4_expert(rng, hidden, inter)], cb.FP4_FORMAT, hidden, inter)
+    x32 = torch.from_numpy(rng.standard_normal((1, hidden)).astype(np.float32)).cuda()
+    slots = torch.zeros((1, 1), dtype=torch.int32, device="cuda")
+    w = torch.ones((1, 1), device="cuda")
+    a = cb.moe_forward(x32, slots, w, bank)
+    b = cb.moe_forward(x32.to(torch.bfloat16), slots, w, bank)
+    assert torch.equal(a, b)

@@ -49,3 +49,33 @@ def test_self_check_switches_to_the_simple_kernels_on_a_mismatch(monkeypatch):
     nan[0] = float("nan")
     monkeypatch.setattr(ops, "FORCE_SIMPLE_KERNELS", False)
     assert ops.self_check("fake:2", _run=lambda kind: (nan, good)) is False and ops.FORCE_SIMPLE_KERNELS is True
+
+
+def test_fp4_bank_tracks_its_scale_window_on_the_host():
+    """`write_expert` re-centres the descriptor on the E8M0 bytes written so far, ignores byte 0 (a zero block) and
+    refuses a bank wider than the 28 binades the grouped kernels can hold."""
+    import numpy as np
+    import torch
+
+    import cachalot_b200 as cb
+    hidden, inter = 64, 32
+    bank = cb.SlabBank(cb.FP4_FORMAT, hidden, inter, 2, device="cpu")
+
+    def expert(lo, hi, zero=False):
+        rng = np.random.default_rng(lo)
+        t = {}
+        for proj, (n, k) in (("w1", (inter, hidden)), ("w3", (inter, hidden)), ("w2", (hidden, inter))):
+            t[f"{proj}.weight"] = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+            sc = rng.integers(lo, hi + 1, (n, k // 32), dtype=np.uint8)
+            sc.flat[0], sc.flat[1] = lo, hi
+            if zero:
+                sc.flat[2] = 0
+            t[f"{proj}.scale"] = sc
+        return t
+
+    bank.write_expert(0, expert(100, 110, zero=True))
+    assert bank.desc.fp4_scale_centre == 105
+    bank.write_expert(1, expert(112, 120))
+    assert bank.desc.fp4_scale_centre == 110
+    with pytest.raises(NotImplementedError):
+        bank.write_expert(1, expert(90, 130))

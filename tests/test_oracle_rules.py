@@ -117,3 +117,33 @@ def test_prefill_slot_order_equals_decode_per_row():
     for t in range(6):
         want = fp4.routed_topk_forward(x[t], [experts[int(e)] for e in ids[t]], w[t])
         assert np.allclose(out[t], want, rtol=1e-5, atol=1e-5)
+
+
+def test_affine_expert_oracle_matches_dense_math_to_two_percent():
+    """The reference's own check of a 2-bit g128 expert (tests/test_expert_bank.py:93-116) restated on the oracle:
+    the quantised expert against dense matrices (the dequantised weights) with the same bf16 rounding points,
+    within 2 % of the output's maximum; a row of a batch equals the same row alone within 2 %."""
+    from oracle import affine
+    from oracle.bf16 import round_bf16
+
+    rng = np.random.default_rng(7)
+    hidden, inter, bits, group = 256, 128, 2, 128
+    mats, dense = {}, {}
+    for proj, (n, k) in (("w1", (inter, hidden)), ("w3", (inter, hidden)), ("w2", (hidden, inter))):
+        w = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+        words, s, b = affine.quantize_affine_minmax(w, bits=bits, group_size=group)
+        mats[f"{proj}.weight"], mats[f"{proj}.scales"], mats[f"{proj}.biases"] = words, s, b
+        dense[proj] = affine.dequantize_affine(words, s, b, bits=bits, group_size=group).astype(np.float64)
+    x = round_bf16(rng.standard_normal(hidden).astype(np.float32))
+    got = affine.affine_expert_forward(x, mats, bits=bits, group_size=group, weight=0.7, swiglu_limit=10.0)
+    xb = x.astype(np.float64)
+    gate = np.minimum(round_bf16((dense["w1"] @ xb).astype(np.float32)), 10.0)
+    up = np.clip(round_bf16((dense["w3"] @ xb).astype(np.float32)), -10.0, 10.0)
+    h = round_bf16((gate / (1.0 + np.exp(-gate)) * up * 0.7).astype(np.float32))
+    want = round_bf16((dense["w2"] @ h.astype(np.float64)).astype(np.float32))
+    scale = float(np.abs(want).max())
+    assert float(np.abs(got - want).max()) < 0.02 * scale
+    xm = round_bf16(rng.standard_normal((4, hidden)).astype(np.float32))
+    batched = affine.affine_expert_forward(xm, mats, bits=bits, group_size=group, weight=np.array([0.7, 0.1, 1.0, 0.3]))
+    single = affine.affine_expert_forward(xm[1], mats, bits=bits, group_size=group, weight=0.1)
+    assert float(np.abs(batched[1] - single).max()) < 0.02 * max(1e-6, float(np.abs(single).max()))
