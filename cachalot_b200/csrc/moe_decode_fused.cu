@@ -1,15 +1,29 @@
 // Decode-time routed experts for ONE token in ONE launch (cooperative, one CTA per SM).
 //
 //   phase 0 : hidden[j, i] = silu(min(g,L)) * clip(u,+-L) * gate_w[j]     g = W1_j x, u = W3_j x
-//   grid barrier
+//   (hidden crosses the CTAs through L2 as self-validating words: see below)
 //   phase 1 : out[n]       = sum_j W2_j[n, :] . hidden[j, :]               j in routing order
+//
+// There is no grid barrier between the phases.  A hidden value travels through L2 as one 32-bit word that carries
+// its own validity: the fp32 value rounded to 15 mantissa bits (exact for the bf16 numerics; the consumer turns it
+// into 15-bit fixed point or f16 anyway) with the launch's 8-bit tag in the low byte, written and read with relaxed
+// GPU-scope accesses, which are single-copy atomic per word.  A CTA that finds another launch's tag reads the word
+// again (bounded).  Every launch writes all k rows (tag only, for an expert that is absent), so the tag a word held
+// before is the previous launch's.  No release fence is needed, and a fence is what a barrier costs here: at GPU
+// scope it waits for the SM's copies in flight, 2-3 us with the ring full.
+// The experts are taken in two groups (about two thirds of the present experts, then the rest).  Every CTA owns
+// a slice of the inter rows of EVERY expert and walks them expert by expert, so group A's hidden rows are long
+// written by every CTA when a CTA, through with all its phase-0 units, converts them into operand form and runs
+// A's part of phase 1; group B's follow, by then written too: the skew between the CTAs hides under work.
 //
 // The kernel is a stream of weight bytes: HBM -> cp.async.bulk (four copies of four weight rows per
 // unit, one per copy warp) -> a ring of shared-memory stages -> registers -> mma.sync.  Warps 0..3
 // issue the copies (one lane each) and run ahead of the consumers by the depth of the ring; they keep
 // issuing the down projection's rows while the CTA waits at the grid barrier, so HBM stays busy across it.
-// Warps 4..11 are four pairs of MMA warps.  A pair takes one unit; each warp of the pair does half
-// of the reduction dimension and the two partial sums meet in shared memory.
+// Warps 4..11 are the MMA warps.  In phase 0 they work as four pairs: a pair takes one unit, each warp of the
+// pair does half of the reduction dimension and the two partial sums meet in shared memory (gate and up must be
+// complete before SwiGLU).  In phase 1 every warp works alone on its half of a unit's reduction dimension and
+// leaves its partial sums in shared memory; the closing sum adds halves and experts in a fixed order.
 //
 //   unit, phase 0 : 8 rows of W1 (MMA rows 0..7) + the same 8 rows of W3 (MMA rows 8..15) of one expert
 //   unit, phase 1 : 16 rows of W2 of one expert; a CTA owns whole 16-row output tiles and walks
@@ -48,7 +62,13 @@ constexpr int kUnroll = CB_UNROLL;  // steps of the reduction loop unrolled toge
 constexpr int NPROD = 4;                          // producer warps (one issuing lane each; a lane's copies do not overlap)
 constexpr int KMAX = 8;                           // routed experts per token
 constexpr int MAX_TILES = 8;                      // phase-1 output tiles one CTA may own
+#ifndef CB_W2_HOLD
+#define CB_W2_HOLD 4
+#endif
+constexpr int W2_HOLD = CB_W2_HOLD;               // down-projection units copied ahead before the first hidden rows have been asked for
+constexpr int KP1 = 2;                            // parts the reduction dimension of a phase-1 unit is cut into (one warp each)
 constexpr uint32_t WAIT_LIMIT = 1u << 20;         // polls before a wait gives up and flags an error
+constexpr uint32_t HIDDEN_TRIES = 1u << 16;       // reads of a hidden block before a CTA gives up on the others (about 10 ms)
 constexpr int SMEM_LIMIT = 227 * 1024;
 
 template <int FMT>
@@ -65,10 +85,22 @@ struct Fm {
 };
 
 
-// Grid barrier word (sense reversal on the top bit, so it needs no reset): every device that loads
-// the library has its own copy, zero at load.  A launch uses it once; two launches cannot be at
-// their barrier at the same time because a launch holds every SM until it has passed its own.
-__device__ unsigned grid_bar_word;
+// The hidden rows between the phases: KMAX rows of up to INTER_MAX tagged words (value & ~0xff | tag).  In the
+// library image, zero at load, so a word is either zero (no launch has tag 0) or what an earlier launch wrote: never
+// garbage that could pass for this launch's.  Every device that loads the library has its own copy; one launch at a
+// time per device uses it (a launch holds every SM, so two cannot overlap).
+constexpr int INTER_MAX = 8192;
+__device__ uint32_t fused_hidden[KMAX * INTER_MAX];
+// Layout of a row (one routed expert): 16-value blocks in chunks of 32; inside a chunk the words are ordered
+// [quarter of the block 0..3][block 0..31][4 values], so that the 32 lanes of a warp, one block each, read 512
+// contiguous bytes per 16-byte load.  A row is padded to whole chunks.
+__device__ __forceinline__ int hidden_row_words(int inter) { return ((inter / 16 + 31) / 32) * 512; }
+__device__ __forceinline__ int hidden_word(int i) {  // position of value i of a row
+  const int b = i >> 4, v = i & 15;
+  return (((b >> 5) * 4 + (v >> 2)) << 7) + ((b & 31) << 2) + (v & 3);
+}
+// {number of the next launch (never 0), CTAs of the current launch that have finished}
+__device__ unsigned fused_epoch[2] = {1u, 0u};
 
 // Routing done inside the kernel (logits == nullptr: the caller passes slots and weights instead).
 struct RouteArgs {
@@ -94,7 +126,7 @@ struct Geo {
   int tiles1;         // hidden / 16
   int stage_bytes[2], nst[2];  // ring geometry per phase (the same memory, cut into stages of the phase's unit size)
   int off_ring, off_act, off_pe, off_part, off_bar, total;
-  int balance;        // 1: split phase-0 units by bytes so that every CTA streams the same total
+  int max_tiles;      // phase-1 output tiles a CTA owns at most (sizes the partial-sum area)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -153,47 +185,13 @@ __device__ __forceinline__ void fp4_word(uint32_t w, uint32_t (&h)[4]) {
       : "r"(w));
 }
 
-// One arrival per CTA; returns false when the other CTAs do not show up within the wait limit.
-__device__ __forceinline__ bool grid_barrier(unsigned* word, unsigned n_ctas, bool master) {
-  // release: the CTA's writes (ordered before this thread by the CTA barrier) are visible to whoever acquires the
-  // word; no separate fence, which would also wait for the producers' copies in flight
-  const unsigned inc = master ? 0x80000000u - (n_ctas - 1u) : 1u;
-  unsigned old;
-  asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(word), "r"(inc) : "memory");
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    unsigned cur;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(cur) : "l"(word) : "memory");
-    if ((old ^ cur) & 0x80000000u) return true;
-  }
-  return false;
+__device__ __forceinline__ void st_relaxed_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-
-// split of the phase-0 units and phase-1 tiles over the CTAs
-__device__ __forceinline__ void cta_ranges(const Geo& G, int np, int b, int nb, int& u0, int& u1, int& t0, int& t1) {
-  const long long U0 = (long long)np * G.tiles0;
-  if (!G.balance && U0 * nb < 0x7fffffffLL && (long long)G.tiles1 * nb < 0x7fffffffLL) {
-    // the usual case in 32-bit arithmetic: every thread does this before the first copy can be issued
-    const unsigned ub = (unsigned)b, un = (unsigned)nb, u32 = (unsigned)U0, t32 = (unsigned)G.tiles1;
-    t0 = (int)(t32 * ub / un), t1 = (int)(t32 * (ub + 1u) / un);
-    u0 = (int)(u32 * ub / un), u1 = (int)(u32 * (ub + 1u) / un);
-    return;
-  }
-  t0 = (int)((long long)G.tiles1 * b / nb);
-  t1 = (int)((long long)G.tiles1 * (b + 1) / nb);
-  if (!G.balance) {
-    u0 = (int)(U0 * b / nb);
-    u1 = (int)(U0 * (b + 1) / nb);
-    return;
-  }
-  const long long b0 = G.unit_bytes[0], b1 = (long long)np * G.unit_bytes[1];
-  const long long T = U0 * b0 + (long long)G.tiles1 * b1;
-  auto f = [&](int bb, int tt) {
-    long long v = (T * bb / nb - (long long)tt * b1 + b0 / 2) / b0;
-    return (int)(v < 0 ? 0 : (v > U0 ? U0 : v));
-  };
-  u0 = f(b, t0);
-  u1 = b + 1 == nb ? (int)U0 : f(b + 1, t1);
-  if (u1 < u0) u1 = u0;
+__device__ __forceinline__ uint4 ld_relaxed_v4(const uint32_t* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
 }
 
 __device__ __forceinline__ void unpack16_bf16(const uint4 a, const uint4 b, float (&v)[16]) {
@@ -355,21 +353,24 @@ __device__ __forceinline__ void step_fp4(float& accA, float& accB, const uint8_t
   accB = fmaf(T[2], sb * pe, accB);
 }
 
-// One unit of one consumer warp: the lane's partial sums of MMA rows g and g+8 over the whole
+// One unit of one consumer warp: the lane's partial sums of MMA rows g and g+8 over the warp's part of the
 // reduction (its own sub-block of every step).  stage: the unit's 16 rows then its scale arrays;
 // act_row / pexs_row: the operand row (activation in operand form, per sub-block constants);
 // zeros: 64 zero bytes for the lanes whose operand column belongs to another lane's sub-block.
 template <int FMT, int PHASE, int SDT>
 __device__ __forceinline__ float2 unit_dot(const uint8_t* stage, const Geo& G, const uint8_t* act_row, const float2* pexs_row,
-                                           const uint8_t* zeros, int g, int t, int part) {
+                                           const uint8_t* zeros, int g, int t, int part, int nparts) {
   constexpr int SUB = Fm<FMT>::SUB, STEP = Fm<FMT>::STEP;
   const int K = G.K[PHASE];
   const int rb = G.row_bytes[PHASE];
   const int full = K / STEP;  // whole steps; one more, partial, when K is not a multiple of STEP
   const int nsub = K / SUB;
-  // part 0 takes the first half of the whole steps, part 1 the rest and the partial step
-  const int c_begin = part ? (full + 1) / 2 : 0, c_end = part ? full : (full + 1) / 2;
-  const bool tail = part && full * STEP < K;
+  // the steps (the partial one included, which costs as much as a whole one) are cut into `nparts` runs
+  const bool has_tail = full * STEP < K;
+  const int all = full + (has_tail ? 1 : 0);
+  const int c_begin = all * part / nparts, c_end_all = all * (part + 1) / nparts;
+  const bool tail = has_tail && c_end_all == all && c_begin < all;  // only the last non-empty run reaches it
+  const int c_end = tail ? full : c_end_all;
   // MMA row g is row wr = (g >> 1) + 4 * (g & 1) of its 8-row tile: the two rows a quarter-warp
   // reads in one LDS come from different 4-row halves, which sit `skew` bytes apart modulo 128
   const int wr = (g >> 1) + 4 * (g & 1);
@@ -429,18 +430,24 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
   __shared__ int s_slot[KMAX];    // its bank slot
   __shared__ float s_gw[KMAX];    // its router weight
   __shared__ int s_np;
+  __shared__ unsigned s_tag;
+  __shared__ unsigned s_absent;           // routing positions < k whose expert is not in the bank
+  __shared__ int s_ta[KMAX], s_tb[KMAX];  // this CTA's inter tiles [ta, tb) of the p-th present expert
+  __shared__ int s_n0;                    // its phase-0 units
   uint8_t* ring = smem + G.off_ring;
   uint8_t* act = smem + G.off_act;
   float2* pexs = reinterpret_cast<float2*>(smem + G.off_pe);
-  float* ybuf = reinterpret_cast<float*>(smem + G.off_part);  // [tiles of this CTA][KMAX][16]
+  float* ybuf = reinterpret_cast<float*>(smem + G.off_part);  // [tiles of this CTA][KMAX][KP1][16]
   // mbarriers: full / empty per ring stage and phase (the ring is re-cut into smaller stages for phase 1)
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + G.off_bar);
   uint64_t* full0 = bars, *empty0 = bars + 16, *full1 = bars + 32, *empty1 = bars + 48;
   const uint8_t* zeros = smem + G.off_bar + 512;  // 512 zero bytes
   float2* xch = reinterpret_cast<float2*>(smem + G.off_bar + 1024);  // [NPAIR][2][8] partial sums between the warps of a pair
+  uint64_t* hold = reinterpret_cast<uint64_t*>(smem + G.off_bar + 1536);  // the consumers have issued their first reads of hidden rows
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int H = bank.hidden, I = bank.inter;
   int err = 0;
+  (void)hidden;  // the hidden rows live in the library image (fused_hidden)
   // Under programmatic dependent launch the next kernel of the stream may be set up while this one runs (it cannot
   // become resident before this CTA leaves: a CTA fills the SM).  Until griddepcontrol.wait returns, only shared
   // memory is touched: the inputs may still be in the making by the previous kernel.  Both are no-ops otherwise.
@@ -449,14 +456,18 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
   if (threadIdx.x == 0) {
     for (int s = 0; s < 16; ++s) {
       mbar_init(&full0[s], NPROD), mbar_init(&empty0[s], 2);
-      mbar_init(&full1[s], NPROD), mbar_init(&empty1[s], 2);
+      mbar_init(&full1[s], NPROD), mbar_init(&empty1[s], KP1);
     }
+    mbar_init(hold, Fm<FMT>::NCW);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // number of this exchange: every CTA reads the counter before any CTA can move it on (the last one to finish does)
   const uint32_t xe = P.world > 0 ? *reinterpret_cast<volatile const uint32_t*>(P.epoch) + 1u : 0u;
 
+  // number of this launch: every CTA reads it before any CTA can move it on (the last one to finish does, and none
+  // finishes before all have written their hidden values)
+  if (threadIdx.x == 0) s_tag = *reinterpret_cast<volatile const unsigned*>(&fused_epoch[0]);
   // consumers fetch their part of x before anything else (up to XB 16-element blocks per thread)
   constexpr int XB = 3;
   const int tid = threadIdx.x - NPROD * 32;
@@ -561,14 +572,37 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
     if (__any_sync(0xffffffffu, oob) && lane == 0 && blockIdx.x == 0 && status) atomicOr(status, CACHALOT_STATUS_SLOT_RANGE);
     const bool bad_w = lane < k && !(fabsf(my_w) <= 3.0e38f);  // NaN or infinite
     if (__any_sync(0xffffffffu, bad_w) && lane == 0 && blockIdx.x == 0 && status) atomicOr(status, CACHALOT_STATUS_BAD_WEIGHT);
-    if (lane == 0) s_np = __popc(pmask);
+    // Phase-0 split: unit (routing position r, inter tile) has the number tile * k + r; CTA b takes the numbers
+    // [V b / n, V (b+1) / n), V = tiles0 * k - a run of consecutive tiles of every expert, the totals of two CTAs
+    // at most one unit apart.  (Numbered by routing position, not by present expert, so an absent expert only
+    // leaves holes.)
+    const int npres = __popc(pmask);
+    int cnt = 0;
+    if (present) {
+      const unsigned V = (unsigned)G.tiles0 * (unsigned)k;
+      const unsigned v0 = V * blockIdx.x / gridDim.x, v1 = V * (blockIdx.x + 1u) / gridDim.x;
+      const int ta = (int)((v0 + (unsigned)(k - 1 - lane)) / (unsigned)k), tb = (int)((v1 + (unsigned)(k - 1 - lane)) / (unsigned)k);
+      const int p = __popc(pmask & ((1u << lane) - 1u));
+      s_ta[p] = ta, s_tb[p] = tb;
+      cnt = tb - ta;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+    const unsigned absent = __ballot_sync(0xffffffffu, lane < k && !present);
+    if (lane == 0) s_np = npres, s_n0 = cnt, s_absent = absent;
   }
   __syncthreads();
   const int np = s_np;
-  int u_begin, u_end, t_begin, t_end;
-  cta_ranges(G, np, blockIdx.x, gridDim.x, u_begin, u_end, t_begin, t_end);
-  const int n0 = u_end - u_begin;         // phase-0 units of this CTA
-  const int n1 = (t_end - t_begin) * np;  // phase-1 units of this CTA
+  // experts of the two groups: about two thirds, then the rest (6 experts: 4 + 2, so that a CTA with two output tiles
+  // has 8 and 4 phase-1 units for its four pairs of MMA warps)
+  const int nB = np >= 3 ? np / 3 : (np == 2 ? 1 : 0), nA = np - nB;
+  const int t_begin = (int)((unsigned)G.tiles1 * blockIdx.x / gridDim.x), t_end = (int)((unsigned)G.tiles1 * (blockIdx.x + 1u) / gridDim.x);
+  const int ntl = t_end - t_begin;                  // phase-1 output tiles of this CTA
+  const int n0 = s_n0;                              // phase-0 units of this CTA
+  const unsigned tag32 = s_tag;                     // number of this launch
+  const unsigned tag8 = tag32 % 255u + 1u;          // marks this launch's hidden values (never 0)
+  const int roww = hidden_row_words(I);             // words of a hidden row in fused_hidden
+  const int n1 = ntl * np;                          // phase-1 units of this CTA
   const int nst0 = G.nst[0], nst1 = G.nst[1];
 
   if (warp < NPROD) {
@@ -582,10 +616,12 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
         const int rb = G.row_bytes[0], sb = G.sc_bytes[0];
         const int tw = warp < 2 ? t_w1 : t_w3;
         const int n_arr = 2 * n_sc;  // arrays in stage order: W1's, then W3's
-        int p = n0 > 0 ? u_begin / G.tiles0 : 0, tile = n0 > 0 ? u_begin - p * G.tiles0 : 0;
+        // the CTA's units in (present expert, tile) order; experts of which it owns no tile are skipped
+        int p = 0, tile = 0, tend = 0;
+        while (p < np && (tile = s_ta[p]) >= (tend = s_tb[p])) ++p;
         // One thread issues every copy of its warp, so its scalar code is on the critical path of the stream:
         // stage index and round are counted, nothing is divided inside the loops.
-        const uint8_t* rec = n0 > 0 ? bank.base + (size_t)s_slot[p] * bank.record_bytes : bank.base;
+        const uint8_t* rec = p < np ? bank.base + (size_t)s_slot[p] * bank.record_bytes : bank.base;
         const long long off_w = bank.off[tw] + (long long)(warp & 1) * 4 * rb;
         long long off_s = -1;
         if (warp < n_arr) {
@@ -607,9 +643,10 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
           mbar_expect_tx(bar, tx);
           bulk_g2s(dst + dst_w, rec + off_w + (size_t)tile * 8 * rb, (uint32_t)(4 * rb), bar);
           if (off_s >= 0) bulk_g2s(dst + dst_s, rec + off_s + (size_t)tile * sb, (uint32_t)sb, bar);
-          if (++tile == G.tiles0) {
-            tile = 0, ++p;
-            if (i + 1 < n0) rec = bank.base + (size_t)s_slot[p] * bank.record_bytes;
+          if (++tile == tend) {
+            ++p;
+            while (p < np && (tile = s_ta[p]) >= (tend = s_tb[p])) ++p;
+            if (p < np) rec = bank.base + (size_t)s_slot[p] * bank.record_bytes;
           }
           if (++idx == nst0) idx = 0, ++round;
         }
@@ -619,7 +656,8 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
       {
         const int rb = G.row_bytes[1], sb = G.sc_bytes[1];
         const int S0 = G.stage_bytes[0], S1 = G.stage_bytes[1];
-        int p = 0, tile = t_begin;
+        // unit order: group A (tile by tile, its experts inside), then group B the same way
+        int pa = 0, pn = nA, pi = 0, tl = 0;
         // phase-0 stage s was used uses(s) = full + (s < rest) times
         const int full = n0 / nst0, rest = n0 - full * nst0;
         const long long off_w = bank.off[t_w2] + (long long)warp * 4 * rb;
@@ -631,6 +669,10 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
         int end_byte = 0;  // end of the current phase-1 stage inside the ring
         int s_end = 0, s_end_byte = 0;  // first phase-0 stage that starts at or behind end_byte, and its start
         for (int q = 0; q < n1 && !err; ++q) {
+          // The reads of the hidden rows wait in line behind the copies that are in flight when they are issued, and
+          // nothing can start before they are back: only W2_HOLD units are asked for before the consumers have
+          // issued those reads.  The rest of W2 streams while phase 1 runs.
+          if (q == W2_HOLD && !mbar_wait(hold, 0u)) err = 1;
           if (round > 0) {
             if (!mbar_wait(&empty1[idx], (round - 1u) & 1u)) err = 1;
           } else {
@@ -643,13 +685,16 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
             }
           }
           if (err) break;
-          const uint8_t* rec = bank.base + (size_t)s_slot[p] * bank.record_bytes;
+          const uint8_t* rec = bank.base + (size_t)s_slot[pa + pi] * bank.record_bytes;
           uint8_t* dst = ring + (size_t)idx * S1;
           uint64_t* bar = &full1[idx];
           mbar_expect_tx(bar, tx);
-          bulk_g2s(dst + warp * 4 * rb, rec + off_w + (size_t)tile * 16 * rb, (uint32_t)(4 * rb), bar);
-          if (off_s >= 0) bulk_g2s(dst + G.sc_off[1] + warp * sb, rec + off_s + (size_t)tile * sb, (uint32_t)sb, bar);
-          if (++p == np) p = 0, ++tile;
+          bulk_g2s(dst + warp * 4 * rb, rec + off_w + (size_t)(t_begin + tl) * 16 * rb, (uint32_t)(4 * rb), bar);
+          if (off_s >= 0) bulk_g2s(dst + G.sc_off[1] + warp * sb, rec + off_s + (size_t)(t_begin + tl) * sb, (uint32_t)sb, bar);
+          if (++pi == pn) {
+            pi = 0;
+            if (++tl == ntl) tl = 0, pa = nA, pn = nB;
+          }
           if (++idx == nst1) idx = 0, ++round;
         }
       }
@@ -671,16 +716,37 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
       }
     }
     named_bar_sync(1, NCT);
+    // Rows of absent experts are not read in this launch, but their words get this launch's tag all the same (the CTA's
+    // share of each): a word's previous tag is then always the previous launch's, never an old one that could recur.
+    for (unsigned am = s_absent; am; am &= am - 1u) {
+      const int r = __ffs(am) - 1;
+      const int lo = (int)((unsigned)roww * blockIdx.x / gridDim.x), hi = (int)((unsigned)roww * (blockIdx.x + 1u) / gridDim.x);
+      for (int i = lo + tid; i < hi; i += NCT) st_relaxed_u32(fused_hidden + (size_t)r * roww + i, tag8);
+    }
     int n_done = 0;  // units of this pair so far (selects the exchange buffer)
 
     // -------- phase 0 --------
     // stage index and round of the pair's units are counted (no division per unit)
     int idx = pr % nst0;
     uint32_t rnd = (uint32_t)(pr / nst0);
-    int pu = n0 > 0 ? (u_begin + pr) / G.tiles0 : 0, tu = n0 > 0 ? (u_begin + pr) - pu * G.tiles0 : 0;  // expert and tile of unit i
+    // expert and tile of the pair's current unit: the CTA's units in (present expert, tile) order, NPAIR apart
+    int pu = 0, tu = 0, te = 0;
+    auto skip_units = [&](int n) {
+      while (pu < np) {
+        if (tu + n < te) {
+          tu += n;
+          return;
+        }
+        n -= te - tu;
+        ++pu;
+        while (pu < np && (tu = s_ta[pu]) >= (te = s_tb[pu])) ++pu;
+      }
+    };
+    while (pu < np && (tu = s_ta[pu]) >= (te = s_tb[pu])) ++pu;
+    skip_units(pr);
     for (int i = pr; i < n0; i += NPAIR, ++n_done) {
       if (!err && !mbar_wait(&full0[idx], rnd & 1u)) err = 1;
-      float2 r = unit_dot<FMT, 0, SDT>(ring + (size_t)idx * G.stage_bytes[0], G, act, pexs, zeros, g, t, part);
+      float2 r = unit_dot<FMT, 0, SDT>(ring + (size_t)idx * G.stage_bytes[0], G, act, pexs, zeros, g, t, part, 2);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty0[idx]);
       r.x += __shfl_xor_sync(0xffffffffu, r.x, 1), r.y += __shfl_xor_sync(0xffffffffu, r.y, 1);
@@ -695,127 +761,137 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
         if (numerics != CACHALOT_NUMERICS_F32) gv = bf16_round(gv), uv = bf16_round(uv);
         float h = swiglu(gv, uv, limit) * s_gw[p];
         if (numerics == CACHALOT_NUMERICS_BF16) h = bf16_round(h);
-        // bf16 numerics: h is a bf16 value already, so the hidden rows travel between the CTAs as bf16 (half the bytes
-        // every CTA reads back after the barrier)
-        const size_t hi_ = (size_t)s_route[p] * I + tile * 8 + (g >> 1) + 4 * (g & 1);
-        if (numerics == CACHALOT_NUMERICS_BF16) reinterpret_cast<__nv_bfloat16*>(hidden)[hi_] = __float2bfloat16_rn(h);
-        else hidden[hi_] = h;
+        const size_t hi_ = (size_t)s_route[p] * roww + hidden_word(tile * 8 + (g >> 1) + 4 * (g & 1));
+        // the value rounded to nearest at bit 8 (a bf16 value has nothing there), the tag in the low byte
+        st_relaxed_u32(fused_hidden + hi_, ((__float_as_uint(h) + 0x80u) & 0xffffff00u) | tag8);
       }
       idx += NPAIR;
       while (idx >= nst0) idx -= nst0, ++rnd;
-      tu += NPAIR;
-      while (tu >= G.tiles0) tu -= G.tiles0, ++pu;
+      skip_units(NPAIR);
     }
-
-    // -------- grid barrier: every CTA's hidden rows are written --------
-    named_bar_sync(1, NCT);
-    if (cw == 0) {
-      if (lane == 0) {
-        if (!grid_barrier(&grid_bar_word, gridDim.x, blockIdx.x == 0)) err = 2;
-      }
-      __syncwarp();
-    }
+    // every pair is through with x, whose operand row the hidden rows are about to overwrite
     named_bar_sync(1, NCT);
 
-    // phase 1 operand: the hidden rows of the present experts (operand row p = p-th present expert)
     const int row_stride1 = G.act_stride[1];
     const int nsub1 = I / SUB;
-    if (numerics == CACHALOT_NUMERICS_BF16) {
-      constexpr int SB = 5;  // blocks per thread and round (one round at 6 experts x 2880); all loads first
-      const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(hidden);
-      const int nblk = I / 16, total = np * nblk;
-      for (int base = 0; base < total; base += SB * NCT) {
-        uint4 q[SB][2];
-        int rr[SB], bbk[SB];
-        bool ok[SB];
+    const int kp = cw % KP1;               // the warp's part of the reduction dimension in phase 1
+    constexpr int UPR = NCW / KP1;         // phase-1 units the consumer warps work on at a time
+    static_assert(NCW % KP1 == 0, "the consumer warps must split into whole groups of KP1");
+    int q_base = 0;                        // phase-1 units of the groups before this one
+    for (int gsel = 0; gsel < 2; ++gsel) {
+      const int pa = gsel ? nA : 0, pn = gsel ? nB : nA;  // the group's experts: pa .. pa + pn - 1
+      if (pn == 0) break;
+      // phase-1 operand: the group's hidden rows (operand row p = p-th present expert).  A block of 16 values is
+      // read until every word carries this launch's tag; the lanes of a warp go round together (the conversion
+      // shuffles between the lanes that share a sub-block).
+      const int nblk = I / 16, nblk_pad = roww / 16, total = pn * nblk_pad;  // padded: a warp's 32 blocks share a chunk
+      {
+        constexpr int SB = 3;  // blocks per thread and round (4 experts x 2880 in one round); all loads are issued first
+        for (int base = 0; base < total; base += SB * NCT) {
+          uint4 q[SB][4];
+          int rr[SB], bbk[SB];
+          bool ok[SB], bad[SB];
 #pragma unroll
-        for (int h = 0; h < SB; ++h) {
-          const int idx = base + h * NCT + tid;
-          ok[h] = idx < total;
-          rr[h] = ok[h] ? idx / nblk : 0;
-          bbk[h] = ok[h] ? idx - rr[h] * nblk : 0;
-          q[h][0] = q[h][1] = make_uint4(0, 0, 0, 0);
-          if (ok[h]) {
-            const uint4* src = reinterpret_cast<const uint4*>(hb + (size_t)s_route[rr[h]] * I + bbk[h] * 16);
-            q[h][0] = __ldcg(src), q[h][1] = __ldcg(src + 1);  // written by other CTAs in this launch: read from L2
+          for (int h = 0; h < SB; ++h) {
+            const int ix = base + h * NCT + tid;
+            rr[h] = ix < total ? ix / nblk_pad : 0;
+            bbk[h] = ix < total ? ix - rr[h] * nblk_pad : nblk;
+            ok[h] = bbk[h] < nblk;
+            if (!ok[h]) bbk[h] = 0;
+            rr[h] += pa;
+            bad[h] = ok[h];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) q[h][i] = make_uint4(0, 0, 0, 0);
           }
-        }
+          for (uint32_t tries = 0;; ++tries) {
 #pragma unroll
-        for (int h = 0; h < SB; ++h) {
-          if (base + h * NCT < total) {  // warp-uniform
-            const uint32_t wds[8] = {q[h][0].x, q[h][0].y, q[h][0].z, q[h][0].w, q[h][1].x, q[h][1].y, q[h][1].z, q[h][1].w};
-            float v[16];
+            for (int h = 0; h < SB; ++h) {
+              if (bad[h]) {
+                const uint32_t* src = fused_hidden + (size_t)s_route[rr[h]] * roww + ((bbk[h] >> 5) << 9) + ((bbk[h] & 31) << 2);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[2 * i] = __uint_as_float(wds[i] << 16), v[2 * i + 1] = __uint_as_float(wds[i] & 0xffff0000u);
-            convert_block<FMT>(act + (size_t)rr[h] * row_stride1, pexs + rr[h] * nsub1, bbk[h], ok[h], v);
+                for (int i = 0; i < 4; ++i) q[h][i] = ld_relaxed_v4(src + 128 * i);
+              }
+            }
+            if (gsel == 0 && base == 0 && tries == 0) {  // once per launch and warp
+              __syncwarp();
+              if (lane == 0) mbar_arrive(hold);
+            }
+            bool any = false;
+#pragma unroll
+            for (int h = 0; h < SB; ++h) {
+              if (bad[h]) {
+                uint32_t diff = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  diff |= ((q[h][i].x ^ tag8) | (q[h][i].y ^ tag8) | (q[h][i].z ^ tag8) | (q[h][i].w ^ tag8)) & 0xffu;
+                bad[h] = diff != 0;
+                any |= bad[h];
+              }
+            }
+            if (!__any_sync(0xffffffffu, any)) break;
+            if (tries >= HIDDEN_TRIES) {  // a CTA did not deliver: flag it and go on with what is there
+              err = 2;
+              break;
+            }
+            if (tries > 4) __nanosleep(100);
+          }
+#pragma unroll
+          for (int h = 0; h < SB; ++h) {
+            if (base + h * NCT < total) {  // warp-uniform
+              float v[16];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                v[4 * i] = __uint_as_float(q[h][i].x & 0xffffff00u), v[4 * i + 1] = __uint_as_float(q[h][i].y & 0xffffff00u);
+                v[4 * i + 2] = __uint_as_float(q[h][i].z & 0xffffff00u), v[4 * i + 3] = __uint_as_float(q[h][i].w & 0xffffff00u);
+              }
+              convert_block<FMT>(act + (size_t)rr[h] * row_stride1, pexs + rr[h] * nsub1, bbk[h], ok[h], v);
+            }
           }
         }
       }
-    } else {
-      constexpr int SB = 4;  // blocks per thread and round; all their loads are issued before any is used
-      const int nblk = I / 16, total = np * nblk;
-      for (int base = 0; base < total; base += SB * NCT) {
-        float4 q[SB][4];
-        int rr[SB], bbk[SB];
-        bool ok[SB];
-#pragma unroll
-        for (int h = 0; h < SB; ++h) {
-          const int idx = base + h * NCT + tid;
-          ok[h] = idx < total;
-          rr[h] = ok[h] ? idx / nblk : 0;
-          bbk[h] = ok[h] ? idx - rr[h] * nblk : 0;
-          if (ok[h]) {
-            const float4* src = reinterpret_cast<const float4*>(hidden + (size_t)s_route[rr[h]] * I + bbk[h] * 16);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) q[h][i] = __ldcg(src + i);  // written by other CTAs in this launch: read from L2
-          } else {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) q[h][i] = make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-        }
-#pragma unroll
-        for (int h = 0; h < SB; ++h) {
-          if (base + h * NCT < total) {  // warp-uniform
-            float v[16];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) v[4 * i] = q[h][i].x, v[4 * i + 1] = q[h][i].y, v[4 * i + 2] = q[h][i].z, v[4 * i + 3] = q[h][i].w;
-            convert_block<FMT>(act + (size_t)rr[h] * row_stride1, pexs + rr[h] * nsub1, bbk[h], ok[h], v);
-          }
-        }
-      }
-    }
-    named_bar_sync(1, NCT);
+      named_bar_sync(1, NCT);
 
-    // -------- phase 1: unit q of the CTA = (tile t_begin + q / np, expert q % np) --------
-    for (int q = pr; q < n1; q += NPAIR, ++n_done) {
-      const int idx = q % nst1;
-      const int tl = q / np, p = q - tl * np;
-      if (!err && !mbar_wait(&full1[idx], (uint32_t)(q / nst1) & 1u)) err = 1;
-      float2 r = unit_dot<FMT, 1, SDT>(ring + (size_t)idx * G.stage_bytes[1], G, act + (size_t)p * row_stride1, pexs + p * nsub1, zeros, g, t, part);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty1[idx]);
-      r.x += __shfl_xor_sync(0xffffffffu, r.x, 1), r.y += __shfl_xor_sync(0xffffffffu, r.y, 1);
-      r.x += __shfl_xor_sync(0xffffffffu, r.x, 2), r.y += __shfl_xor_sync(0xffffffffu, r.y, 2);
-      float2* xb2 = xch + (pr * 2 + (n_done & 1)) * 8;
-      if (part == 1 && t == 0) xb2[g] = r;
-      named_bar_sync(pair_bar, 64);
-      if (part == 0 && t == 0) {
-        const float2 o = xb2[g];
-        float y0 = r.x + o.x, y1 = r.y + o.y;
-        if (numerics != CACHALOT_NUMERICS_F32) y0 = bf16_round(y0), y1 = bf16_round(y1);
-        const int wr = (g >> 1) + 4 * (g & 1);  // the weight row of MMA row g
-        ybuf[(tl * KMAX + p) * 16 + wr] = y0;
-        ybuf[(tl * KMAX + p) * 16 + wr + 8] = y1;
+      // -------- phase 1 of the group: unit u = (tile u / pn, expert pa + u % pn); a warp takes part kp of every
+      // UPR-th unit and leaves its partial sums in shared memory --------
+      const int n1g = ntl * pn;
+      for (int u = cw / KP1; u < n1g; u += UPR) {
+        const int q = q_base + u;
+        const int sidx = q % nst1;
+        const int tl = u / pn, p = pa + (u - tl * pn);
+        if (!err && !mbar_wait(&full1[sidx], (uint32_t)(q / nst1) & 1u)) err = 1;
+        float2 r = unit_dot<FMT, 1, SDT>(ring + (size_t)sidx * G.stage_bytes[1], G, act + (size_t)p * row_stride1, pexs + p * nsub1, zeros, g, t, kp, KP1);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty1[sidx]);
+        r.x += __shfl_xor_sync(0xffffffffu, r.x, 1), r.y += __shfl_xor_sync(0xffffffffu, r.y, 1);
+        r.x += __shfl_xor_sync(0xffffffffu, r.x, 2), r.y += __shfl_xor_sync(0xffffffffu, r.y, 2);
+        if (t == 0) {
+          const int wr = (g >> 1) + 4 * (g & 1);  // the weight row of MMA row g
+          float* y = ybuf + (((size_t)tl * KMAX + p) * KP1 + kp) * 16;
+          y[wr] = r.x, y[wr + 8] = r.y;
+        }
       }
+      q_base += n1g;
     }
     named_bar_sync(1, NCT);
-    // sum over the experts in routing order
-    const int n_mine = (t_end - t_begin) * 16;
+    // sum over the experts in routing order; an expert's value is the sum of its KP1 partial sums in part order
+    // (rounded to bf16 where the numerics ask for it)
+    auto expert_sum = [&](int tl, int r) {
+      float tot = 0.f;
+      for (int p = 0; p < np; ++p) {
+        const float* y = ybuf + ((size_t)tl * KMAX + p) * KP1 * 16 + r;
+        float v = y[0];
+#pragma unroll
+        for (int c = 1; c < KP1; ++c) v += y[c * 16];
+        if (numerics != CACHALOT_NUMERICS_F32) v = bf16_round(v);
+        tot += v;
+      }
+      return tot;
+    };
+    const int n_mine = ntl * 16;
     if (P.world <= 0) {
       for (int o = tid; o < n_mine; o += NCT) {
         const int tl = o >> 4, r = o & 15;
-        float tot = 0.f;
-        for (int p = 0; p < np; ++p) tot += ybuf[(tl * KMAX + p) * 16 + r];
+        const float tot = expert_sum(tl, r);
         if constexpr (sizeof(OutT) == 2)
           out[(t_begin + tl) * 16 + r] = __float2bfloat16_rn(tot);
         else
@@ -830,8 +906,7 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
       const int slot = (int)(xe & 1u), H1 = bank.hidden;
       for (int o = tid; o < n_mine; o += NCT) {
         const int tl = o >> 4, r = o & 15;
-        float tot = 0.f;
-        for (int p = 0; p < np; ++p) tot += ybuf[(tl * KMAX + p) * 16 + r];
+        const float tot = expert_sum(tl, r);
         const size_t at = ((size_t)slot * P.world + P.rank) * H1 + (size_t)t_begin * 16 + o;
         for (int q = 0; q < P.world; ++q) P.inbox[q][at] = tot;
       }
@@ -875,6 +950,16 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
         }
       }
     }
+    // the launch number moves on once per launch: by the CTA that takes the last ticket (every CTA has read the
+    // number long before: none gets here before all have written their hidden values)
+    if (tid == 0) {
+      const unsigned ticket = atomicAdd(&fused_epoch[1], 1u);
+      if (ticket == gridDim.x - 1) {
+        const unsigned nx = tag32 + 1u;
+        fused_epoch[1] = 0u;
+        fused_epoch[0] = nx ? nx : 1u;
+      }
+    }
     if (err && lane == 0 && status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
   }
 }
@@ -883,8 +968,21 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 constexpr int MAX_DEVICES = 64;
 
+// SM count of the current device (the grid size); 148 when there is no device to ask
+int device_sms() {
+  static int cached[MAX_DEVICES] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return 148;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 template <int FMT>
-bool make_geo_fmt(const BankView& v, int k, Geo* out) {
+bool make_geo_fmt(const BankView& v, int k, int sms, Geo* out) {
   Geo G = {};
   constexpr bool fp4 = FMT == CACHALOT_BANK_FP4;
   constexpr int STEP = Fm<FMT>::STEP, SUB = Fm<FMT>::SUB;
@@ -895,7 +993,7 @@ bool make_geo_fmt(const BankView& v, int k, Geo* out) {
     G.row_bytes[p] = fp4 ? G.K[p] / 2 : G.K[p] / 4;
   }
   if (!fp4 && v.hidden % 128) return false;  // phase 0 indexes scale groups per row
-  if (v.inter % 8 || v.hidden % 16) return false;
+  if (v.inter % 8 || v.hidden % 16 || v.inter > INTER_MAX) return false;
   if (v.hidden > 16 * 3 * Fm<FMT>::NCW * 32) return false;  // x is staged in at most three 16-element blocks per thread
   G.tiles0 = v.inter / 8, G.tiles1 = v.hidden / 16;
   int n_sc[2];
@@ -931,7 +1029,9 @@ bool make_geo_fmt(const BankView& v, int k, Geo* out) {
   G.off_bar = p, p += 2048;  // mbarriers (512 B), 512 zero bytes, pair exchange buffers
   G.off_act = p, p += act;
   G.off_pe = p, p += pe;
-  G.off_part = p, p += MAX_TILES * KMAX * 16 * 4;  // per-expert results of the CTA's output tiles
+  G.max_tiles = (G.tiles1 + sms - 1) / sms;
+  if (G.max_tiles > MAX_TILES) return false;
+  G.off_part = p, p += G.max_tiles * KMAX * KP1 * 16 * 4;  // partial sums of the CTA's output tiles per expert and part
   G.off_ring = p;
   const int room = SMEM_LIMIT - 256 /* static shared */ - p;
   for (int ph = 0; ph < 2; ++ph) {
@@ -947,7 +1047,8 @@ bool make_geo_fmt(const BankView& v, int k, Geo* out) {
 }
 
 bool make_geo(const BankView& v, int k, Geo* out) {
-  return v.format == CACHALOT_BANK_FP4 ? make_geo_fmt<CACHALOT_BANK_FP4>(v, k, out) : make_geo_fmt<CACHALOT_BANK_AFFINE>(v, k, out);
+  const int sms = device_sms();
+  return v.format == CACHALOT_BANK_FP4 ? make_geo_fmt<CACHALOT_BANK_FP4>(v, k, sms, out) : make_geo_fmt<CACHALOT_BANK_AFFINE>(v, k, sms, out);
 }
 
 }  // namespace
@@ -974,23 +1075,9 @@ static int launch_fused_fmt(const BankView& v, const Geo& G, const RouteArgs& R,
   float* hidden = static_cast<float*>(workspace);
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return fail(CACHALOT_ECUDA, "moe_decode (fused): no current device");
-  static int sm_count[MAX_DEVICES] = {};
-  if (!sm_count[dev] && (cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count[dev] <= 0))
-    return fail(CACHALOT_ECUDA, "moe_decode (fused): cannot read the SM count");
-  const int sms = sm_count[dev];
+  const int sms = device_sms();
   const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
-  Geo Gl = G;
-  // the byte-balanced split needs every CTA's share to be larger than the phase-1 tiles it owns
-  {
-    const long long U0 = (long long)k * G.tiles0, b0 = G.unit_bytes[0], b1 = (long long)k * G.unit_bytes[1];
-    const long long T = U0 * b0 + (long long)G.tiles1 * b1;
-    const long long max_tiles = (G.tiles1 + sms - 1) / sms;
-    // the grid barrier makes every CTA wait for the slowest one in each phase, so the units of a phase are
-    // split evenly (a split by total bytes would only pay if the kernel were bandwidth-bound throughout)
-    Gl.balance = 0;
-    (void)T;
-    if (max_tiles > MAX_TILES) return CACHALOT_EUNSUPPORTED;
-  }
+  const Geo& Gl = G;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)sms);
   cfg.blockDim = dim3(Fm<FMT>::NTHREADS);
