@@ -419,6 +419,36 @@ __device__ __forceinline__ float2 unit_dot(const uint8_t* stage, const Geo& G, c
   return make_float2(accA, accB);
 }
 
+// k rounds of a warp-wide arg-best over the experts' order keys (shared memory).  Lane l keeps experts l, l + 32, ...
+// in registers (NE of them); a taken expert's key drops to 0 (below every real one).  Returns the expert of output
+// position `lane` (-1: none).
+template <int NE>
+__device__ __forceinline__ int topk_rounds(const uint32_t* r_ord, int n_experts, int k, bool low_wins, bool ascending, int lane) {
+  uint32_t ord[NE];
+#pragma unroll
+  for (int i = 0; i < NE; ++i) ord[i] = (i * 32 + lane < n_experts) ? r_ord[i * 32 + lane] : 0u;
+  int my_e = -1;
+  for (int r = 0; r < k; ++r) {
+    uint32_t bo = 0u;
+    int bi = -1;
+#pragma unroll
+    for (int i = 0; i < NE; ++i) {
+      const bool better = low_wins ? ord[i] > bo : (ord[i] >= bo && ord[i] != 0u);
+      if (better) bo = ord[i], bi = i * 32 + lane;
+    }
+    const uint32_t wo = __reduce_max_sync(0xffffffffu, bo);
+    const bool cand = bo == wo && bi >= 0;
+    const int win = low_wins ? (int)__reduce_min_sync(0xffffffffu, cand ? (unsigned)bi : 0x7fffffffu)
+                             : (int)__reduce_max_sync(0xffffffffu, cand ? (unsigned)(bi + 1) : 0u) - 1;
+    if (wo == 0u) break;  // fewer than k experts
+#pragma unroll
+    for (int i = 0; i < NE; ++i)
+      if (i * 32 + lane == win) ord[i] = 0u;
+    if (lane == (ascending ? k - 1 - r : r)) my_e = win;
+  }
+  return my_e;
+}
+
 template <int FMT, int SDT, typename OutT>
 __global__ void __launch_bounds__(Fm<FMT>::NTHREADS, 1)
 fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ slots,
@@ -513,28 +543,11 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
       // the larger one, as route_topk_kernel does.
       const bool low_wins = R.mode == CACHALOT_ROUTER_SIGMOID;
       const bool ascending = !low_wins;  // the sqrt-softplus router writes the weakest first
-      uint32_t ord[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) ord[i] = (i * 32 + lane < R.n_experts) ? r_ord[i * 32 + lane] : 0u;
+      // the rounds are unrolled over the entries a lane keeps: as few as the expert count needs
       int my_e = -1;
-      for (int r = 0; r < k; ++r) {
-        uint32_t bo = 0u;
-        int bi = -1;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const bool better = low_wins ? ord[i] > bo : (ord[i] >= bo && ord[i] != 0u);
-          if (better) bo = ord[i], bi = i * 32 + lane;
-        }
-        const uint32_t wo = __reduce_max_sync(0xffffffffu, bo);
-        const bool cand = bo == wo && bi >= 0;
-        const int win = low_wins ? (int)__reduce_min_sync(0xffffffffu, cand ? (unsigned)bi : 0x7fffffffu)
-                                 : (int)__reduce_max_sync(0xffffffffu, cand ? (unsigned)(bi + 1) : 0u) - 1;
-        if (wo == 0u) break;  // fewer than k experts
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i * 32 + lane == win) ord[i] = 0u;
-        if (lane == (ascending ? k - 1 - r : r)) my_e = win;
-      }
+      if (R.n_experts <= 128) my_e = topk_rounds<4>(r_ord, R.n_experts, k, low_wins, ascending, lane);
+      else if (R.n_experts <= 384) my_e = topk_rounds<12>(r_ord, R.n_experts, k, low_wins, ascending, lane);
+      else my_e = topk_rounds<32>(r_ord, R.n_experts, k, low_wins, ascending, lane);
       // lane r holds output position r; the total is added up in output order as route_topk_kernel does
       float total = 0.f;
       for (int r = 0; r < k; ++r) {
