@@ -39,7 +39,7 @@ SWIGLU_LIMIT = 10.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # capture summarised under profiles/ (None until a capture exists for the workload)
-NCU_TRAFFIC_BYTES = {("affine2", 1, "fused"): 59832832 + 1246720}
+NCU_TRAFFIC_BYTES = {("affine2", 1, "fused"): 59843072 + 1057792, ("fp4", 1, "fused"): 112921344 + 16384}
 
 
 def parse_args():
