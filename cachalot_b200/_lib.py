@@ -42,7 +42,7 @@ class BankDesc(C.Structure):
 class PeerCtx(C.Structure):
     """Mirror of `cachalot_peer_ctx`."""
 
-    _fields_ = [("inbox", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("epoch", C.c_void_p), ("world", C.c_int32), ("rank", C.c_int32)]
+    _fields_ = [("inbox", C.c_void_p * 8), ("epoch", C.c_void_p), ("world", C.c_int32), ("rank", C.c_int32)]
 
 
 _vp, _i, _f, _sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
@@ -80,7 +80,6 @@ SIGNATURES = {
     "cachalot_peer_sum_flag_bytes": (_sz, [_i]),
     "cachalot_peer_sum": (_i, [_vp, _vp, _i, _i, _vp, _vp, _i, _vp, _vp, _vp]),
     "cachalot_peer_layer_inbox_bytes": (_sz, [_i, _i]),
-    "cachalot_peer_layer_flag_bytes": (_sz, [_i]),
     "cachalot_moe_layer_decode_peer": (_i, [_vp, _desc, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _i, _i, _f, _i, _vp, _sz, _vp, _i,
                                             _vp, _vp, _vp, _vp, _vp]),
     "cachalot_moe_prefill": (_i, [_vp, _desc, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp, _sz, _vp, _vp, _vp]),

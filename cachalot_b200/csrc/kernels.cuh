@@ -49,14 +49,12 @@ size_t decode_mma_workspace_bytes(int hidden, int inter, int rows, int k);
 bool decode_mma_supported(const BankView& v, int rows, int k);
 
 
-// Expert-parallel exchange done in the tail of the single-launch decode kernel: every rank's inbox (f32
-// [2 slots][world][hidden]) and flag array (u32 [2 slots][world][PEER_LINK_CTAS]) as mapped in this process, the
-// device-resident exchange counter, and this rank.  world == 0: no exchange.
+// Expert-parallel exchange done in the tail of the single-launch decode kernel: every rank's inbox (u64
+// [2 slots][world][hidden]: fp32 value | number of the exchange << 32) as mapped in this process, the device-resident
+// exchange counter, and this rank.  world == 0: no exchange.
 constexpr int PEER_LINK_MAX = 8;
-constexpr int PEER_LINK_CTAS = 256;
 struct PeerLink {
-  float* inbox[PEER_LINK_MAX];
-  uint32_t* flags[PEER_LINK_MAX];
+  unsigned long long* inbox[PEER_LINK_MAX];
   uint32_t* epoch;  // u32 [2]: exchanges done, arrival ticket
   int world, rank;
 };

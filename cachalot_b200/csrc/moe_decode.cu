@@ -385,8 +385,7 @@ extern "C" int cachalot_moe_layer_decode(const void* bank, const cachalot_bank_d
                              status, stream);
 }
 
-extern "C" size_t cachalot_peer_layer_inbox_bytes(int world, int hidden) { return (size_t)2 * world * hidden * sizeof(float); }
-extern "C" size_t cachalot_peer_layer_flag_bytes(int world) { return (size_t)2 * world * PEER_LINK_CTAS * sizeof(uint32_t); }
+extern "C" size_t cachalot_peer_layer_inbox_bytes(int world, int hidden) { return (size_t)2 * world * hidden * sizeof(unsigned long long); }
 
 extern "C" int cachalot_moe_layer_decode_peer(const void* bank, const cachalot_bank_desc* desc, const void* x_bf16,
                                               const float* logits, const float* bias, const int32_t* slot_table, int layer,
@@ -412,15 +411,10 @@ extern "C" int cachalot_moe_layer_decode_peer(const void* bank, const cachalot_b
   if (!aligned(workspace, 256) || !aligned(x_bf16, 16) || !aligned(out, 4)) return fail(CACHALOT_EALIGN, "moe_layer_decode_peer: workspace needs 256-byte, x 16-byte alignment");
   if (!layer_fused_supported(v, n_experts, k))
     return fail(CACHALOT_EUNSUPPORTED, "moe_layer_decode_peer: the single-launch kernel does not cover this bank shape or top-k; use cachalot_moe_layer_decode and cachalot_peer_sum");
-  int sms = 0, dev = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (sms > PEER_LINK_CTAS) return fail(CACHALOT_EUNSUPPORTED, "moe_layer_decode_peer: %d SMs exceed the %d flag columns", sms, PEER_LINK_CTAS);
   PeerLink P = {};
   for (int r = 0; r < peer->world; ++r) {
-    P.inbox[r] = static_cast<float*>(peer->inbox[r]);
-    P.flags[r] = static_cast<uint32_t*>(peer->flags[r]);
-    if (!P.inbox[r] || !P.flags[r] || !aligned(P.inbox[r], 16)) return fail(CACHALOT_EINVAL, "moe_layer_decode_peer: rank %d's inbox or flags pointer is null or misaligned", r);
+    P.inbox[r] = static_cast<unsigned long long*>(peer->inbox[r]);
+    if (!P.inbox[r] || !aligned(P.inbox[r], 16)) return fail(CACHALOT_EINVAL, "moe_layer_decode_peer: rank %d's inbox pointer is null or misaligned", r);
   }
   P.epoch = peer->epoch, P.world = peer->world, P.rank = peer->rank;
   return launch_layer_fused(v, x_bf16, logits, bias, slot_table, layer, n_experts, k, mode, gate_temp, route_scale, norm_topk_prob,

@@ -911,40 +911,40 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
           out[(t_begin + tl) * 16 + r] = tot;
       }
     } else if (n_mine > 0) {
-      // Expert parallel: this rank's sum is a partial one.  The CTA stores its rows into row `rank` of every rank's
-      // inbox (plain stores over NVLink; every rank splits the output rows over its CTAs in the same way), raises its
-      // flag on every rank, waits with a bound for the same CTA of every rank and adds the rows in rank order: no
-      // second launch, and every rank ends with the same bits.  Two inbox slots alternate: a rank cannot be two
-      // exchanges ahead of a peer, because finishing one takes every peer's flag of it.
+      // Expert parallel: this rank's sum is a partial one.  A thread stores its output value into row `rank` of every
+      // rank's inbox as ONE 64-bit word (value, number of this exchange): plain relaxed stores at system scope over
+      // NVLink, single-copy atomic, so the word needs no flag and no fence behind it.  It then reads the same element
+      // of every rank's row in its own inbox until the word carries this exchange's number (bounded), and adds the
+      // values in rank order: no second launch, and every rank ends with the same bits.  Two inbox slots alternate: a
+      // rank cannot be two exchanges ahead of a peer, because finishing one takes every peer's values of it.
       const int slot = (int)(xe & 1u), H1 = bank.hidden;
       for (int o = tid; o < n_mine; o += NCT) {
-        const int tl = o >> 4, r = o & 15;
-        const float tot = expert_sum(tl, r);
-        const size_t at = ((size_t)slot * P.world + P.rank) * H1 + (size_t)t_begin * 16 + o;
-        for (int q = 0; q < P.world; ++q) P.inbox[q][at] = tot;
-      }
-      named_bar_sync(1, NCT);
-      if (tid < P.world) {
-        const size_t mine = ((size_t)slot * P.world + P.rank) * PEER_LINK_CTAS + blockIdx.x;
-        // release at system scope: the CTA's stores (ordered before this thread by the CTA barrier) first
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(P.flags[tid] + mine), "r"(xe) : "memory");
-        const uint32_t* f = P.flags[P.rank] + ((size_t)slot * P.world + tid) * PEER_LINK_CTAS + blockIdx.x;
-        uint32_t i = 0, got;
-        for (;;) {
-          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(f) : "memory");
-          if (got == xe) break;
-          if (++i >= (1u << 22)) {  // a peer did not show up: flag it and carry on with what is there
-            if (status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
-            break;
+        const float mine = expert_sum(o >> 4, o & 15);
+        const size_t el = (size_t)t_begin * 16 + o;
+        const unsigned long long word = (unsigned long long)__float_as_uint(mine) | ((unsigned long long)xe << 32);
+        const size_t at = ((size_t)slot * P.world + P.rank) * H1 + el;
+        for (int q = 0; q < P.world; ++q)
+          asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(P.inbox[q] + at), "l"(word) : "memory");
+        float tot = 0.f;
+        for (int q = 0; q < P.world; ++q) {
+          const unsigned long long* src = P.inbox[P.rank] + ((size_t)slot * P.world + q) * H1 + el;
+          unsigned long long got = 0ull;
+          if (q == P.rank) {
+            got = word;
+          } else {
+            for (uint32_t i = 0;; ++i) {
+              asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(got) : "l"(src) : "memory");
+              if ((uint32_t)(got >> 32) == xe) break;
+              if (i >= (1u << 22)) {  // a peer did not show up: flag it and count its value as zero
+                if (status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
+                got = 0ull;
+                break;
+              }
+              if (i > 64) __nanosleep(64);
+            }
           }
-          if (i > 64) __nanosleep(64);
+          tot += __uint_as_float((uint32_t)got);
         }
-      }
-      named_bar_sync(1, NCT);
-      const float* rows = P.inbox[P.rank] + (size_t)slot * P.world * H1 + (size_t)t_begin * 16;
-      for (int o = tid; o < n_mine; o += NCT) {
-        float tot = __ldcg(rows + o);  // written by other GPUs: read past L1
-        for (int q = 1; q < P.world; ++q) tot += __ldcg(rows + (size_t)q * H1 + o);
         if constexpr (sizeof(OutT) == 2)
           out[t_begin * 16 + o] = __float2bfloat16_rn(tot);
         else

@@ -122,16 +122,15 @@ class PeerLayer:
         else:
             self.group, self.world, self.rank = None, 1, 0
         inbox = (int(lib.cachalot_peer_layer_inbox_bytes(self.world, hidden)) + 255) // 256 * 256
-        flags = int(lib.cachalot_peer_layer_flag_bytes(self.world))
         if self.world > 1:
-            self.buf, self.handle, ptrs = _symmetric_buffer(inbox + flags, device, self.group)
+            self.buf, self.handle, ptrs = _symmetric_buffer(inbox, device, self.group)
         else:
-            self.buf = torch.zeros(inbox + flags, dtype=torch.uint8, device=device)
+            self.buf = torch.zeros(inbox, dtype=torch.uint8, device=device)
             ptrs = [self.buf.data_ptr()]
         self.epoch = torch.zeros(2, dtype=torch.int32, device=device)
         ctx = PeerCtx()
         for r, p in enumerate(ptrs):
-            ctx.inbox[r], ctx.flags[r] = p, p + inbox
+            ctx.inbox[r] = p
         ctx.epoch, ctx.world, ctx.rank = self.epoch.data_ptr(), self.world, self.rank
         self.ctx, self.hidden = ctx, hidden
 

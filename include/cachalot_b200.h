@@ -312,23 +312,22 @@ CACHALOT_API int cachalot_peer_sum(void* const* inbox_ptrs /* host */, void* con
                       const float* partial, float* out, int n, uint32_t* epoch, int* status, cachalot_stream_t stream);
 
 /* No counterpart in the reference.  cachalot_moe_layer_decode for an expert-parallel rank with the sum over the ranks
- * done in the tail of the same launch: every CTA stores the output rows it owns into row `rank` of every rank's inbox
- * (plain peer stores over NVLink, no multicast), raises a flag per (rank, CTA), waits with a bound for the same CTA of
- * every peer and adds the rows in rank order, so `out` holds the full layer output on every rank and all ranks hold
- * the same bits.  The ranks must run on GPUs with the same number of SMs and make the same sequence of calls; a
- * peer that does not show up makes the wait expire (CACHALOT_STATUS_WAIT_EXPIRED) and the call returns with an
- * incomplete sum.  inbox[r] / flags[r] (device pointers as mapped in THIS process): rank r's inbox of
- * cachalot_peer_layer_inbox_bytes(world, hidden) bytes and flag array of cachalot_peer_layer_flag_bytes(world)
- * bytes in memory every rank can write, zeroed once; epoch: u32 [2] in local device memory, zeroed once.  Only bank
- * shapes and top-k the single-launch kernel covers (else CACHALOT_EUNSUPPORTED: use cachalot_peer_sum). */
+ * done in the tail of the same launch: every thread that owns an output element stores it into row `rank` of every
+ * rank's inbox as one 64-bit word (fp32 value | number of the exchange << 32; plain peer stores over NVLink, no
+ * multicast, no flag, no fence), reads the same element of every rank's row in its own inbox until the word carries
+ * this exchange's number, and adds the values in rank order, so `out` holds the full layer output on every rank and
+ * all ranks hold the same bits.  The ranks must run on GPUs with the same number of SMs and make the same sequence
+ * of calls; a peer that does not show up makes the bounded wait expire (CACHALOT_STATUS_WAIT_EXPIRED), its values
+ * count as zero and the call returns instead of hanging.  inbox[r] (device pointer as mapped in THIS process): rank
+ * r's inbox of cachalot_peer_layer_inbox_bytes(world, hidden) bytes in memory every rank can write, 16-byte aligned,
+ * zeroed once; epoch: u32 [2] in local device memory, zeroed once.  Only bank shapes and top-k the single-launch
+ * kernel covers (else CACHALOT_EUNSUPPORTED: use cachalot_peer_sum). */
 typedef struct {
   void* inbox[8];
-  void* flags[8];
   uint32_t* epoch;
   int32_t world, rank;
 } cachalot_peer_ctx;
 CACHALOT_API size_t cachalot_peer_layer_inbox_bytes(int world, int hidden);
-CACHALOT_API size_t cachalot_peer_layer_flag_bytes(int world);
 CACHALOT_API int cachalot_moe_layer_decode_peer(const void* bank, const cachalot_bank_desc* desc /* host */, const void* x_bf16,
                                    const float* logits, const float* bias, const int32_t* slot_table, int layer,
                                    int n_experts, int k, int mode, float gate_temp, float route_scale, int norm_topk_prob,

@@ -162,12 +162,11 @@ def test_layer_exchange_missing_peer_expires_not_hangs():
     from cachalot_b200._lib import lib
     bank, hidden, n_exp = _small_layer()
     peer = ep.PeerLayer(hidden, torch.device("cuda"))
-    other = torch.zeros(int(lib.cachalot_peer_layer_inbox_bytes(2, hidden)) + 256 + int(lib.cachalot_peer_layer_flag_bytes(2)),
-                        dtype=torch.uint8, device="cuda")   # stands for rank 1's memory; nobody signals from there
+    other = torch.zeros(int(lib.cachalot_peer_layer_inbox_bytes(2, hidden)) + 256,
+                        dtype=torch.uint8, device="cuda")   # stands for rank 1's memory; nobody writes from there
     mine = torch.zeros_like(other)
-    inbox = (int(lib.cachalot_peer_layer_inbox_bytes(2, hidden)) + 255) // 256 * 256
     for r, buf in enumerate((mine, other)):
-        peer.ctx.inbox[r], peer.ctx.flags[r] = buf.data_ptr(), buf.data_ptr() + inbox
+        peer.ctx.inbox[r] = buf.data_ptr()
     peer.ctx.world, peer.ctx.rank = 2, 0
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     g = torch.Generator().manual_seed(9)
