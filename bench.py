@@ -50,8 +50,8 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--bank", default="affine2", choices=["affine2", "fp4"])
     p.add_argument("--batch", type=int, default=1)
-    p.add_argument("--workload", default="decode", choices=["decode", "prefill", "fp8"],
-                   help="prefill: one 4096-token chunk through one FP4 layer, Zipf(1.1) expert popularity (1 GPU)")
+    p.add_argument("--workload", default="decode", choices=["decode", "prefill", "fp8", "head"],
+                   help="prefill: one 4096-token chunk through one FP4 layer, Zipf(1.1) expert popularity (1 GPU); fp8: the FP8 trunk GEMV; head: the bf16 output head GEMV")
     p.add_argument("--tokens", type=int, default=4096, help="prefill chunk length")
     p.add_argument("--experts", type=int, default=EXPERTS, help="prefill: experts in the layer (smaller = a case sized for profiling)")
     p.add_argument("--distinct-layers", type=int, default=8)
@@ -879,6 +879,85 @@ def run_fp8(args):
     print(json.dumps(line), flush=True)
 
 
+HEAD_SHAPE = (129280, 5120)   # the reference's output head (model/bf16_gemv_metal.py:4-8)
+
+
+def run_head(args):
+    """One step = one bf16-weight fp32 GEMV over the output head ([129280,5120] bf16 = 1.32 GB, ten times L2),
+    `--batch` activation rows (1..8) sharing the pass; value = algorithmic GB/s.  One GPU (not sharded)."""
+    import numpy as np
+    import torch
+
+    import cachalot_b200 as cb
+    from cachalot_b200._lib import check, lib
+    n, k = HEAD_SHAPE
+    B = max(1, min(8, args.batch))
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(11)
+    w = (torch.randn((n, k), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    P = 8
+    x_host = torch.randn((P, B, k), generator=torch.Generator().manual_seed(3)).pin_memory()
+    x_dev, x = x_host.to(dev), torch.empty((B, k), device=dev)
+    y, y_host = torch.empty((B, n), device=dev), torch.empty((B, n)).pin_memory()
+    stream = torch.cuda.Stream(device=dev)
+
+    def timed(steps, host=False):
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for i in range(steps):
+                x.copy_((x_host if host else x_dev)[i % P], non_blocking=True)
+                check(lib.cachalot_bf16_gemv_f32(x.data_ptr(), B, w.data_ptr(), n, k, y.data_ptr(), stream.cuda_stream))
+                if host:
+                    y_host.copy_(y, non_blocking=True)
+                    stream.synchronize()
+            e1.record(stream)
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1)
+
+    timed(max(args.warmup, 3))
+    sampler = ClockSampler(0)
+    sampler.start()
+    all_ms = sorted(timed(args.steps) for _ in range(max(5, args.repeats)))
+    ms = all_ms[len(all_ms) // 2]
+    ms_e2e = sorted(timed(args.steps, True) for _ in range(5))[2]
+    clocks = sampler.stop()
+    # parity of what was timed: sampled rows against a float64 product
+    want = (w[::1009].double() @ x.double().T).T.float()
+    err = float((y[:, ::1009] - want).abs().max() / want.abs().max())
+    if not err < 1e-5:
+        print(f"head workload: output differs from the float64 product ({err:.3e})", file=sys.stderr, flush=True)
+        sys.exit(3)
+    alg = n * k * 2 + B * k * 4 + B * n * 4
+    peak, which = measured_peak()
+    gbs = alg * args.steps / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "bf16_head_gemv_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "ms_per_step_min": all_ms[0] / args.steps, "repeats": len(all_ms), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 x f32 -> f32", "data": "synthetic",
+        "config": {"workload": f"bf16-weight fp32 GEMV over the output head [{n},{k}], batch {B}", "batch": B,
+                   "l2": f"inputs larger than L2: a step streams {alg / 1e6:.0f} MB"},
+        "clocks": clocks,
+        "e2e": {"value": alg * args.steps / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": B * k * 4, "d2h_bytes_per_step": B * n * 4},
+        "gpu_launches": args.steps,
+        "roofline": {"kernel": "bf16_gemv_kernel", "bound": "hbm", "achieved": gbs, "peak": peak, "peak_kind": which, "unit": "GB/s",
+                     "frac": gbs / peak, "us_per_launch": ms / args.steps * 1e3, "algorithmic_bytes_per_launch": alg, "traffic": None},
+    }
+    if not args.no_cpu_baseline:
+        from oracle import bf16_gemv as obg
+        bits = w[:8192].cpu().view(torch.int16).numpy().view(np.uint16)
+        xs = x[:1].cpu().numpy()
+        obg.bf16_gemv_f32(xs, bits[:64])
+        t0 = time.perf_counter()
+        obg.bf16_gemv_f32(xs, bits)
+        secs = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": 8192 * k * 2 / secs / 1e9, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
+                                "sample": f"8192 of the {n} rows, one activation row, numpy (widen to float64, matmul), {secs:.2f} s"}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
     if args.watchdog > 0:
@@ -887,6 +966,8 @@ def main():
         faulthandler.dump_traceback_later(args.watchdog, exit=True)
     if args.workload == "fp8":
         run_fp8(args)
+    elif args.workload == "head":
+        run_head(args)
     elif args.impl == "reference":
         run_reference(args)
     elif args.workload == "prefill":

@@ -15,7 +15,7 @@ _OPS = (
     "quantize_fp8_activation", "quantize_mxfp4", "route_tail", "route_topk", "route_topk_fused", "route_topk_rows",
     "routed_expert_forward", "router_logits", "routed_expert_forward_batched", "routed_expert_forward_sgmm",
     "affine_expert_forward_batched", "SlabExperts", "shared_expert_forward", "shared_expert_forward_fused",
-    "shared_expert_forward_batched", "fp8_linear_rows", "fused_qr_kv_linear", "moe_layer_forward", "validate_routing", "self_check", "requantize_fp4_to_affine", "requantize_bank",
+    "shared_expert_forward_batched", "fp8_linear_rows", "bf16_gemv_f32", "fused_qr_kv_linear", "moe_layer_forward", "validate_routing", "self_check", "requantize_fp4_to_affine", "requantize_bank",
 )
 _LOADER = ("load_bank", "detect_expert_bank", "build_expert_index", "build_stacked_expert_index")
 __all__ = [*_BANK, *_OPS, *_LOADER, "NUMERICS_VERSION"]

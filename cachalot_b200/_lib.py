@@ -66,6 +66,7 @@ SIGNATURES = {
     "cachalot_moe_decode_static": (_i, [_vp, _desc, _vp, _vp, _vp, _i, _i, _f, _i, _vp, _i, _vp, _vp]),
     "cachalot_fp8_act_quant": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp]),
     "cachalot_fp8_gemv": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
+    "cachalot_bf16_gemv_f32": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp]),
     "cachalot_fp8_linear": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
     "cachalot_shared_expert_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "cachalot_shared_expert": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp, _vp, _sz, _vp, _vp]),

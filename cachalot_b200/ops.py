@@ -662,6 +662,28 @@ def shared_expert_forward_batched(x: torch.Tensor, *, w1, w1_scales, w2, w2_scal
     return _shared(x, w1, w1_scales, w3, w3_scales, w2, w2_scales, swiglu_limit, None)
 
 
+def bf16_gemv_f32(x: torch.Tensor, weight_bf16: torch.Tensor) -> torch.Tensor:
+    """bf16-weight, fp32-activation GEMV with fp32 accumulation (model/bf16_gemv_metal.py:50-63; the output head):
+    x [K] any float dtype (or [rows<=8, K]: the rows share one pass over the weights), weight_bf16 [N, K] bfloat16
+    -> float32 [N] (or [rows, N])."""
+    if weight_bf16.dtype != torch.bfloat16 or weight_bf16.dim() != 2:
+        raise ValueError("weight must be 2D bfloat16")
+    _need_cuda(x, weight_bf16)
+    n, k = weight_bf16.shape
+    if k % 64:
+        raise ValueError("in_features must be a multiple of 64")
+    x2 = x.reshape(-1, x.shape[-1]) if x.dim() > 1 else x.reshape(1, -1)
+    if x2.shape[1] != k:
+        raise ValueError(f"x has {x2.shape[1]} features, weight has {k}")
+    xf = x2.to(torch.float32).contiguous()
+    w = weight_bf16.contiguous()
+    out = torch.empty((xf.shape[0], n), dtype=torch.float32, device=x.device)
+    for r0 in range(0, xf.shape[0], 8):
+        r1 = min(r0 + 8, xf.shape[0])
+        check(lib.cachalot_bf16_gemv_f32(_ptr(xf[r0:r1]), r1 - r0, _ptr(w), n, k, _ptr(out[r0:r1]), _stream()))
+    return out[0] if x.dim() == 1 else out.reshape(*x.shape[:-1], n)
+
+
 def fp8_linear_rows(x: torch.Tensor, weight: torch.Tensor, weight_scales: torch.Tensor) -> torch.Tensor:
     """x [T,K] -> bf16 [T,N] (model/moe_prefill_batched.py:93-97): act_quant per row, then the GEMV's arithmetic."""
     return fp8_linear(x, weight, weight_scales)

@@ -217,6 +217,13 @@ CACHALOT_API int cachalot_fp8_gemv(const uint8_t* codes, const float* act_scales
                       int scale_rule, int block, int rows, int n, int k, void* out, int out_dtype,
                       cachalot_stream_t stream);
 
+/* Replaces model/bf16_gemv_metal.py:50-63 bf16_gemv_f32 (the output head, model/model_boundary_mlx.py:183, and any
+ * other bf16 trunk matrix): out[r,n] = sum_k f32(weight[n,k]) * x[r,k], fp32 accumulation.  x f32 [rows,K] (rows <=
+ * 8 share one pass over the weights), weight bf16 [N,K] row-major, K a multiple of 64 (the reference's condition),
+ * out f32 [rows,N].  x and weight 16-byte aligned. */
+CACHALOT_API int cachalot_bf16_gemv_f32(const float* x_f32, int rows, const void* weight_bf16, int n, int k, float* out,
+                           cachalot_stream_t stream);
+
 /* Replaces model/fp8_linear_metal.py:92-107 fp8_linear: the two calls above as one (act_quant, then the GEMV, which
  * starts to stream its weights while the quantiser still runs).  codes u8 [rows,K] and scales f32 [rows,K/block]
  * are the caller's buffers and hold the quantised activation afterwards (another projection of the same

@@ -147,3 +147,14 @@ def test_affine_expert_oracle_matches_dense_math_to_two_percent():
     batched = affine.affine_expert_forward(xm, mats, bits=bits, group_size=group, weight=np.array([0.7, 0.1, 1.0, 0.3]))
     single = affine.affine_expert_forward(xm[1], mats, bits=bits, group_size=group, weight=0.1)
     assert float(np.abs(batched[1] - single).max()) < 0.02 * max(1e-6, float(np.abs(single).max()))
+
+
+def test_bf16_gemv_oracle_widens_by_a_shift():
+    """bf16 -> fp32 is a shift (model/bf16_gemv_metal.py:33-35): known bit patterns, and the product against
+    hand-computed sums."""
+    from oracle import bf16_gemv
+    bits = np.array([[0x3F80, 0xBF80, 0x4000, 0x0000], [0x3F00, 0x3E80, 0xC040, 0x7F80]], dtype=np.uint16)
+    assert bf16_gemv.bf16_to_f32(bits).tolist() == [[1.0, -1.0, 2.0, 0.0], [0.5, 0.25, -3.0, float("inf")]]
+    x = np.array([1.0, 2.0, 3.0, 4.0], dtype=np.float32)
+    assert bf16_gemv.bf16_gemv_f32(x, bits[:1]).tolist() == [1.0 - 2.0 + 6.0]
+    assert bf16_gemv.bf16_gemv_f32(np.stack([x, 2 * x]), bits[:1]).tolist() == [[5.0], [10.0]]
