@@ -449,6 +449,10 @@ extern "C" size_t cachalot_moe_prefill_workspace_bytes(const cachalot_bank_desc*
                                                        int mxfp4_act) {
   if (!desc || tokens <= 0 || k <= 0) return 0;
   size_t rows = (size_t)tokens * k;
+  // the tensor-core path (what prefill_tc_supported() accepts, stated on the descriptor) needs its own scratch only
+  if (mxfp4_act == 1 && desc->format == CACHALOT_BANK_FP4 && desc->hidden % 128 == 0 && desc->inter % 64 == 0 &&
+      desc->record_bytes % 16 == 0)
+    return prefill_tc_workspace_bytes(desc->hidden, desc->inter, tokens, k, tokens * k);
   size_t b = align_up(rows * desc->inter * sizeof(float), 256);   // hidden
   b += align_up(rows * sizeof(int32_t), 256);                     // slot per routed row
   if (mxfp4_act) b += align_up((size_t)tokens * desc->hidden * 2, 256);  // MXFP4-rounded x as bf16
@@ -471,14 +475,16 @@ extern "C" int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc* 
   if (tokens < 0 || k <= 0 || n_experts <= 0) return fail(CACHALOT_EINVAL, "moe_prefill: bad shape");
   if (tokens == 0) return CACHALOT_OK;  // an empty chunk: nothing to read or write
   if (!x_bf16 || !perm || !offsets || !gate_w || !out) return fail(CACHALOT_EINVAL, "moe_prefill: null pointer");
-  if ((long long)tokens * k > 65535) return fail(CACHALOT_EINVAL, "moe_prefill: tokens*k=%lld exceeds 65535 (chunk the prompt)", (long long)tokens * k);
-  if (tokens == 0) return CACHALOT_OK;
+  const bool tc = mxfp4_act == 1 && prefill_tc_supported(v);
+  if ((long long)tokens * k > 0x7fffffffLL) return fail(CACHALOT_EINVAL, "moe_prefill: tokens*k=%lld is too large", (long long)tokens * k);
+  // the per-row kernels index routed rows in a grid dimension; the tensor-core path has no such limit
+  if (!tc && (long long)tokens * k > 65535) return fail(CACHALOT_EINVAL, "moe_prefill: tokens*k=%lld exceeds 65535 (chunk the prompt)", (long long)tokens * k);
   size_t need = cachalot_moe_prefill_workspace_bytes(desc, tokens, k, mxfp4_act);
   if (!workspace || workspace_bytes < need) return fail(CACHALOT_ESCRATCH, "moe_prefill: workspace %zu < %zu bytes", workspace_bytes, need);
   if (!aligned(workspace, 256)) return fail(CACHALOT_EALIGN, "moe_prefill: workspace must be 256-byte aligned");
   cudaStream_t s = (cudaStream_t)stream;
   const size_t rows = (size_t)tokens * k;
-  if (mxfp4_act == 1 && prefill_tc_supported(v))
+  if (tc)
     return launch_prefill_tc(v, x_bf16, perm, offsets, slot_of_expert, gate_w, tokens, k, n_experts, swiglu_limit, workspace, out,
                              status, s);
   uint8_t* ws = static_cast<uint8_t*>(workspace);

@@ -243,18 +243,16 @@ __device__ __forceinline__ void convert_block(uint8_t* act_row, float2* pexs_row
     *reinterpret_cast<uint4*>(dst + 64) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
     if ((b & (LPS - 1)) == 0) pexs_row[sub] = make_float2(__uint_as_float((uint32_t)(127 - e) << 23), sum);
   } else {
-    int hi[16], lo[16];
+    // X = rint(x * 2**e) = 256 * hi + lo with lo in [-128, 127].  With Y = X + 128, hi is byte 1 of Y and lo is byte 0
+    // of Y with its top bit flipped, so the bytes are picked straight out of Y by byte permutes.
+    int Y[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int X = __float2int_rn(v[i] * P);
-      hi[i] = (X + 128) >> 8;
-      lo[i] = X - hi[i] * 256;
-    }
+    for (int i = 0; i < 16; ++i) Y[i] = __float2int_rn(v[i] * P) + 128;
     uint32_t ph[4], pl[4];
 #pragma unroll
     for (int c = 0; c < 4; ++c) {  // word c = elements c, c+4, c+8, c+12
-      ph[c] = __byte_perm(__byte_perm(hi[c], hi[c + 4], 0x0040), __byte_perm(hi[c + 8], hi[c + 12], 0x0040), 0x5410);
-      pl[c] = __byte_perm(__byte_perm(lo[c], lo[c + 4], 0x0040), __byte_perm(lo[c + 8], lo[c + 12], 0x0040), 0x5410);
+      ph[c] = __byte_perm(__byte_perm(Y[c], Y[c + 4], 0x0051), __byte_perm(Y[c + 8], Y[c + 12], 0x0051), 0x5410);
+      pl[c] = __byte_perm(__byte_perm(Y[c], Y[c + 4], 0x0040), __byte_perm(Y[c + 8], Y[c + 12], 0x0040), 0x5410) ^ 0x80808080u;
     }
     // word c of block q goes to [c][sub-block][hi|lo][q]: a lane of the MMA loop reads its sub-block's 16 bytes of
     // every c with one load and finds the words of blocks 0..3 side by side (two MMA operand register pairs)
