@@ -421,6 +421,12 @@ def run_ours(args):
     run_token = make_runner(token_step)
 
     def barrier():
+        # Drain this rank's stream BEFORE the NCCL barrier: its kernel runs on NCCL's own stream and does not wait for
+        # work queued on `stream`.  A decode launch needs every SM (one CTA with all its shared memory per SM) and
+        # waits for its peers inside the kernel, so an NCCL kernel that slips in between two queued launches on one
+        # rank, while a peer's GPU is filled by a launch that waits for this rank, stalls both until the kernel's
+        # bounded wait runs out.
+        torch.cuda.synchronize(dev)
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
@@ -646,6 +652,12 @@ def run_prefill(args):
             result[0] = cb.moe_prefill_grouped(x, ids, w, bank, swiglu_limit=SWIGLU_LIMIT, mxfp4_act=1, status=status)
 
     def barrier():
+        # Drain this rank's stream BEFORE the NCCL barrier: its kernel runs on NCCL's own stream and does not wait for
+        # work queued on `stream`.  A decode launch needs every SM (one CTA with all its shared memory per SM) and
+        # waits for its peers inside the kernel, so an NCCL kernel that slips in between two queued launches on one
+        # rank, while a peer's GPU is filled by a launch that waits for this rank, stalls both until the kernel's
+        # bounded wait runs out.
+        torch.cuda.synchronize(dev)
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)

@@ -328,7 +328,9 @@ CACHALOT_API int cachalot_peer_sum(void* const* inbox_ptrs /* host */, void* con
  * count as zero and the call returns instead of hanging.  inbox[r] (device pointer as mapped in THIS process): rank
  * r's inbox of cachalot_peer_layer_inbox_bytes(world, hidden) bytes in memory every rank can write, 16-byte aligned,
  * zeroed once; epoch: u32 [2] in local device memory, zeroed once.  Only bank shapes and top-k the single-launch
- * kernel covers (else CACHALOT_EUNSUPPORTED: use cachalot_peer_sum). */
+ * kernel covers (else CACHALOT_EUNSUPPORTED: use cachalot_peer_sum).  The launch takes every SM and waits for its
+ * peers: do not let a kernel of another stream that itself waits for peers (an NCCL collective) run between two
+ * queued calls, or the two can block each other across ranks until the bounded wait expires. */
 typedef struct {
   void* inbox[8];
   uint32_t* epoch;
