@@ -53,6 +53,8 @@ def parse_args():
     p.add_argument("--workload", default="decode", choices=["decode", "prefill", "fp8", "head"],
                    help="prefill: one 4096-token chunk through one FP4 layer, Zipf(1.1) expert popularity (1 GPU); fp8: the FP8 trunk GEMV; head: the bf16 output head GEMV")
     p.add_argument("--tokens", type=int, default=4096, help="prefill chunk length")
+    p.add_argument("--act", default="mxfp4", choices=["mxfp4", "bf16"],
+                   help="prefill: activations quantised to MXFP4 per 32 (BASELINE config 3) or taken as bf16 with the reference's per-expert rounding points")
     p.add_argument("--experts", type=int, default=EXPERTS, help="prefill: experts in the layer (smaller = a case sized for profiling)")
     p.add_argument("--distinct-layers", type=int, default=8)
     p.add_argument("--no-cpu-baseline", action="store_true")
@@ -649,7 +651,7 @@ def run_prefill(args):
         if world > 1:
             result[0] = ep.ep_moe_prefill(x, ids, w, bank, n_experts=E, swiglu_limit=SWIGLU_LIMIT, status=status)
         else:
-            result[0] = cb.moe_prefill_grouped(x, ids, w, bank, swiglu_limit=SWIGLU_LIMIT, mxfp4_act=1, status=status)
+            result[0] = cb.moe_prefill_grouped(x, ids, w, bank, swiglu_limit=SWIGLU_LIMIT, mxfp4_act=1 if args.act == "mxfp4" else 0, status=status)
 
     def barrier():
         # Drain this rank's stream BEFORE the NCCL barrier: its kernel runs on NCCL's own stream and does not wait for
@@ -709,7 +711,8 @@ def run_prefill(args):
     peak, which = measured_peak()
     flops = 6.0 * rows * INTER * HIDDEN
     cfg = {"workload": f"prefill expert-major MoE layer: FP4 E2M1/E8M0 bank, {E} experts, {T} tokens, top-{K}, Zipf(1.1) expert "
-                       f"popularity, hidden {HIDDEN}, inter {INTER}, activations MXFP4 per 32",
+                       f"popularity, hidden {HIDDEN}, inter {INTER}, "
+                       + ("activations MXFP4 per 32" if args.act == "mxfp4" else "activations bf16 (as four residual MXFP4 terms), g, u, h, y rounded to bf16"),
            "l2": f"inputs larger than L2: {E * 18.8e6 / 1e9:.1f} GB of expert weights are streamed per step",
            "parallelism": f"ep{world}"}
     if world > 1:

@@ -89,7 +89,13 @@ int launch_combine_rows(const __nv_bfloat16* y, const int32_t* inv, int tokens, 
 bool prefill_tc_supported(const BankView& v);
 // decode batches through the same grouped kernels (FP4 bank, fp32 numerics), every distinct expert streamed once
 int launch_decode_tc(const BankView& v, const void* x_bf16, const int32_t* slots, const float* gate_w, int rows, int k, float limit,
-                     void* workspace, void* out, int out_dtype, int* status, cudaStream_t stream);
+                     void* workspace, void* out, int out_dtype, int* status, cudaStream_t stream, bool round_bf16 = false);
+// Expert-major prefill with bf16 activations as they are and the reference's per-expert rounding points, on the same
+// grouped kernels (prefill_tc.cu).
+size_t prefill_exact_workspace_bytes(int hidden, int inter, int tokens, int k, int n_experts);
+int launch_prefill_exact(const BankView& v, const void* x_bf16, const int32_t* perm, const int32_t* offsets, const int32_t* slot_of_expert,
+                         const float* gate_w, int tokens, int k, int n_experts, float limit, void* workspace, float* out, int* status,
+                         cudaStream_t stream);
 size_t decode_tc_workspace_bytes(int hidden, int inter, int rows, int k);
 bool decode_tc_supported(const BankView& v, int rows, int k);
 

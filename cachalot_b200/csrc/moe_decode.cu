@@ -318,9 +318,10 @@ extern "C" int cachalot_moe_decode(const void* bank, const cachalot_bank_desc* d
   const bool fused_ok = !(numerics & (CACHALOT_DECODE_SIMPLE | CACHALOT_DECODE_UNFUSED | CACHALOT_DECODE_ONLY_GATE_UP | CACHALOT_DECODE_ONLY_DOWN));
   if (fused_ok && decode_fused_supported(v, rows, k))
     return launch_decode_fused(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, numerics, workspace, out, out_dtype, status, (cudaStream_t)stream);
-  if (fused_ok && rows >= GROUPED_TC_MIN_ROWS && (numerics & 0xff) == CACHALOT_NUMERICS_F32 && v.format == CACHALOT_BANK_FP4 &&
-      decode_tc_supported(v, rows, k))
-    return launch_decode_tc(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, workspace, out, out_dtype, status, (cudaStream_t)stream);
+  if (fused_ok && rows >= GROUPED_TC_MIN_ROWS && v.format == CACHALOT_BANK_FP4 && decode_tc_supported(v, rows, k) &&
+      ((numerics & 0xff) == CACHALOT_NUMERICS_F32 || (numerics & 0xff) == CACHALOT_NUMERICS_BF16))
+    return launch_decode_tc(v, x_bf16, slots, gate_w, rows, k, swiglu_limit, workspace, out, out_dtype, status, (cudaStream_t)stream,
+                            (numerics & 0xff) == CACHALOT_NUMERICS_BF16);
   // Up to 64 tokens: one single-launch kernel per token, back to back.  Tokens share few experts at these sizes (384
   // routed rows touch about 244 of 384 experts), so grouping rows by expert saves less than the per-token kernel
   // gains by streaming its experts about twice as fast as the grouped kernels (measured: FP4 bank, 8 tokens 0.29 ms
@@ -450,9 +451,11 @@ extern "C" size_t cachalot_moe_prefill_workspace_bytes(const cachalot_bank_desc*
   if (!desc || tokens <= 0 || k <= 0) return 0;
   size_t rows = (size_t)tokens * k;
   // the tensor-core path (what prefill_tc_supported() accepts, stated on the descriptor) needs its own scratch only
-  if (mxfp4_act == 1 && desc->format == CACHALOT_BANK_FP4 && desc->hidden % 128 == 0 && desc->inter % 64 == 0 &&
-      desc->record_bytes % 16 == 0)
-    return prefill_tc_workspace_bytes(desc->hidden, desc->inter, tokens, k, tokens * k);
+  const bool tc_shape = desc->format == CACHALOT_BANK_FP4 && desc->hidden % 128 == 0 && desc->inter % 64 == 0 && desc->record_bytes % 16 == 0;
+  if (mxfp4_act == 1 && tc_shape) return prefill_tc_workspace_bytes(desc->hidden, desc->inter, tokens, k, tokens * k);
+  // bf16 activations on the same kernels (residual MXFP4 rows); the caller's expert count is not known here, and a
+  // segment list never has more entries than routed rows plus the 8192 experts the grouping accepts
+  if (mxfp4_act == 0 && tc_shape) return prefill_exact_workspace_bytes(desc->hidden, desc->inter, tokens, k, 8192);
   size_t b = align_up(rows * desc->inter * sizeof(float), 256);   // hidden
   b += align_up(rows * sizeof(int32_t), 256);                     // slot per routed row
   if (mxfp4_act) b += align_up((size_t)tokens * desc->hidden * 2, 256);  // MXFP4-rounded x as bf16
@@ -475,7 +478,8 @@ extern "C" int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc* 
   if (tokens < 0 || k <= 0 || n_experts <= 0) return fail(CACHALOT_EINVAL, "moe_prefill: bad shape");
   if (tokens == 0) return CACHALOT_OK;  // an empty chunk: nothing to read or write
   if (!x_bf16 || !perm || !offsets || !gate_w || !out) return fail(CACHALOT_EINVAL, "moe_prefill: null pointer");
-  const bool tc = mxfp4_act == 1 && prefill_tc_supported(v);
+  const bool tc = (mxfp4_act == 1 || mxfp4_act == 0) && prefill_tc_supported(v);
+  if (tc && mxfp4_act == 0 && n_experts > 8192) return fail(CACHALOT_EUNSUPPORTED, "moe_prefill: more than 8192 experts");
   if ((long long)tokens * k > 0x7fffffffLL) return fail(CACHALOT_EINVAL, "moe_prefill: tokens*k=%lld is too large", (long long)tokens * k);
   // the per-row kernels index routed rows in a grid dimension; the tensor-core path has no such limit
   if (!tc && (long long)tokens * k > 65535) return fail(CACHALOT_EINVAL, "moe_prefill: tokens*k=%lld exceeds 65535 (chunk the prompt)", (long long)tokens * k);
@@ -484,6 +488,8 @@ extern "C" int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc* 
   if (!aligned(workspace, 256)) return fail(CACHALOT_EALIGN, "moe_prefill: workspace must be 256-byte aligned");
   cudaStream_t s = (cudaStream_t)stream;
   const size_t rows = (size_t)tokens * k;
+  if (tc && mxfp4_act == 0)
+    return launch_prefill_exact(v, x_bf16, perm, offsets, slot_of_expert, gate_w, tokens, k, n_experts, swiglu_limit, workspace, out, status, s);
   if (tc)
     return launch_prefill_tc(v, x_bf16, perm, offsets, slot_of_expert, gate_w, tokens, k, n_experts, swiglu_limit, workspace, out,
                              status, s);

@@ -158,6 +158,7 @@ struct GemmArgs {
   // down epilogue
   __nv_bfloat16* y;           // bf16 [R, N]
   float* y32;                 // TERMS > 1: f32 [R / TERMS, N], one row per routed row
+  int round_bf16;             // TERMS > 1: the reference's prefill rounding points (g, u, h and y rounded to bf16)
   int* status;
 };
 
@@ -555,8 +556,10 @@ grouped_mxf4_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_con
               gs += __uint_as_float(g[r * TERMS + tt]);
               if (NA == 2) us += __uint_as_float(up[r * TERMS + tt]);
             }
+            if (A.round_bf16) gs = bf16_round(gs), us = bf16_round(us);
             if (NA == 2) {
               float res = swiglu(gs, us, A.limit) * __shfl_sync(0xffffffffu, wv, r);
+              if (A.round_bf16) res = bf16_round(res);
 #pragma unroll
               for (int tt = 0; tt < TERMS; ++tt) {
                 const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(res))));
@@ -909,7 +912,7 @@ struct DecodeScratch {
   Unit* units;
   size_t total;
 };
-DecodeScratch carve_decode(uint8_t* base, int hidden, int inter, size_t R) {
+DecodeScratch carve_decode(uint8_t* base, int hidden, int inter, size_t R, size_t n_seg = 0) {
   DecodeScratch s;
   size_t at = 0;
   auto take = [&](size_t bytes) {
@@ -918,13 +921,14 @@ DecodeScratch carve_decode(uint8_t* base, int hidden, int inter, size_t R) {
     return p;
   };
   const size_t Q = R * DTERMS;
-  s.seg_off = reinterpret_cast<int32_t*>(take((R + 1) * 4));
-  s.seg_slot = reinterpret_cast<int32_t*>(take(R * 4));
+  const size_t S = n_seg > R ? n_seg : R;  // segments: one per routed row at most (decode), or one per expert (prefill)
+  s.seg_off = reinterpret_cast<int32_t*>(take((S + 1) * 4));
+  s.seg_slot = reinterpret_cast<int32_t*>(take(S * 4));
   s.inv = reinterpret_cast<int32_t*>(take(R * 4));
   s.src_token = reinterpret_cast<int32_t*>(take(R * 4));
   s.row_w = reinterpret_cast<float*>(take(R * 4));
   s.n_units = reinterpret_cast<int32_t*>(take(256));
-  s.units = reinterpret_cast<Unit*>(take((Q / NTMAX + R + 1) * sizeof(Unit)));
+  s.units = reinterpret_cast<Unit*>(take((Q / NTMAX + (S < R ? S : R) + R + 1) * sizeof(Unit)));
   s.x_codes = take(Q * (hidden / 2));
   s.x_scales = take(Q * (hidden / 32) + 32);
   s.h_codes = take(Q * (inter / 2));
@@ -941,25 +945,14 @@ bool decode_tc_supported(const BankView& v, int rows, int k) {
 }
 size_t decode_tc_workspace_bytes(int hidden, int inter, int rows, int k) { return carve_decode(nullptr, hidden, inter, (size_t)rows * k).total; }
 
-// Routed experts of a decode batch with every distinct expert streamed once: rows grouped by bank slot, activations as
-// DTERMS residual MXFP4 rows, the two grouped block-scaled GEMMs, slot-ordered fp32 sum.  fp32 numerics (the FP4 decode op).
-int launch_decode_tc(const BankView& v, const void* x_bf16, const int32_t* slots, const float* gate_w, int rows, int k, float limit,
-                     void* workspace, void* out, int out_dtype, int* status, cudaStream_t stream) {
-  if (!decode_tc_supported(v, rows, k)) return CACHALOT_EUNSUPPORTED;
-  const int H = v.hidden, I = v.inter, R = rows * k;
-  const long long Q = (long long)R * DTERMS;
-  const DecodeScratch s = carve_decode(static_cast<uint8_t*>(workspace), H, I, (size_t)R);
-  const int threads = R < 1024 ? ((R + 31) / 32) * 32 : 1024;
-  decode_plan_kernel<<<1, threads, 2 * R * sizeof(int32_t), stream>>>(slots, gate_w, R, k, v.n_slots, s.seg_off, s.seg_slot, s.inv, s.src_token,
-                                                                    s.row_w, status);
-  {
-    const long long warps = (long long)R * (H / 32);
-    mxfp4_residual_quant_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x_bf16, s.src_token, R, H,
-                                                                                      s.x_codes, s.x_scales);
-  }
-  plan_units_kernel<<<1, 256, 256 * sizeof(int32_t), stream>>>(s.seg_off, s.seg_slot, R, v.n_slots, s.units, s.n_units);
+// The two grouped GEMMs over DTERMS residual MXFP4 rows per routed row (gate/up with SwiGLU, router weight and the
+// re-quantisation of h; down into s.y32).  seg_off is in MXFP4 rows; seg_slot may be null (segment e = slot e).
+static int run_terms4(const BankView& v, const DecodeScratch& s, const int32_t* seg_off, const int32_t* seg_slot, int n_seg, long long Q,
+                      float limit, bool round_bf16, int* status, cudaStream_t stream) {
+  const int H = v.hidden, I = v.inter;
+  plan_units_kernel<<<1, 256, 256 * sizeof(int32_t), stream>>>(seg_off, seg_slot, n_seg, v.n_slots, s.units, s.n_units);
   int rc;
-  if ((rc = check_launch("moe_decode (grouped) plan"))) return rc;
+  if ((rc = check_launch("moe (grouped, exact activations) plan"))) return rc;
   CUtensorMap m_w1, m_w3, m_w2, m_x, m_h;
   if ((rc = make_map(&m_w1, v.base + v.off[0], H / 2, H / 2, I, v.record_bytes, v.n_slots, BM))) return rc;
   if ((rc = make_map(&m_w3, v.base + v.off[4], H / 2, H / 2, I, v.record_bytes, v.n_slots, BM))) return rc;
@@ -987,6 +980,7 @@ int launch_decode_tc(const BankView& v, const void* x_bf16, const int32_t* slots
   a.h_scales = s.h_scales;
   a.y = nullptr;
   a.y32 = s.y32;
+  a.round_bf16 = round_bf16 ? 1 : 0;
   a.status = status;
   a.off_sc[0] = v.off[1];
   a.off_sc[1] = v.off[5];
@@ -997,7 +991,7 @@ int launch_decode_tc(const BankView& v, const void* x_bf16, const int32_t* slots
     launch(grouped_mxf4_kernel<2, STAGES_GU, KSUB, true, DTERMS>, 2, STAGES_GU, true, m_w1, m_w3, m_x, a);
   else
     launch(grouped_mxf4_kernel<2, STAGES_GU, KSUB, false, DTERMS>, 2, STAGES_GU, false, m_w1, m_w3, m_x, a);
-  if ((rc = check_launch("moe_decode (grouped) gate/up"))) return rc;
+  if ((rc = check_launch("moe (grouped, exact activations) gate/up"))) return rc;
   a.off_sc[0] = v.off[3];
   a.off_sc[1] = v.off[3];
   a.act_scales = s.h_scales;
@@ -1007,12 +1001,67 @@ int launch_decode_tc(const BankView& v, const void* x_bf16, const int32_t* slots
     launch(grouped_mxf4_kernel<1, STAGES_DN, KSUB, true, DTERMS>, 1, STAGES_DN, true, m_w2, m_w2, m_h, a);
   else
     launch(grouped_mxf4_kernel<1, STAGES_DN, KSUB, false, DTERMS>, 1, STAGES_DN, false, m_w2, m_w2, m_h, a);
-  if ((rc = check_launch("moe_decode (grouped) down"))) return rc;
+  return check_launch("moe (grouped, exact activations) down");
+}
+
+static void residual_quant(const void* x_bf16, const DecodeScratch& s, long long R, int H, cudaStream_t stream) {
+  const long long warps = R * (H / 32);
+  mxfp4_residual_quant_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x_bf16, s.src_token, (int)R, H,
+                                                                                    s.x_codes, s.x_scales);
+}
+
+// Routed experts of a decode batch with every distinct expert streamed once: rows grouped by bank slot, activations as
+// DTERMS residual MXFP4 rows, the two grouped block-scaled GEMMs, slot-ordered fp32 sum.  round_bf16 = false: fp32
+// numerics (the FP4 decode op); true: the reference's per-expert prefill rounding points.
+int launch_decode_tc(const BankView& v, const void* x_bf16, const int32_t* slots, const float* gate_w, int rows, int k, float limit,
+                     void* workspace, void* out, int out_dtype, int* status, cudaStream_t stream, bool round_bf16) {
+  if (!decode_tc_supported(v, rows, k)) return CACHALOT_EUNSUPPORTED;
+  const int H = v.hidden, R = rows * k;
+  const DecodeScratch s = carve_decode(static_cast<uint8_t*>(workspace), H, v.inter, (size_t)R);
+  const int threads = R < 1024 ? ((R + 31) / 32) * 32 : 1024;
+  decode_plan_kernel<<<1, threads, 2 * R * sizeof(int32_t), stream>>>(slots, gate_w, R, k, v.n_slots, s.seg_off, s.seg_slot, s.inv, s.src_token,
+                                                                    s.row_w, status);
+  residual_quant(x_bf16, s, R, H, stream);
+  int rc = run_terms4(v, s, s.seg_off, s.seg_slot, R, (long long)R * DTERMS, limit, round_bf16, status, stream);
+  if (rc) return rc;
   if (out_dtype == CACHALOT_BF16)
     decode_combine_kernel<<<rows, 256, 0, stream>>>(s.y32, s.inv, k, H, static_cast<__nv_bfloat16*>(out));
   else
     decode_combine_kernel<<<rows, 256, 0, stream>>>(s.y32, s.inv, k, H, static_cast<float*>(out));
   return check_launch("moe_decode (grouped) combine");
+}
+
+__global__ void scale_offsets_kernel(const int32_t* __restrict__ in, int n, int mul, int32_t* __restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = in[i] * mul;
+}
+
+// Expert-major prefill with bf16 activations taken as they are (the reference's per-expert prefill numerics,
+// model/moe_prefill_batched.py:31-61): the grouping's permutation and offsets as in launch_prefill_tc, activations
+// as DTERMS residual MXFP4 rows (their sum reproduces the bf16 value to 2.4e-4), g, u, h and y rounded to bf16.
+size_t prefill_exact_workspace_bytes(int hidden, int inter, int tokens, int k, int n_experts) {
+  return carve_decode(nullptr, hidden, inter, (size_t)tokens * k, (size_t)n_experts).total;
+}
+int launch_prefill_exact(const BankView& v, const void* x_bf16, const int32_t* perm, const int32_t* offsets, const int32_t* slot_of_expert,
+                         const float* gate_w, int tokens, int k, int n_experts, float limit, void* workspace, float* out, int* status,
+                         cudaStream_t stream) {
+  if (!prefill_tc_supported(v)) return CACHALOT_EUNSUPPORTED;
+  const int H = v.hidden;
+  const size_t R = (size_t)tokens * k;
+  if (R * DTERMS > 0x7fffffffULL) return CACHALOT_EUNSUPPORTED;
+  const DecodeScratch s = carve_decode(static_cast<uint8_t*>(workspace), H, v.inter, R, (size_t)n_experts);
+  cudaError_t e = cudaMemsetAsync(s.inv, 0xFF, R * 4, stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(s.src_token, 0, R * 4, stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(s.row_w, 0, R * 4, stream);
+  if (e != cudaSuccess) return fail(CACHALOT_ECUDA, "moe_prefill: %s", cudaGetErrorString(e));
+  plan_rows_kernel<<<n_experts, 128, 0, stream>>>(perm, offsets, slot_of_expert, v.n_slots, k, gate_w, s.inv, s.src_token, s.row_w, status);
+  scale_offsets_kernel<<<(n_experts + 256) / 256, 256, 0, stream>>>(offsets, n_experts + 1, DTERMS, s.seg_off);
+  int rc;
+  if ((rc = check_launch("moe_prefill plan rows"))) return rc;
+  residual_quant(x_bf16, s, (long long)R, H, stream);
+  if ((rc = run_terms4(v, s, s.seg_off, slot_of_expert, n_experts, (long long)R * DTERMS, limit, true, status, stream))) return rc;
+  decode_combine_kernel<<<tokens, 256, 0, stream>>>(s.y32, s.inv, k, H, out);
+  return check_launch("moe_prefill combine");
 }
 
 bool prefill_tc_supported(const BankView& v) {

@@ -277,7 +277,11 @@ CACHALOT_API size_t cachalot_moe_prefill_workspace_bytes(const cachalot_bank_des
  * gate_w f32 [tokens,k]; mxfp4_act != 0 quantises x and the hidden activation to MXFP4 per 32
  * first: 1 = on the block-scaled FP4 tensor cores when the bank is FP4 (grouped GEMM, weights as
  * the M side), 2 = always on the plain per-row kernels (the same arithmetic in a fixed summation
- * order, kept as the check for 1).  out f32 [tokens,H]. */
+ * order, kept as the check for 1).  mxfp4_act = 0 keeps the bf16 activations and the reference's per-expert
+ * rounding points (g, u, h and each expert's output rounded to bf16); on an FP4 bank this also runs on the tensor
+ * cores, every activation row as four residual MXFP4 rows whose sum reproduces the bf16 values to 2.4e-4 (a result
+ * that sat on a bf16 rounding boundary may come out one step away from the per-row kernels').  out f32 [tokens,H].
+ * tokens * k <= 65535 only where the per-row kernels run (2-bit banks, mxfp4_act = 2). */
 CACHALOT_API int cachalot_moe_prefill(const void* bank, const cachalot_bank_desc* desc /* host */, const void* x_bf16,
                          const int32_t* perm, const int32_t* offsets, const int32_t* slot_of_expert,
                          const float* gate_w, int tokens, int k, int n_experts, float swiglu_limit, int mxfp4_act,

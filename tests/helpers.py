@@ -9,6 +9,16 @@ def max_rel(got: np.ndarray, want: np.ndarray) -> float:
     return float(np.max(np.abs(np.asarray(got, np.float64) - np.asarray(want, np.float64))) / max(np.max(np.abs(want)), 1e-30))
 
 
+def within_bf16_flips(got: np.ndarray, want: np.ndarray, tol: float = 2e-3, share: float = 1 / 32) -> bool:
+    """The criterion for outputs that pass through bf16 rounding points when the inputs of those roundings carry a
+    small error (the tensor-core path takes a bf16 activation as four MXFP4 terms, good to 2.4e-4): a value that sat
+    on a rounding boundary moves one bf16 step.  Every element within `tol` of the largest output, except a counted
+    share that may be off by one bf16 step of the largest output (2**-7)."""
+    scale = float(np.max(np.abs(want)))
+    err = np.abs(np.asarray(got, dtype=np.float64) - np.asarray(want, dtype=np.float64)) / scale
+    return bool(err.max() < 2.0 ** -7 and np.count_nonzero(err >= tol) <= max(2, int(err.size * share)))
+
+
 def bf16_tensor(x_f32: np.ndarray, device="cuda"):
     import torch
 
