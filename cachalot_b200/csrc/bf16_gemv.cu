@@ -124,7 +124,7 @@ extern "C" int cachalot_bf16_gemv_f32(const float* x_f32, int rows, const void* 
   const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(weight_bf16);
   cudaError_t e = cudaSuccess;
   auto go = [&](auto kern) {
-    if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (smem > 48 * 1024) e = smem_optin_once(kern, 200 * 1024);
     if (e == cudaSuccess) kern<<<grid, BG_THREADS, smem, s>>>(x_f32, w, n, k, out);
   };
   switch (rows) {

@@ -9,6 +9,9 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
+#include <set>
+#include <utility>
 
 #include "../../include/cachalot_b200.h"
 
@@ -141,6 +144,23 @@ __device__ __forceinline__ void router_score_key(int mode, float raw, float b, f
 __device__ __forceinline__ bool router_before(int mode, float ka, int ia, float kb, int ib) {
   if (mode == CACHALOT_ROUTER_SQRT_SOFTPLUS) return ka > kb || (ka == kb && ia > ib);
   return ka < kb || (ka == kb && ia < ib);
+}
+
+// The dynamic shared-memory opt-in is an attribute of a kernel on a device: set it the first time a kernel is launched
+// on a device, not on every launch (the pointer types of different instantiations coincide, so the record is keyed
+// by the pointer's value).  `bytes` must be the same for every call with one kernel.
+template <typename K>
+inline cudaError_t smem_optin_once(K kern, int bytes) {
+  static std::mutex mu;
+  static std::set<std::pair<const void*, int>> done;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count({(const void*)kern, dev})) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done.insert({(const void*)kern, dev});
+  return e;
 }
 
 }  // namespace cachalot

@@ -781,7 +781,7 @@ static int launch_fmt(const BankView& v, const void* x, const int32_t* slots, co
   do {                                                                                                                \
     auto kern = stream_kernel<FMT, KCHV, PH, HL, OC, OT>;                                                             \
     const StSmem L = st_layout(FMT, KK, KCHV, cols, HL);                                                              \
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);                              \
+    smem_optin_once(kern, 200 * 1024);                                                                                \
     kern<<<grid_for((long long)R * ((PH) == 0 ? I / 8 : H / 16)), ST_WARPS * 32, L.total, stream>>>(                  \
         v, (const __nv_bfloat16*)x, slots, gate_w, plan, R, k, cols, limit, numerics, hidden, ybuf, counters,          \
         (OT*)out, status, 0x64006400u);                                                                                          \

@@ -965,7 +965,7 @@ static int run_terms4(const BankView& v, const DecodeScratch& s, const int32_t* 
   auto launch = [&](auto kern, int na, int nstage, bool raw, const CUtensorMap& ma0, const CUtensorMap& ma1, const CUtensorMap& mb,
                     const GemmArgs& ga) {
     const size_t sm = smem_bytes(na, nstage, ga.k_codes / 32, raw);
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    smem_optin_once(kern, (int)SMEM_LIMIT);
     kern<<<sms, NTHREADS, sm, stream>>>(ma0, ma1, mb, ga);
   };
   GemmArgs a = {};
@@ -1102,7 +1102,7 @@ int launch_prefill_rows(const BankView& v, const uint8_t* x_codes, const uint8_t
   auto launch = [&](auto kern, int na, int nstage, bool raw, const CUtensorMap& ma0, const CUtensorMap& ma1, const CUtensorMap& mb,
                     const GemmArgs& ga) {
     const size_t sm = smem_bytes(na, nstage, ga.k_codes / 32, raw);
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    smem_optin_once(kern, (int)SMEM_LIMIT);
     kern<<<sms, NTHREADS, sm, stream>>>(ma0, ma1, mb, ga);
   };
   GemmArgs a;
