@@ -62,10 +62,6 @@ constexpr int kUnroll = CB_UNROLL;  // steps of the reduction loop unrolled toge
 constexpr int NPROD = 4;                          // producer warps (one issuing lane each; a lane's copies do not overlap)
 constexpr int KMAX = 8;                           // routed experts per token
 constexpr int MAX_TILES = 8;                      // phase-1 output tiles one CTA may own
-#ifndef CB_W2_HOLD
-#define CB_W2_HOLD 4
-#endif
-constexpr int W2_HOLD = CB_W2_HOLD;               // down-projection units copied ahead before the first hidden rows have been asked for
 constexpr int KP1 = 2;                            // parts the reduction dimension of a phase-1 unit is cut into (one warp each)
 constexpr uint32_t WAIT_LIMIT = 1u << 20;         // polls before a wait gives up and flags an error
 constexpr uint32_t HIDDEN_TRIES = 1u << 16;       // reads of a hidden block before a CTA gives up on the others (about 10 ms)
@@ -471,7 +467,6 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
   uint64_t* full0 = bars, *empty0 = bars + 16, *full1 = bars + 32, *empty1 = bars + 48;
   const uint8_t* zeros = smem + G.off_bar + 512;  // 512 zero bytes
   float2* xch = reinterpret_cast<float2*>(smem + G.off_bar + 1024);  // [NPAIR][2][8] partial sums between the warps of a pair
-  uint64_t* hold = reinterpret_cast<uint64_t*>(smem + G.off_bar + 1536);  // the consumers have issued their first reads of hidden rows
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int H = bank.hidden, I = bank.inter;
   int err = 0;
@@ -486,7 +481,6 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
       mbar_init(&full0[s], NPROD), mbar_init(&empty0[s], 2);
       mbar_init(&full1[s], NPROD), mbar_init(&empty1[s], KP1);
     }
-    mbar_init(hold, Fm<FMT>::NCW);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -680,10 +674,6 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
         int end_byte = 0;  // end of the current phase-1 stage inside the ring
         int s_end = 0, s_end_byte = 0;  // first phase-0 stage that starts at or behind end_byte, and its start
         for (int q = 0; q < n1 && !err; ++q) {
-          // The reads of the hidden rows wait in line behind the copies that are in flight when they are issued, and
-          // nothing can start before they are back: only W2_HOLD units are asked for before the consumers have
-          // issued those reads.  The rest of W2 streams while phase 1 runs.
-          if (q == W2_HOLD && !mbar_wait(hold, 0u)) err = 1;
           if (round > 0) {
             if (!mbar_wait(&empty1[idx], (round - 1u) & 1u)) err = 1;
           } else {
@@ -822,10 +812,6 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
 #pragma unroll
                 for (int i = 0; i < 4; ++i) q[h][i] = ld_relaxed_v4(src + 128 * i);
               }
-            }
-            if (gsel == 0 && base == 0 && tries == 0) {  // once per launch and warp
-              __syncwarp();
-              if (lane == 0) mbar_arrive(hold);
             }
             bool any = false;
 #pragma unroll
