@@ -19,7 +19,7 @@
 // The kernel is a stream of weight bytes: HBM -> cp.async.bulk (four copies of four weight rows per
 // unit, one per copy warp) -> a ring of shared-memory stages -> registers -> mma.sync.  Warps 0..3
 // issue the copies (one lane each) and run ahead of the consumers by the depth of the ring; they keep
-// issuing the down projection's rows while the CTA waits at the grid barrier, so HBM stays busy across it.
+// issuing the down projection's rows while the consumers collect and convert the hidden rows, so HBM stays busy.
 // Warps 4..11 are the MMA warps.  In phase 0 they work as four pairs: a pair takes one unit, each warp of the
 // pair does half of the reduction dimension and the two partial sums meet in shared memory (gate and up must be
 // complete before SwiGLU).  In phase 1 every warp works alone on its half of a unit's reduction dimension and
@@ -1079,13 +1079,13 @@ static int launch_fused_fmt(const BankView& v, const Geo& G, const RouteArgs& R,
   cfg.gridDim = dim3((unsigned)sms);
   cfg.blockDim = dim3(Fm<FMT>::NTHREADS);
   // Always the whole shared memory of an SM, also for small banks: one CTA per SM, so a second launch (from
-  // another stream) cannot become resident, and cannot touch the grid barrier word, before this launch's CTAs
+  // another stream) cannot become resident, and cannot touch the hidden rows or the launch counter, before this launch's CTAs
   // have passed their barrier and left.
   cfg.dynamicSmemBytes = (size_t)(SMEM_LIMIT - 256);
   (void)G.total;
   cfg.stream = stream;
   cudaLaunchAttribute at[2];
-  at[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident: the grid barrier cannot starve
+  at[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident: they read each other's hidden values
   at[0].val.cooperative = 1;
   at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // the prologue may overlap the previous kernel's tail
   at[1].val.programmaticStreamSerializationAllowed = 1;

@@ -419,7 +419,7 @@ def test_self_check_passes_and_a_nan_weight_sets_its_status_bit():
 
 def test_two_streams_decode_small_banks_concurrently():
     """Small banks leave most of an SM's shared memory unused, yet the single-launch kernel always takes a whole SM per
-    CTA: launches from two streams cannot be at the grid barrier together, and both streams get the right answers."""
+    CTA: launches from two streams cannot overlap on the shared hidden rows, and both streams get the right answers."""
     import cachalot_b200 as cb
     hidden, inter, n_slots, k = 512, 384, 12, 6
     bank = cb.SlabBank(cb.affine_format(hidden, inter), hidden, inter, n_slots)
