@@ -1079,8 +1079,8 @@ static int launch_fused_fmt(const BankView& v, const Geo& G, const RouteArgs& R,
   cfg.gridDim = dim3((unsigned)sms);
   cfg.blockDim = dim3(Fm<FMT>::NTHREADS);
   // Always the whole shared memory of an SM, also for small banks: one CTA per SM, so a second launch (from
-  // another stream) cannot become resident, and cannot touch the hidden rows or the launch counter, before this launch's CTAs
-  // have passed their barrier and left.
+  // another stream) cannot become resident, and cannot touch the hidden rows or the launch counter, before this
+  // launch's CTAs have left.
   cfg.dynamicSmemBytes = (size_t)(SMEM_LIMIT - 256);
   (void)G.total;
   cfg.stream = stream;
