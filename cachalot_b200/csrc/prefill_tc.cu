@@ -861,30 +861,44 @@ __global__ void decode_plan_kernel(const int32_t* __restrict__ slots, const floa
   }
 }
 
-// One warp per (routed row, block of 32): the block as DTERMS MXFP4 blocks, each the quantisation (reference rule:
-// model/fp4_act_mlx.py:101-250) of what the ones before it left over.  x bf16 [tokens, K]; row p reads token src[p].
+// One thread per 8 consecutive elements (one 16-byte load), four threads per 32-block: the block as DTERMS MXFP4
+// blocks, each the quantisation (reference rule: model/fp4_act_mlx.py:101-250) of what the ones before it left over.
+// x bf16 [tokens, K]; row p reads token src[p].
 __global__ void mxfp4_residual_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ src, int rows, int k,
                                             uint8_t* __restrict__ codes, uint8_t* __restrict__ scales) {
-  const int nblk = k / 32;
-  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (warp >= (long long)rows * nblk) return;
-  const long long p = warp / nblk;
-  const int b = (int)(warp - p * nblk);
-  float res = __bfloat162float(x[(size_t)src[p] * k + b * 32 + lane]);
+  const int per_row = k / 8;
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const bool live = i < (long long)rows * per_row;
+  const long long p = live ? i / per_row : 0;
+  const int c = live ? (int)(i - p * per_row) : 0;
+  uint4 raw = make_uint4(0, 0, 0, 0);
+  if (live) raw = *reinterpret_cast<const uint4*>(x + (size_t)src[p] * k + c * 8);
+  const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+  float res[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) res[2 * j] = __uint_as_float(wds[j] << 16), res[2 * j + 1] = __uint_as_float(wds[j] & 0xffff0000u);
 #pragma unroll
   for (int tt = 0; tt < DTERMS; ++tt) {
-    const float amax = warp_max(fabsf(res));
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(res[j]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     const int e = mxfp4_exponent(amax);
-    const float qv = res * pow2f(-e);
-    const float qn = __shfl_down_sync(0xffffffffu, qv, 1);
-    const uint32_t byte = e2m1x2_byte(qv, qn);
-    const uint32_t pair = __shfl_sync(0xffffffffu, byte, lane & ~1);
-    const uint32_t code = (lane & 1) ? pair >> 4 : pair & 15u;
-    res -= e2m1_to_f32(code) * pow2f(e);
-    const size_t row = (size_t)p * DTERMS + tt;
-    if ((lane & 1) == 0) codes[row * (size_t)(k / 2) + b * 16 + (lane >> 1)] = (uint8_t)byte;
-    if (lane == 0) scales[row * (size_t)nblk + b] = (uint8_t)(e + 127);
+    const float inv = pow2f(-e), sc = pow2f(e);
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t byte = e2m1x2_byte(res[2 * j] * inv, res[2 * j + 1] * inv);
+      packed |= byte << (8 * j);
+      res[2 * j] -= e2m1_to_f32(byte & 15u) * sc;
+      res[2 * j + 1] -= e2m1_to_f32(byte >> 4) * sc;
+    }
+    if (live) {
+      const size_t row = (size_t)p * DTERMS + tt;
+      *reinterpret_cast<uint32_t*>(codes + row * (size_t)(k / 2) + c * 4) = packed;
+      if ((c & 3) == 0) scales[row * (size_t)(k / 32) + (c >> 2)] = (uint8_t)(e + 127);
+    }
   }
 }
 
@@ -1005,8 +1019,8 @@ static int run_terms4(const BankView& v, const DecodeScratch& s, const int32_t* 
 }
 
 static void residual_quant(const void* x_bf16, const DecodeScratch& s, long long R, int H, cudaStream_t stream) {
-  const long long warps = R * (H / 32);
-  mxfp4_residual_quant_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x_bf16, s.src_token, (int)R, H,
+  const long long threads = R * (H / 8);
+  mxfp4_residual_quant_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x_bf16, s.src_token, (int)R, H,
                                                                                     s.x_codes, s.x_scales);
 }
 
