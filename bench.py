@@ -973,13 +973,43 @@ def run_head(args):
     print(json.dumps(line), flush=True)
 
 
+def run_reference_gemv(args):
+    """CPU arm of the two GEMV workloads: the numpy oracle on the host cores, a bounded sample."""
+    import numpy as np
+
+    if args.workload == "fp8":
+        gbs, desc = time_cpu_fp8(max(1, args.batch))
+        metric, cfg = "fp8_trunk_gemv_gbs", "FP8 E4M3 trunk GEMV with act_quant: [12288,4096] and [4096,8192], fp32 scales per 128x128"
+    else:
+        from oracle import bf16_gemv as obg
+        n, k = HEAD_SHAPE
+        rng = np.random.default_rng(0)
+        bits = (rng.standard_normal((8192, k)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+        xs = rng.standard_normal((1, k)).astype(np.float32)
+        obg.bf16_gemv_f32(xs, bits[:64])
+        t0 = time.perf_counter()
+        obg.bf16_gemv_f32(xs, bits)
+        secs = time.perf_counter() - t0
+        gbs, desc = 8192 * k * 2 / secs / 1e9, f"8192 of the {n} rows, one activation row, numpy (widen to float64, matmul), {secs:.2f} s"
+        metric, cfg = "bf16_head_gemv_gbs", f"bf16-weight fp32 GEMV over the output head [{n},{k}]"
+    line = {"impl": "reference", "metric": metric, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": 1, "warmup": 0,
+            "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": cfg, "batch": max(1, args.batch)},
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port", "sample": desc},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
     if args.watchdog > 0:
         import faulthandler
 
         faulthandler.dump_traceback_later(args.watchdog, exit=True)
-    if args.workload == "fp8":
+    if args.impl == "reference" and args.workload in ("fp8", "head"):
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_reference_gemv(args)
+    elif args.workload == "fp8":
         run_fp8(args)
     elif args.workload == "head":
         run_head(args)
