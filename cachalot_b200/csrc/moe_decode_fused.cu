@@ -14,16 +14,20 @@
 // The experts are taken in two groups (about two thirds of the present experts, then the rest).  Every CTA owns
 // a slice of the inter rows of EVERY expert and walks them expert by expert, so group A's hidden rows are long
 // written by every CTA when a CTA, through with all its phase-0 units, converts them into operand form and runs
-// A's part of phase 1; group B's follow, by then written too: the skew between the CTAs hides under work.
+// A's part of phase 1; group B's rows are converted by the copy warps meanwhile: the skew between the CTAs and the
+// second conversion hide under work.
 //
-// The kernel is a stream of weight bytes: HBM -> cp.async.bulk (four copies of four weight rows per
-// unit, one per copy warp) -> a ring of shared-memory stages -> registers -> mma.sync.  Warps 0..3
-// issue the copies (one lane each) and run ahead of the consumers by the depth of the ring; they keep
-// issuing the down projection's rows while the consumers collect and convert the hidden rows, so HBM stays busy.
+// The kernel is a stream of weight bytes: HBM -> cp.async.bulk -> a ring of shared-memory stages -> registers ->
+// mma.sync.  Warps 0..3 issue the copies (one lane each) and run ahead of the consumers by the depth of the ring.
+// In phase 0 every copy warp brings four rows (and one scale array) of every unit; in phase 1, where a unit's 16
+// rows are contiguous in the bank, two of the copy warps bring whole units, turn about: the down projection's rows
+// are all on their way shortly after phase 0 ends.  The copy warps then help with the hidden rows.
 // Warps 4..11 are the MMA warps.  In phase 0 they work as four pairs: a pair takes one unit, each warp of the
 // pair does half of the reduction dimension and the two partial sums meet in shared memory (gate and up must be
 // complete before SwiGLU).  In phase 1 every warp works alone on its half of a unit's reduction dimension and
 // leaves its partial sums in shared memory; the closing sum adds halves and experts in a fixed order.
+// Code that only a few warps run on their own is slow here (the kernel is larger than the instruction cache, and a
+// lone warp pays every miss itself): work that several roles share goes through one non-inlined function.
 //
 //   unit, phase 0 : 8 rows of W1 (MMA rows 0..7) + the same 8 rows of W3 (MMA rows 8..15) of one expert
 //   unit, phase 1 : 16 rows of W2 of one expert; a CTA owns whole 16-row output tiles and walks
@@ -62,6 +66,7 @@ constexpr int kUnroll = CB_UNROLL;  // steps of the reduction loop unrolled toge
 constexpr int NPROD = 4;                          // producer warps (one issuing lane each; a lane's copies do not overlap)
 constexpr int KMAX = 8;                           // routed experts per token
 constexpr int MAX_TILES = 8;                      // phase-1 output tiles one CTA may own
+constexpr int NISSUE1 = 2;                        // copy warps that issue phase 1's copies (the others start on the hidden rows)
 constexpr int KP1 = 2;                            // parts the reduction dimension of a phase-1 unit is cut into (one warp each)
 constexpr uint32_t WAIT_LIMIT = 1u << 20;         // polls before a wait gives up and flags an error
 constexpr uint32_t HIDDEN_TRIES = 1u << 16;       // reads of a hidden block before a CTA gives up on the others (about 10 ms)
@@ -122,6 +127,8 @@ struct Geo {
   int tiles1;         // hidden / 16
   int stage_bytes[2], nst[2];  // ring geometry per phase (the same memory, cut into stages of the phase's unit size)
   int off_ring, off_act, off_pe, off_part, off_bar, total;
+  int x_off;          // x's operand row inside the operand area: at its end, clear of the first hidden rows
+  int xpe_off;        // the same for x's per-sub-block entries (in entries)
   int max_tiles;      // phase-1 output tiles a CTA owns at most (sizes the partial-sum area)
 };
 
@@ -144,11 +151,37 @@ __device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// One look at the barrier that never suspends the thread (try_wait may hold it for a while before it says no).
+__device__ __forceinline__ bool mbar_test(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(smem_u32(b)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: false after WAIT_LIMIT polls (the caller flags the error and carries on).
 __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity) {
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
     if (mbar_try(b, parity)) return true;
   return false;
+}
+// A long wait of a whole warp: one lane looks, with pauses, so that the waiting warps leave the shared-memory pipe to
+// the warps that are being waited for; the other lanes learn of it at the warp barrier.
+__device__ __forceinline__ bool mbar_wait_quiet(uint64_t* b, uint32_t parity, int lane) {
+  int ok = 1;
+  if (lane == 0) {
+    ok = 0;
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+      if (mbar_test(b, parity)) {
+        ok = 1;
+        break;
+      }
+      __nanosleep(40);
+    }
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
@@ -262,6 +295,64 @@ __device__ __forceinline__ void convert_block(uint8_t* act_row, float2* pexs_row
     // the class sum of the IMMA accumulators carries a factor 64
     if (q == 0) pexs_row[sub] = make_float2(__uint_as_float((uint32_t)(127 - e - 6) << 23), sum);
   }
+}
+
+// Makes operand rows of phase 1 from the other CTAs' hidden values.  A chunk is 32 consecutive 16-value blocks of one
+// row, one block per lane (the conversion shuffles between the lanes that share a sub-block).  Warps take chunks off
+// a shared counter, fetch the next chunk's words while they convert the current one's, read a chunk again until every
+// word carries this launch's tag (bounded), and arrive once per finished chunk on `ready` (count = chunks of the
+// group).  One copy of the code for every warp that calls it: code that few warps run on their own is fetched slowly.
+// Returns true if some CTA did not deliver in time (the chunk is converted from what was there).
+template <int FMT>
+__device__ __noinline__ bool convert_chunks(int* next, uint64_t* ready, int nchunk, int nblk, int roww, const int* route,
+                                            uint8_t* act_rows, float2* pexs_rows, int row_stride, int nsub, unsigned tag8, int lane) {
+  const int per_row = roww >> 9;  // chunks of a row (padded: the last one may hold blocks past the row's end)
+  bool late = false;
+  auto grab = [&]() {
+    int c = 0;
+    if (lane == 0) c = atomicAdd(next, 1);
+    return __shfl_sync(0xffffffffu, c, 0);
+  };
+  auto fetch = [&](int c, uint4 (&q)[4]) {
+    const int r = c / per_row, ch = c - r * per_row;
+    const uint32_t* src = fused_hidden + (size_t)route[r] * roww + (ch << 9) + (lane << 2);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = ld_relaxed_v4(src + 128 * i);
+  };
+  uint4 qc[4], qn[4];
+  int c = grab();
+  if (c < nchunk) fetch(c, qc);
+  while (c < nchunk) {
+    const int cn = grab();
+    if (cn < nchunk) fetch(cn, qn);
+    const int r = c / per_row, bk = (c - r * per_row) * 32 + lane;
+    const bool ok = bk < nblk;
+    for (uint32_t tries = 0;; ++tries) {
+      uint32_t diff = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) diff |= ((qc[i].x ^ tag8) | (qc[i].y ^ tag8) | (qc[i].z ^ tag8) | (qc[i].w ^ tag8)) & 0xffu;
+      if (!__any_sync(0xffffffffu, ok && diff != 0)) break;
+      if (tries >= HIDDEN_TRIES) {
+        late = true;
+        break;
+      }
+      if (tries > 4) __nanosleep(100);
+      fetch(c, qc);
+    }
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[4 * i] = __uint_as_float(qc[i].x & 0xffffff00u), v[4 * i + 1] = __uint_as_float(qc[i].y & 0xffffff00u);
+      v[4 * i + 2] = __uint_as_float(qc[i].z & 0xffffff00u), v[4 * i + 3] = __uint_as_float(qc[i].w & 0xffffff00u);
+    }
+    convert_block<FMT>(act_rows + (size_t)r * row_stride, pexs_rows + r * nsub, ok ? bk : 0, ok, v);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(ready);
+    c = cn;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) qc[i] = qn[i];
+  }
+  return late;
 }
 
 // d = a * b (no accumulator input: the first MMA of a chain)
@@ -467,6 +558,11 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
   uint64_t* full0 = bars, *empty0 = bars + 16, *full1 = bars + 32, *empty1 = bars + 48;
   const uint8_t* zeros = smem + G.off_bar + 512;  // 512 zero bytes
   float2* xch = reinterpret_cast<float2*>(smem + G.off_bar + 1024);  // [NPAIR][2][8] partial sums between the warps of a pair
+  // phase 0 is over in this CTA (x's operand row may be overwritten); the operand rows of group A / B are in place
+  uint64_t* p0done = reinterpret_cast<uint64_t*>(smem + G.off_bar + 1536), *op_ready = p0done + 1;
+  int* work = reinterpret_cast<int*>(smem + G.off_bar + 1600);  // next chunk of group A / B to convert
+  uint8_t* act_x = act + G.x_off;
+  float2* pexs_x = pexs + G.xpe_off;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int H = bank.hidden, I = bank.inter;
   int err = 0;
@@ -479,8 +575,10 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
   if (threadIdx.x == 0) {
     for (int s = 0; s < 16; ++s) {
       mbar_init(&full0[s], NPROD), mbar_init(&empty0[s], 2);
-      mbar_init(&full1[s], NPROD), mbar_init(&empty1[s], KP1);
+      mbar_init(&full1[s], 1), mbar_init(&empty1[s], KP1);
     }
+    mbar_init(p0done, 1);
+    work[0] = work[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -507,7 +605,7 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
   }
   // routing inside the kernel: every CTA selects the top-k itself (same arithmetic and tie rules as
   // route_topk_kernel), so no launch and no round trip through global memory sits before the first copy
-  uint32_t* r_ord = reinterpret_cast<uint32_t*>(smem + G.off_act + G.act_stride[0]);  // scratch behind x in the operand area
+  uint32_t* r_ord = reinterpret_cast<uint32_t*>(smem + G.off_act);  // scratch in the operand area (x is converted into it later)
   float* r_score = reinterpret_cast<float*>(r_ord + 1024);
   int32_t* r_slot = reinterpret_cast<int32_t*>(r_ord + 2048);
   if (R.logits) {
@@ -594,7 +692,13 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
     const unsigned absent = __ballot_sync(0xffffffffu, lane < k && !present);
-    if (lane == 0) s_np = npres, s_n0 = cnt, s_absent = absent;
+    if (lane == 0) {
+      s_np = npres, s_n0 = cnt, s_absent = absent;
+      // one arrival per converted chunk of a group's hidden rows (the groups: see below)
+      const int b_ = npres >= 3 ? npres / 3 : (npres == 2 ? 1 : 0), a_ = npres - b_;
+      const int per_row = hidden_row_words(I) >> 9;
+      mbar_init(&op_ready[0], a_ > 0 ? a_ * per_row : 1), mbar_init(&op_ready[1], b_ > 0 ? b_ * per_row : 1);
+    }
   }
   __syncthreads();
   const int np = s_np;
@@ -609,6 +713,19 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
   const int roww = hidden_row_words(I);             // words of a hidden row in fused_hidden
   const int n1 = ntl * np;                          // phase-1 units of this CTA
   const int nst0 = G.nst[0], nst1 = G.nst[1];
+
+  // The operand rows of phase 1 (row p = p-th present expert) are made from the other CTAs' hidden values by whichever
+  // warps have time: convert_chunks.  Group A's rows lie clear of x when the operand area is large enough (k rows of
+  // inter against one of hidden): then a warp starts on them as soon as its own phase-0 work is done.  Otherwise, and
+  // for group B's rows, which overlap x, the end of phase 0 in this CTA is waited for.
+  const int row_stride1 = G.act_stride[1], nsub1 = I / SUB;
+  const bool early = nA * row_stride1 <= G.x_off && nA * nsub1 <= G.xpe_off;
+  auto convert_group = [&](int grp) {
+    const int pa = grp ? nA : 0, pn = grp ? nB : nA;
+    if (convert_chunks<FMT>(&work[grp], &op_ready[grp], pn * (roww >> 9), I / 16, roww, s_route + pa, act + (size_t)pa * row_stride1,
+                            pexs + pa * nsub1, row_stride1, nsub1, tag8, lane))
+      err = 2;
+  };
 
   if (warp < NPROD) {
     // ---------------- producers: four rows (and one scale array) of every unit per warp ----------------
@@ -657,50 +774,65 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
         }
       }
       // phase 1: the ring is cut into nst1 stages of the smaller unit.  Before a stage is first used, the
-      // phase-0 stages it overlaps must have been released by their last phase-0 unit.
+      // phase-0 stages it overlaps must have been released by their last phase-0 unit.  A unit's 16 rows are contiguous
+      // in the bank: copy warp w < NISSUE1 brings the whole of units w, w + NISSUE1, ... (one copy of the rows, one per
+      // scale array); the other copy warps go on to the hidden rows at once.
       {
         const int rb = G.row_bytes[1], sb = G.sc_bytes[1];
         const int S0 = G.stage_bytes[0], S1 = G.stage_bytes[1];
         // unit order: group A (tile by tile, its experts inside), then group B the same way
-        int pa = 0, pn = nA, pi = 0, tl = 0;
+        const int n1a = ntl * nA;
         // phase-0 stage s was used uses(s) = full + (s < rest) times
         const int full = n0 / nst0, rest = n0 - full * nst0;
-        const long long off_w = bank.off[t_w2] + (long long)warp * 4 * rb;
-        const long long off_s = warp < n_sc ? bank.off[t_w2 + 1 + warp] : -1;
-        const uint32_t tx = (uint32_t)(4 * rb + (off_s >= 0 ? sb : 0));
-        int idx = 0;
-        uint32_t round = 0;
-        int waited = -1;   // phase-0 stages 0..waited are known to be free
-        int end_byte = 0;  // end of the current phase-1 stage inside the ring
+        const uint32_t tx = (uint32_t)(16 * rb + n_sc * sb);
+        int idx = warp % nst1;
+        uint32_t round = 0;  // NISSUE1 <= nst1
+        int waited = -1;             // phase-0 stages 0..waited are known to be free
+        int end_byte = warp * S1;    // end of the previous unit's phase-1 stage inside the ring
         int s_end = 0, s_end_byte = 0;  // first phase-0 stage that starts at or behind end_byte, and its start
-        for (int q = 0; q < n1 && !err; ++q) {
+        for (int q = warp; warp < NISSUE1 && q < n1 && !err; q += NISSUE1) {
           if (round > 0) {
             if (!mbar_wait(&empty1[idx], (round - 1u) & 1u)) err = 1;
           } else {
             end_byte += S1;
-            while (s_end_byte < end_byte) s_end_byte += S0, ++s_end;  // stages waited..s_end-1 overlap this or an earlier stage
+            while (s_end_byte < end_byte) s_end_byte += S0, ++s_end;  // stages waited+1 .. s_end-1 overlap this or an earlier stage
             for (int s0 = waited + 1; s0 < s_end && s0 < nst0 && !err; ++s0) {
               const int uses = full + (s0 < rest ? 1 : 0);
               if (uses > 0 && !mbar_wait(&empty0[s0], (uint32_t)(uses - 1) & 1u)) err = 1;
               waited = s0;
             }
+            end_byte += (NISSUE1 - 1) * S1;
           }
           if (err) break;
-          const uint8_t* rec = bank.base + (size_t)s_slot[pa + pi] * bank.record_bytes;
+          const bool in_a = q < n1a;
+          const int qq = in_a ? q : q - n1a, pn = in_a ? nA : nB;
+          const int tl = qq / pn, p = (in_a ? 0 : nA) + (qq - tl * pn);
+          const uint8_t* rec = bank.base + (size_t)s_slot[p] * bank.record_bytes;
           uint8_t* dst = ring + (size_t)idx * S1;
           uint64_t* bar = &full1[idx];
           mbar_expect_tx(bar, tx);
-          bulk_g2s(dst + warp * 4 * rb, rec + off_w + (size_t)(t_begin + tl) * 16 * rb, (uint32_t)(4 * rb), bar);
-          if (off_s >= 0) bulk_g2s(dst + G.sc_off[1] + warp * sb, rec + off_s + (size_t)(t_begin + tl) * sb, (uint32_t)sb, bar);
-          if (++pi == pn) {
-            pi = 0;
-            if (++tl == ntl) tl = 0, pa = nA, pn = nB;
-          }
-          if (++idx == nst1) idx = 0, ++round;
+          bulk_g2s(dst, rec + bank.off[t_w2] + (size_t)(t_begin + tl) * 16 * rb, (uint32_t)(16 * rb), bar);
+          for (int a = 0; a < n_sc; ++a)
+            bulk_g2s(dst + G.sc_off[1] + a * sb, rec + bank.off[t_w2 + 1 + a] + (size_t)(t_begin + tl) * sb, (uint32_t)sb, bar);
+          idx += NISSUE1;
+          while (idx >= nst1) idx -= nst1, ++round;
         }
       }
       if (err && status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
     }
+    __syncwarp();
+    // All copies are on their way: the copy warps help with the operand rows.  Group B's are theirs alone, converted
+    // while the MMA warps work on group A.
+    auto wait_phase0 = [&]() {
+      if (!mbar_wait_quiet(p0done, 0u, lane)) err = 1;
+    };
+    if (!early) wait_phase0();
+    convert_group(0);
+    if (nB > 0) {
+      if (early) wait_phase0();
+      convert_group(1);
+    }
+    if (err && lane == 0 && status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
   } else {
     // ---------------- consumers: pair `pr` takes units pr, pr + NPAIR, ... of the CTA's stream ----------------
     constexpr int NPAIR = Fm<FMT>::NPAIR;
@@ -713,7 +845,7 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
       if (j * NCT < H / 16) {  // warp-uniform: the lanes of a sub-block convert together
         float v[16];
         unpack16_bf16(xa[j], xb[j], v);
-        convert_block<FMT>(act, pexs, b < H / 16 ? b : 0, b < H / 16, v);
+        convert_block<FMT>(act_x, pexs_x, b < H / 16 ? b : 0, b < H / 16, v);
       }
     }
     named_bar_sync(1, NCT);
@@ -747,7 +879,7 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
     skip_units(pr);
     for (int i = pr; i < n0; i += NPAIR, ++n_done) {
       if (!err && !mbar_wait(&full0[idx], rnd & 1u)) err = 1;
-      float2 r = unit_dot<FMT, 0, SDT>(ring + (size_t)idx * G.stage_bytes[0], G, act, pexs, zeros, g, t, part, 2);
+      float2 r = unit_dot<FMT, 0, SDT>(ring + (size_t)idx * G.stage_bytes[0], G, act_x, pexs_x, zeros, g, t, part, 2);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty0[idx]);
       r.x += __shfl_xor_sync(0xffffffffu, r.x, 1), r.y += __shfl_xor_sync(0xffffffffu, r.y, 1);
@@ -770,11 +902,13 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
       while (idx >= nst0) idx -= nst0, ++rnd;
       skip_units(NPAIR);
     }
-    // every pair is through with x, whose operand row the hidden rows are about to overwrite
+    // through with its phase-0 units, a warp helps with group A's operand rows (if they lie clear of x)
+    if (early) convert_group(0);
+    // every pair is through with x, whose operand row may now be overwritten with hidden rows
     named_bar_sync(1, NCT);
+    if (tid == 0) mbar_arrive(p0done);
+    if (!early) convert_group(0);
 
-    const int row_stride1 = G.act_stride[1];
-    const int nsub1 = I / SUB;
     const int kp = cw % KP1;               // the warp's part of the reduction dimension in phase 1
     constexpr int UPR = NCW / KP1;         // phase-1 units the consumer warps work on at a time
     static_assert(NCW % KP1 == 0, "the consumer warps must split into whole groups of KP1");
@@ -782,71 +916,10 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
     for (int gsel = 0; gsel < 2; ++gsel) {
       const int pa = gsel ? nA : 0, pn = gsel ? nB : nA;  // the group's experts: pa .. pa + pn - 1
       if (pn == 0) break;
-      // phase-1 operand: the group's hidden rows (operand row p = p-th present expert).  A block of 16 values is
-      // read until every word carries this launch's tag; the lanes of a warp go round together (the conversion
-      // shuffles between the lanes that share a sub-block).
-      const int nblk = I / 16, nblk_pad = roww / 16, total = pn * nblk_pad;  // padded: a warp's 32 blocks share a chunk
-      {
-        constexpr int SB = 3;  // blocks per thread and round (4 experts x 2880 in one round); all loads are issued first
-        for (int base = 0; base < total; base += SB * NCT) {
-          uint4 q[SB][4];
-          int rr[SB], bbk[SB];
-          bool ok[SB], bad[SB];
-#pragma unroll
-          for (int h = 0; h < SB; ++h) {
-            const int ix = base + h * NCT + tid;
-            rr[h] = ix < total ? ix / nblk_pad : 0;
-            bbk[h] = ix < total ? ix - rr[h] * nblk_pad : nblk;
-            ok[h] = bbk[h] < nblk;
-            if (!ok[h]) bbk[h] = 0;
-            rr[h] += pa;
-            bad[h] = ok[h];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) q[h][i] = make_uint4(0, 0, 0, 0);
-          }
-          for (uint32_t tries = 0;; ++tries) {
-#pragma unroll
-            for (int h = 0; h < SB; ++h) {
-              if (bad[h]) {
-                const uint32_t* src = fused_hidden + (size_t)s_route[rr[h]] * roww + ((bbk[h] >> 5) << 9) + ((bbk[h] & 31) << 2);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) q[h][i] = ld_relaxed_v4(src + 128 * i);
-              }
-            }
-            bool any = false;
-#pragma unroll
-            for (int h = 0; h < SB; ++h) {
-              if (bad[h]) {
-                uint32_t diff = 0;
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                  diff |= ((q[h][i].x ^ tag8) | (q[h][i].y ^ tag8) | (q[h][i].z ^ tag8) | (q[h][i].w ^ tag8)) & 0xffu;
-                bad[h] = diff != 0;
-                any |= bad[h];
-              }
-            }
-            if (!__any_sync(0xffffffffu, any)) break;
-            if (tries >= HIDDEN_TRIES) {  // a CTA did not deliver: flag it and go on with what is there
-              err = 2;
-              break;
-            }
-            if (tries > 4) __nanosleep(100);
-          }
-#pragma unroll
-          for (int h = 0; h < SB; ++h) {
-            if (base + h * NCT < total) {  // warp-uniform
-              float v[16];
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                v[4 * i] = __uint_as_float(q[h][i].x & 0xffffff00u), v[4 * i + 1] = __uint_as_float(q[h][i].y & 0xffffff00u);
-                v[4 * i + 2] = __uint_as_float(q[h][i].z & 0xffffff00u), v[4 * i + 3] = __uint_as_float(q[h][i].w & 0xffffff00u);
-              }
-              convert_block<FMT>(act + (size_t)rr[h] * row_stride1, pexs + rr[h] * nsub1, bbk[h], ok[h], v);
-            }
-          }
-        }
-      }
-      named_bar_sync(1, NCT);
+      // the group's operand rows: group B's are normally done by the copy warps by now (if those are still held up
+      // in the ring, the chunks are still there to take)
+      if (gsel == 1) convert_group(1);
+      if (!err && !mbar_wait_quiet(&op_ready[gsel], 0u, lane)) err = 1;
 
       // -------- phase 1 of the group: unit u = (tile u / pn, expert pa + u % pn); a warp takes part kp of every
       // UPR-th unit and leaves its partial sums in shared memory --------
@@ -1026,6 +1099,7 @@ bool make_geo_fmt(const BankView& v, int k, int sms, Geo* out) {
   G.off_bar = p, p += 2048;  // mbarriers (512 B), 512 zero bytes, pair exchange buffers
   G.off_act = p, p += act;
   G.off_pe = p, p += pe;
+  G.x_off = act - act0, G.xpe_off = (pe - pe0) / 8;
   G.max_tiles = (G.tiles1 + sms - 1) / sms;
   if (G.max_tiles > MAX_TILES) return false;
   G.off_part = p, p += G.max_tiles * KMAX * KP1 * 16 * 4;  // partial sums of the CTA's output tiles per expert and part
@@ -1140,7 +1214,7 @@ int launch_layer_fused(const BankView& v, const void* x, const float* logits, co
                        int32_t* indices_out, float* weights_out, int* status, cudaStream_t stream, const PeerLink* peer) {
   Geo G;
   if (!make_geo(v, k, &G) || n_experts > 1024) return CACHALOT_EUNSUPPORTED;
-  if (G.act_stride[1] * k < G.act_stride[0] + 12288) return CACHALOT_EUNSUPPORTED;  // the routing scratch sits behind x in the operand area
+  if (G.x_off + G.act_stride[0] < 12288) return CACHALOT_EUNSUPPORTED;  // the routing scratch (12 KB) borrows the operand area
   const int numerics = numerics_flags & 0xff;
   RouteArgs R = {};
   R.logits = logits, R.bias = bias, R.slot_table = slot_table, R.indices_out = indices_out, R.weights_out = weights_out;
@@ -1155,7 +1229,7 @@ bool layer_fused_supported(const BankView& v, int n_experts, int k) {
   Geo G;
   if (k < 1 || k > KMAX || n_experts < k || n_experts > 1024) return false;
   if (v.format == CACHALOT_BANK_AFFINE && (v.group != 128 || v.bits != 2)) return false;
-  return make_geo(v, k, &G) && G.act_stride[1] * k >= G.act_stride[0] + 12288;
+  return make_geo(v, k, &G) && G.x_off + G.act_stride[0] >= 12288;
 }
 
 }  // namespace cachalot
