@@ -56,7 +56,7 @@
 #include "kernels.cuh"
 
 #ifndef CB_UNROLL
-#define CB_UNROLL 4
+#define CB_UNROLL 2
 #endif
 
 namespace cachalot {
