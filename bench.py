@@ -38,8 +38,10 @@ HIDDEN, INTER, EXPERTS, TOPK, LAYERS = 4096, 2880, 384, 6, 40
 SWIGLU_LIMIT = 10.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# capture summarised under profiles/ (None until a capture exists for the workload)
-NCU_TRAFFIC_BYTES = {("affine2", 1, "fused"): 59843072 + 1057792, ("fp4", 1, "fused"): 112921344 + 16384}
+# capture summarised under profiles/ (None until a capture exists for the workload).  Writes: the kernel's own
+# 16 KB of output + 69 KB of hidden words; the capture's write counter also holds dirty lines of the bank fill that
+# the launch's reads evict from L2 (1.7 MB / 14 MB in the two captures), which are not this kernel's traffic.
+NCU_TRAFFIC_BYTES = {("affine2", 1, "fused"): 59829504 + 16384 + 69120, ("fp4", 1, "fused"): 112907264 + 16384 + 69120}
 
 
 def parse_args():
