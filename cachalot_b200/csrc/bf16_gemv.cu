@@ -10,7 +10,7 @@
 namespace cachalot {
 namespace {
 
-constexpr int BG_THREADS = 256;
+constexpr int BG_THREADS = 256;       // threads of a CTA; 512 where the staged activations leave room for one CTA per SM only
 
 __device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
   uint4 v;
@@ -40,18 +40,18 @@ __device__ __forceinline__ void fma8(float (&acc)[ROWS][WR], const uint4 (&w)[WR
   }
 }
 
-template <int ROWS, int WR, int UNROLL>
-__global__ void __launch_bounds__(BG_THREADS) bf16_gemv_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ w, int n, int k,
+template <int ROWS, int WR, int UNROLL, int THREADS>
+__global__ void __launch_bounds__(THREADS) bf16_gemv_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ w, int n, int k,
                                                                float* __restrict__ out) {
   extern __shared__ __align__(16) float xs[];  // [ROWS][k]
-  for (int i = threadIdx.x * 4; i < ROWS * k; i += BG_THREADS * 4)
+  for (int i = threadIdx.x * 4; i < ROWS * k; i += THREADS * 4)
     *reinterpret_cast<float4*>(xs + i) = *reinterpret_cast<const float4*>(x + i);
   __syncthreads();
   const int lane = threadIdx.x & 31;
-  const int warps = gridDim.x * (BG_THREADS / 32);
+  const int warps = gridDim.x * (THREADS / 32);
   const int steps = k / 256;  // a warp step covers 256 weights of a row
   const int groups = (n + WR - 1) / WR;  // a warp walks groups of WR consecutive weight rows
-  for (int gq = blockIdx.x * (BG_THREADS / 32) + (threadIdx.x >> 5); gq < groups; gq += warps) {
+  for (int gq = blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5); gq < groups; gq += warps) {
     const __nv_bfloat16* wr[WR];
 #pragma unroll
     for (int j = 0; j < WR; ++j) {
@@ -118,24 +118,25 @@ extern "C" int cachalot_bf16_gemv_f32(const float* x_f32, int rows, const void* 
   int per_sm = (int)((220 * 1024) / (smem + 1024));
   per_sm = per_sm < 1 ? 1 : (per_sm > 6 ? 6 : per_sm);
   const int wrows = rows == 1 ? 1 : 4;  // weight rows a warp takes at a time
-  const long long want = (((long long)n + wrows - 1) / wrows + BG_THREADS / 32 - 1) / (BG_THREADS / 32);
+  const int threads = per_sm == 1 && rows >= 6 ? 2 * BG_THREADS : BG_THREADS;  // sixteen warps per SM either way
+  const long long want = (((long long)n + wrows - 1) / wrows + threads / 32 - 1) / (threads / 32);
   const unsigned grid = (unsigned)(want < (long long)sms * per_sm ? want : (long long)sms * per_sm);
   cudaStream_t s = (cudaStream_t)stream;
   const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(weight_bf16);
   cudaError_t e = cudaSuccess;
   auto go = [&](auto kern) {
     if (smem > 48 * 1024) e = smem_optin_once(kern, 200 * 1024);
-    if (e == cudaSuccess) kern<<<grid, BG_THREADS, smem, s>>>(x_f32, w, n, k, out);
+    if (e == cudaSuccess) kern<<<grid, threads, smem, s>>>(x_f32, w, n, k, out);
   };
   switch (rows) {
-    case 1: go(bf16_gemv_kernel<1, 1, 4>); break;  // one weight row per warp, four 16-byte loads in flight per lane
-    case 2: go(bf16_gemv_kernel<2, 4, 1>); break;  // four weight rows per warp share every activation read
-    case 3: go(bf16_gemv_kernel<3, 4, 1>); break;
-    case 4: go(bf16_gemv_kernel<4, 4, 1>); break;
-    case 5: go(bf16_gemv_kernel<5, 4, 1>); break;
-    case 6: go(bf16_gemv_kernel<6, 4, 1>); break;
-    case 7: go(bf16_gemv_kernel<7, 4, 1>); break;
-    default: go(bf16_gemv_kernel<8, 4, 1>); break;
+    case 1: go(bf16_gemv_kernel<1, 1, 4, BG_THREADS>); break;  // one weight row per warp, four 16-byte loads in flight per lane
+    case 2: go(bf16_gemv_kernel<2, 4, 1, BG_THREADS>); break;  // four weight rows per warp share every activation read
+    case 3: go(bf16_gemv_kernel<3, 4, 1, BG_THREADS>); break;
+    case 4: go(bf16_gemv_kernel<4, 4, 1, BG_THREADS>); break;
+    case 5: go(bf16_gemv_kernel<5, 4, 1, BG_THREADS>); break;
+    case 6: threads > BG_THREADS ? go(bf16_gemv_kernel<6, 4, 1, 2 * BG_THREADS>) : go(bf16_gemv_kernel<6, 4, 1, BG_THREADS>); break;
+    case 7: threads > BG_THREADS ? go(bf16_gemv_kernel<7, 4, 1, 2 * BG_THREADS>) : go(bf16_gemv_kernel<7, 4, 1, BG_THREADS>); break;
+    default: threads > BG_THREADS ? go(bf16_gemv_kernel<8, 4, 1, 2 * BG_THREADS>) : go(bf16_gemv_kernel<8, 4, 1, BG_THREADS>); break;
   }
   if (e != cudaSuccess) return fail(CACHALOT_ECUDA, "bf16_gemv: %s", cudaGetErrorString(e));
   return check_launch("bf16_gemv");
