@@ -572,13 +572,15 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
   // memory is touched: the inputs may still be in the making by the previous kernel.  Both are no-ops otherwise.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x < 128) reinterpret_cast<uint32_t*>(smem + G.off_bar + 512)[threadIdx.x] = 0u;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < 16; ++s) {
-      mbar_init(&full0[s], NPROD), mbar_init(&empty0[s], 2);
-      mbar_init(&full1[s], 1), mbar_init(&empty1[s], KP1);
+  // one thread per barrier (a single thread would spend most of a microsecond on the 65 of them)
+  if (threadIdx.x >= 128 && threadIdx.x < 193) {
+    const int i = threadIdx.x - 128;  // bars: full0[16], empty0[16], full1[16], empty1[16]; then p0done
+    if (i < 64) {
+      mbar_init(&bars[i], i < 16 ? NPROD : i < 32 ? 2 : i < 48 ? 1 : KP1);
+    } else {
+      mbar_init(p0done, 1);
+      work[0] = work[1] = 0;
     }
-    mbar_init(p0done, 1);
-    work[0] = work[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
