@@ -587,9 +587,16 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
   // number of this exchange: every CTA reads the counter before any CTA can move it on (the last one to finish does)
   const uint32_t xe = P.world > 0 ? *reinterpret_cast<volatile const uint32_t*>(P.epoch) + 1u : 0u;
 
-  // number of this launch: every CTA reads it before any CTA can move it on (the last one to finish does, and none
-  // finishes before all have written their hidden values)
-  if (threadIdx.x == 0) s_tag = *reinterpret_cast<volatile const unsigned*>(&fused_epoch[0]);
+  // Number of this launch.  A CTA takes a ticket as it reads the number; the CTA with the last ticket moves the number
+  // on when it is through - every CTA has read it by then, whatever else happens.  The ticket is asked for here and
+  // looked at only at the end, so nobody waits for the atomic's round trip.
+  unsigned ticket = 0;
+  if (threadIdx.x == 0) {
+    unsigned now;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(now) : "l"(&fused_epoch[0]) : "memory");
+    s_tag = now;
+    ticket = atomicAdd(&fused_epoch[1], 1u);
+  }
   // consumers fetch their part of x before anything else (up to XB 16-element blocks per thread)
   constexpr int XB = 3;
   const int tid = threadIdx.x - NPROD * 32;
@@ -835,6 +842,12 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
       convert_group(1);
     }
     if (err && lane == 0 && status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
+    // the launch number moves on once per launch (the next launch reads it after this grid has completed)
+    if (threadIdx.x == 0 && ticket == gridDim.x - 1) {
+      const unsigned nx = tag32 + 1u;
+      fused_epoch[1] = 0u;
+      fused_epoch[0] = nx ? nx : 1u;
+    }
   } else {
     // ---------------- consumers: pair `pr` takes units pr, pr + NPAIR, ... of the CTA's stream ----------------
     constexpr int NPAIR = Fm<FMT>::NPAIR;
@@ -1020,16 +1033,6 @@ fused_decode_kernel(BankView bank, Geo G, RouteArgs R, const __nv_bfloat16* __re
           __threadfence();
           P.epoch[0] = xe;
         }
-      }
-    }
-    // the launch number moves on once per launch: by the CTA that takes the last ticket (every CTA has read the
-    // number long before: none gets here before all have written their hidden values)
-    if (tid == 0) {
-      const unsigned ticket = atomicAdd(&fused_epoch[1], 1u);
-      if (ticket == gridDim.x - 1) {
-        const unsigned nx = tag32 + 1u;
-        fused_epoch[1] = 0u;
-        fused_epoch[0] = nx ? nx : 1u;
       }
     }
     if (err && lane == 0 && status) atomicOr(status, CACHALOT_STATUS_WAIT_EXPIRED);
