@@ -100,7 +100,7 @@ __device__ __forceinline__ int hidden_word(int i) {  // position of value i of a
   const int b = i >> 4, v = i & 15;
   return (((b >> 5) * 4 + (v >> 2)) << 7) + ((b & 31) << 2) + (v & 3);
 }
-// {number of the next launch (never 0), CTAs of the current launch that have finished}
+// {number of the next launch (never 0), CTAs of the current launch that have read it and taken their ticket}
 __device__ unsigned fused_epoch[2] = {1u, 0u};
 
 // Routing done inside the kernel (logits == nullptr: the caller passes slots and weights instead).
